@@ -1,0 +1,372 @@
+// Batched Cholesky -> unit-diagonal upper factor of the inverse, for all Hessians of a layer at once.
+//
+// The reference (forge/gptq.py:156-170) runs three LAPACK-style calls per matrix:
+//   L = chol(Hp);  Hinv = cholesky_inverse(L);  T = chol(Hinv, upper);  U = T / diag(T)
+// (4/3 C^3 flop).  The same U follows from ONE Cholesky of the index-reversed matrix and ONE
+// triangular inverse (2/3 C^3 flop):  with J the reversal permutation and  J Hp J = L L^T,
+//   T = J L^-1 J   (upper, T^T T = Hp^-1),   U = diag(T)^-1 T = J [diag(L) L^-1] J .
+// The caller hands in A = J Hp J (forge_hessian_gather_damp writes it that way), so everything here
+// is a plain lower Cholesky plus a lower triangular inverse whose rows are scaled by diag(L) as they
+// are produced; one last pass rotates the result by 180 degrees into the upper triangle.
+//
+// Blocked right-looking factorisation with 64-column panels, every step batched over the matrices:
+//   diag  : factor the 64x64 diagonal block in shared memory, invert it (Dinv), emit the matching
+//           diagonal block of the scaled inverse and udiag;
+//   panel : rows below  <-  rows below * Dinv^T   (TRSM as a GEMM); the result is also stored
+//           transposed in the unused upper triangle so that the next step reads both operands with
+//           unit stride;
+//   syrk  : trailing lower triangle -= panel * panel^T   (128x128 tiles, 8x8 per thread, fp32 FMA).
+// The inverse proceeds block column by block column from the right:
+//   M[below, j] = -( M[below, below] * L[below, j] ) * Dinv_j .
+// All arithmetic is fp32 FMA on the SIMT pipe: the solver needs fp32-accurate U, and a
+// split-precision tensor-core variant has not been validated against the oracle.
+#include "common.cuh"
+
+using namespace forge;
+
+namespace {
+
+constexpr int NB = 64;        // panel width
+constexpr int TM = 128;       // tile rows
+constexpr int KC = 16;        // k-chunk staged in shared memory
+constexpr int AS = KC + 4;    // padded row stride of the A chunk (floats)
+
+// acc[8][TN/16] += A[TM x K] * B[K x TN].   A(i,k) = A[i*lda + k], B(k,n) = B[k*ldb + n].
+// Rows i >= m_valid, columns n >= n_valid and k >= K read as zero; with tri_row0 >= 0 the A operand is
+// lower triangular in global indexing: A(i,k) reads as zero when (tri_k0 + k) > (tri_row0 + i).
+// 256 threads: ty = tid/16 owns rows ty + 16*ii, tx = tid%16 owns columns tx*4+e (+64 for TN=128).
+template <int TN>
+__device__ __forceinline__ void tile_gemm(float (&acc)[8][TN / 16], const float *__restrict__ A, int64_t lda,
+                                          int m_valid, const float *__restrict__ B, int64_t ldb, int n_valid,
+                                          int K, bool vec, int64_t tri_row0, int64_t tri_k0, float *As,
+                                          float *Bs) {
+    const int tid = threadIdx.x;
+    const int ty = tid >> 4, tx = tid & 15;
+    for (int k0 = 0; k0 < K; k0 += KC) {
+        // ---- stage A chunk [TM][KC]
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int v = tid + 256 * i;
+            const int row = v >> 2, kq = (v & 3) * 4;
+            float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (row < m_valid && k0 + kq < K) {
+                const float *src = A + (int64_t)row * lda + k0 + kq;
+                if (vec && k0 + kq + 3 < K) val = *reinterpret_cast<const float4 *>(src);
+                else {
+                    val.x = src[0];
+                    if (k0 + kq + 1 < K) val.y = src[1];
+                    if (k0 + kq + 2 < K) val.z = src[2];
+                    if (k0 + kq + 3 < K) val.w = src[3];
+                }
+                if (tri_row0 >= 0) {
+                    const int64_t gr = tri_row0 + row, gk = tri_k0 + k0 + kq;
+                    if (gk + 0 > gr) val.x = 0.f;
+                    if (gk + 1 > gr) val.y = 0.f;
+                    if (gk + 2 > gr) val.z = 0.f;
+                    if (gk + 3 > gr) val.w = 0.f;
+                }
+            }
+            *reinterpret_cast<float4 *>(As + row * AS + kq) = val;
+        }
+        // ---- stage B chunk [KC][TN]
+#pragma unroll
+        for (int i = 0; i < TN / 64; ++i) {
+            const int v = tid + 256 * i;
+            const int row = v / (TN / 4), n4 = (v % (TN / 4)) * 4;
+            float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (k0 + row < K && n4 < n_valid) {
+                const float *src = B + (int64_t)(k0 + row) * ldb + n4;
+                if (vec && n4 + 3 < n_valid) val = *reinterpret_cast<const float4 *>(src);
+                else {
+                    val.x = src[0];
+                    if (n4 + 1 < n_valid) val.y = src[1];
+                    if (n4 + 2 < n_valid) val.z = src[2];
+                    if (n4 + 3 < n_valid) val.w = src[3];
+                }
+            }
+            *reinterpret_cast<float4 *>(Bs + row * TN + n4) = val;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < KC; ++kk) {
+            float a[8];
+#pragma unroll
+            for (int ii = 0; ii < 8; ++ii) a[ii] = As[(ty + 16 * ii) * AS + kk];
+            float bv[TN / 16];
+            {
+                const float4 b0 = *reinterpret_cast<const float4 *>(Bs + kk * TN + tx * 4);
+                bv[0] = b0.x; bv[1] = b0.y; bv[2] = b0.z; bv[3] = b0.w;
+                if (TN == 128) {
+                    const float4 b1 = *reinterpret_cast<const float4 *>(Bs + kk * TN + 64 + tx * 4);
+                    bv[TN / 16 - 4] = b1.x; bv[TN / 16 - 3] = b1.y; bv[TN / 16 - 2] = b1.z; bv[TN / 16 - 1] = b1.w;
+                }
+            }
+#pragma unroll
+            for (int ii = 0; ii < 8; ++ii)
+#pragma unroll
+                for (int jj = 0; jj < TN / 16; ++jj) acc[ii][jj] = fmaf(a[ii], bv[jj], acc[ii][jj]);
+        }
+        __syncthreads();
+    }
+}
+
+__device__ __forceinline__ int col_of(int tx, int jj) { return (jj < 4) ? tx * 4 + jj : 64 + tx * 4 + (jj - 4); }
+
+struct CholWs {
+    float *dinv;  // [nb][nblk][2][NB][NB]  (0: Dinv, 1: Dinv^T)
+};
+
+// ---- diag: factor + invert the diagonal block of step k (one CTA per matrix) -----------------
+__global__ void __launch_bounds__(256) chol_diag_kernel(float *__restrict__ Aall, int64_t C, int k, int nblk,
+                                                         float *__restrict__ dinv_all, float *__restrict__ Uall,
+                                                         float *__restrict__ udiag, int32_t *__restrict__ info) {
+    __shared__ float D[NB][NB + 1];
+    __shared__ float Di[NB][NB + 1];
+    __shared__ int bad_col;
+    const int b = blockIdx.x, tid = threadIdx.x;
+    float *A = Aall + (int64_t)b * C * C;
+    const int64_t cb = (int64_t)k * NB;
+    const int nbk = (int)imin64(NB, C - cb);
+    if (tid == 0) bad_col = -1;
+    for (int e = tid; e < NB * NB; e += 256) {
+        const int r = e / NB, c = e % NB;
+        float v = (r == c) ? 1.0f : 0.0f;
+        if (r < nbk && c < nbk && c <= r) v = A[(cb + r) * C + cb + c];
+        if (c > r) v = 0.0f;
+        D[r][c] = v;
+    }
+    __syncthreads();
+    for (int j = 0; j < nbk; ++j) {
+        if (tid == 0) {
+            const float piv = D[j][j];
+            if (!(piv > 0.0f) && bad_col < 0) bad_col = j;
+            D[j][j] = sqrtf(piv);
+        }
+        __syncthreads();
+        const float inv = __fdiv_rn(1.0f, D[j][j]);
+        if (tid > j && tid < nbk) D[tid][j] = __fmul_rn(D[tid][j], inv);
+        __syncthreads();
+        // trailing update of the lower triangle: D[i][l] -= D[i][j]*D[l][j], i >= l > j
+        for (int e = tid; e < NB * NB; e += 256) {
+            const int i = e / NB, l = e % NB;
+            if (l > j && i >= l && i < nbk) D[i][l] = fmaf(-D[i][j], D[l][j], D[i][l]);
+        }
+        __syncthreads();
+    }
+    // inverse of the lower-triangular block, one column per thread (forward substitution)
+    if (tid < NB) {
+        const int c = tid;
+        for (int i = 0; i < NB; ++i) {
+            float s = (i == c) ? 1.0f : 0.0f;
+            if (i < c) { Di[i][c] = 0.0f; continue; }
+            for (int l = c; l < i; ++l) s = fmaf(-D[i][l], Di[l][c], s);
+            Di[i][c] = __fdiv_rn(s, D[i][i]);
+        }
+    }
+    __syncthreads();
+    float *dinv = dinv_all + ((int64_t)b * nblk + k) * 2 * NB * NB;
+    float *U = Uall + (int64_t)b * C * C;
+    for (int e = tid; e < NB * NB; e += 256) {
+        const int r = e / NB, c = e % NB;
+        dinv[e] = Di[r][c];
+        dinv[NB * NB + e] = Di[c][r];
+        if (r < nbk && c < nbk) {
+            if (c <= r) A[(cb + r) * C + cb + c] = D[r][c];
+            // diagonal block of the row-scaled inverse  diag(L) L^-1  (unit diagonal)
+            U[(cb + r) * C + cb + c] = (c < r) ? __fmul_rn(D[r][r], Di[r][c]) : ((c == r) ? 1.0f : 0.0f);
+        }
+    }
+    if (tid < nbk) udiag[(int64_t)b * C + (C - 1 - (cb + tid))] = __fdiv_rn(1.0f, D[tid][tid]);
+    if (tid == 0 && bad_col >= 0 && info[b] == 0) info[b] = (int32_t)(cb + bad_col + 1);
+}
+
+// ---- panel: rows below the diagonal block <- rows * Dinv^T; also stored transposed above ------
+__global__ void __launch_bounds__(256) chol_panel_kernel(float *__restrict__ Aall, int64_t C, int k, int nblk,
+                                                          const float *__restrict__ dinv_all, int vec) {
+    __shared__ __align__(16) float As[TM * AS];
+    __shared__ __align__(16) float Bs[KC * 64];
+    const int b = blockIdx.y, tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+    float *A = Aall + (int64_t)b * C * C;
+    const int64_t cb = (int64_t)k * NB, rb = cb + NB;
+    const int64_t i0 = (int64_t)blockIdx.x * TM;
+    const int m_valid = (int)imin64(TM, C - rb - i0);
+    if (m_valid <= 0) return;
+    const float *dinvT = dinv_all + ((int64_t)b * nblk + k) * 2 * NB * NB + NB * NB;
+    float acc[8][4];
+#pragma unroll
+    for (int ii = 0; ii < 8; ++ii)
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) acc[ii][jj] = 0.0f;
+    tile_gemm<64>(acc, A + (rb + i0) * C + cb, C, m_valid, dinvT, NB, NB, NB, vec != 0, -1, 0, As, Bs);
+#pragma unroll
+    for (int ii = 0; ii < 8; ++ii) {
+        const int i = ty + 16 * ii;
+        if (i < m_valid) {
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+                const int c = tx * 4 + jj;
+                A[(rb + i0 + i) * C + cb + c] = acc[ii][jj];
+                A[(cb + c) * C + rb + i0 + i] = acc[ii][jj];
+            }
+        }
+    }
+}
+
+// ---- syrk: trailing lower triangle -= panel * panel^T -----------------------------------------
+__global__ void __launch_bounds__(256) chol_syrk_kernel(float *__restrict__ Aall, int64_t C, int k, int vec) {
+    if (blockIdx.y > blockIdx.x) return;  // upper tiles are not needed
+    __shared__ __align__(16) float As[TM * AS];
+    __shared__ __align__(16) float Bs[KC * 128];
+    const int b = blockIdx.z, tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+    float *A = Aall + (int64_t)b * C * C;
+    const int64_t cb = (int64_t)k * NB, rb = cb + NB;
+    const int64_t i0 = (int64_t)blockIdx.x * TM, j0 = (int64_t)blockIdx.y * 128;
+    const int m_valid = (int)imin64(TM, C - rb - i0);
+    const int n_valid = (int)imin64(128, C - rb - j0);
+    if (m_valid <= 0 || n_valid <= 0) return;
+    float acc[8][8];
+#pragma unroll
+    for (int ii = 0; ii < 8; ++ii)
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) acc[ii][jj] = 0.0f;
+    tile_gemm<128>(acc, A + (rb + i0) * C + cb, C, m_valid, A + cb * C + rb + j0, C, n_valid, NB, vec != 0, -1, 0,
+                   As, Bs);
+#pragma unroll
+    for (int ii = 0; ii < 8; ++ii) {
+        const int i = ty + 16 * ii;
+        if (i >= m_valid) continue;
+        float *row = A + (rb + i0 + i) * C + rb + j0;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int c0 = h * 64 + tx * 4;
+            if (vec && c0 + 3 < n_valid) {
+                float4 v = *reinterpret_cast<float4 *>(row + c0);
+                v.x -= acc[ii][4 * h + 0]; v.y -= acc[ii][4 * h + 1];
+                v.z -= acc[ii][4 * h + 2]; v.w -= acc[ii][4 * h + 3];
+                *reinterpret_cast<float4 *>(row + c0) = v;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (c0 + e < n_valid) row[c0 + e] -= acc[ii][4 * h + e];
+            }
+        }
+    }
+}
+
+// ---- triangular inverse, block column j: M[below,j] = -(M[below,below] L[below,j]) Dinv_j -------
+__global__ void __launch_bounds__(256) trtri_step_kernel(const float *__restrict__ Aall, float *__restrict__ Uall,
+                                                          int64_t C, int j, int nblk,
+                                                          const float *__restrict__ dinv_all, int vec) {
+    __shared__ __align__(16) float As[TM * AS];
+    __shared__ __align__(16) float Bs[KC * 64];
+    const int b = blockIdx.y, tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+    const float *A = Aall + (int64_t)b * C * C;
+    float *U = Uall + (int64_t)b * C * C;
+    const int64_t cb = (int64_t)j * NB, rb = cb + NB;
+    const int64_t i0 = (int64_t)blockIdx.x * TM;
+    const int m_valid = (int)imin64(TM, C - rb - i0);
+    if (m_valid <= 0) return;
+    float acc[8][4];
+#pragma unroll
+    for (int ii = 0; ii < 8; ++ii)
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) acc[ii][jj] = 0.0f;
+    // T = M[rows, rb .. rows] * L[rb .. , cb:cb+64]; the K range ends at this tile's last row
+    const int K = (int)imin64(C - rb, i0 + TM);
+    tile_gemm<64>(acc, U + (rb + i0) * C + rb, C, m_valid, A + rb * C + cb, C, NB, K, vec != 0, rb + i0, rb, As, Bs);
+    // park T in the destination (rows are private to this CTA), then multiply by -Dinv_j
+#pragma unroll
+    for (int ii = 0; ii < 8; ++ii) {
+        const int i = ty + 16 * ii;
+        if (i < m_valid) {
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) U[(rb + i0 + i) * C + cb + tx * 4 + jj] = acc[ii][jj];
+        }
+    }
+    __threadfence_block();
+    __syncthreads();
+    const float *dinv = dinv_all + ((int64_t)b * nblk + j) * 2 * NB * NB;
+#pragma unroll
+    for (int ii = 0; ii < 8; ++ii)
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) acc[ii][jj] = 0.0f;
+    tile_gemm<64>(acc, U + (rb + i0) * C + cb, C, m_valid, dinv, NB, NB, NB, vec != 0, -1, 0, As, Bs);
+#pragma unroll
+    for (int ii = 0; ii < 8; ++ii) {
+        const int i = ty + 16 * ii;
+        if (i < m_valid) {
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) U[(rb + i0 + i) * C + cb + tx * 4 + jj] = -acc[ii][jj];
+        }
+    }
+}
+
+// ---- rotate the lower-triangular scaled inverse into the upper triangle (in place) --------------
+// U[t][k] = M[C-1-t][C-1-k] for k >= t.  Sources lie on or below the diagonal, destinations on or
+// above it; the diagonal is 1 on both sides, so the pass is safe in place.
+__global__ void rotate_upper_kernel(float *__restrict__ Uall, int64_t C, const int32_t *__restrict__ info,
+                                    float *__restrict__ udiag) {
+    const int b = blockIdx.z;
+    float *U = Uall + (int64_t)b * C * C;
+    const bool bad = info[b] != 0;
+    const int64_t t = (int64_t)blockIdx.y * 8 + threadIdx.y;
+    const int64_t k = (int64_t)blockIdx.x * 32 + threadIdx.x;
+    if (t >= C || k >= C) return;
+    if (bad) {
+        U[t * C + k] = (t == k) ? 1.0f : 0.0f;
+        if (t == k) udiag[(int64_t)b * C + t] = 1.0f;
+        return;
+    }
+    if (k > t) U[t * C + k] = U[(C - 1 - t) * C + (C - 1 - k)];
+}
+
+__global__ void zero_lower_kernel(float *__restrict__ Uall, int64_t C) {
+    const int b = blockIdx.z;
+    float *U = Uall + (int64_t)b * C * C;
+    const int64_t t = (int64_t)blockIdx.y * 8 + threadIdx.y;
+    const int64_t k = (int64_t)blockIdx.x * 32 + threadIdx.x;
+    if (t < C && k < t) U[t * C + k] = 0.0f;
+}
+
+__global__ void info_clear_kernel(int32_t *info, int nb) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < nb) info[b] = 0;
+}
+
+}  // namespace
+
+extern "C" int64_t forge_chol_workspace_bytes(int nb, int64_t C) {
+    const int64_t nblk = cdiv(C, NB);
+    return (int64_t)nb * nblk * 2 * NB * NB * (int64_t)sizeof(float) + 256;
+}
+
+extern "C" int forge_chol_inv_upper_batched(float *A, int nb, int64_t C, float *U, float *udiag, int32_t *info,
+                                            int zero_lower, void *ws, void *stream) {
+    FORGE_REQUIRE(A && U && udiag && info && ws, "null pointer");
+    FORGE_REQUIRE(nb > 0 && C > 0, "empty batch");
+    FORGE_REQUIRE(A != U, "A must not alias U");
+    FORGE_REQUIRE((uintptr_t)ws % 16 == 0, "workspace must be 16-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int nblk = (int)cdiv(C, NB);
+    float *dinv = (float *)ws;
+    const int vec = (C % 4 == 0) && ((uintptr_t)A % 16 == 0) && ((uintptr_t)U % 16 == 0);
+    info_clear_kernel<<<(nb + 127) / 128, 128, 0, st>>>(info, nb);
+    for (int k = 0; k < nblk; ++k) {
+        chol_diag_kernel<<<nb, 256, 0, st>>>(A, C, k, nblk, dinv, U, udiag, info);
+        const int64_t m = C - (int64_t)(k + 1) * NB;
+        if (m > 0) {
+            const unsigned nt = (unsigned)cdiv(m, TM);
+            chol_panel_kernel<<<dim3(nt, nb), 256, 0, st>>>(A, C, k, nblk, dinv, vec);
+            chol_syrk_kernel<<<dim3(nt, nt, nb), 256, 0, st>>>(A, C, k, vec);
+        }
+    }
+    for (int j = nblk - 2; j >= 0; --j) {
+        const int64_t m = C - (int64_t)(j + 1) * NB;
+        const unsigned nt = (unsigned)cdiv(m, TM);
+        trtri_step_kernel<<<dim3(nt, nb), 256, 0, st>>>(A, U, C, j, nblk, dinv, vec);
+    }
+    dim3 g2((unsigned)cdiv(C, 32), (unsigned)cdiv(C, 8), nb);
+    rotate_upper_kernel<<<g2, dim3(32, 8), 0, st>>>(U, C, info, udiag);
+    if (zero_lower) zero_lower_kernel<<<g2, dim3(32, 8), 0, st>>>(U, C);
+    return check_launch("forge_chol_inv_upper_batched");
+}

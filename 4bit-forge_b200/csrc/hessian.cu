@@ -1,0 +1,409 @@
+// Per-expert Hessian accumulation  H_b = beta_b * H_b + alpha_b * X_b^T X_b  as a grouped
+// tcgen05 / TMEM GEMM with the routing gather fused into the operand load.
+//
+// Shapes: for expert b the GEMM is  [C x n_b] * [n_b x C]  with K = n_b = the tokens routed to b.
+// Both operands are the SAME matrix X (bf16, [T, C] row-major, channels contiguous), read by token
+// index, so both are "MN-major" for the tensor core: a K-tile of 64 tokens x 64 channels is 64
+// rows of 128 bytes, stored with the 128-byte swizzle (16-byte chunk index XOR row-in-8) that the
+// UMMA shared-memory descriptor expects.  The rows are fetched with 16-byte cp.async copies whose
+// source row is token_idx[...] — that is the fused top-k gather: no permuted copy of X exists.
+//
+// One persistent CTA per SM.  A CTA tile is 256 x 256 outputs: two M=128 x N=256 x K=16 bf16 MMAs
+// per k-step into two fp32 accumulators that fill the SM's 512 TMEM columns.  Per 64-token k-tile the
+// CTA stages 256 + 256 channels (64 KB; 32 KB on diagonal tiles where both operands coincide), i.e.
+// 128 flop per staged byte.  Only tiles on or above the diagonal are computed; the epilogue scales
+// by alpha/beta and optionally mirrors into the lower triangle.
+//
+// Warp roles (160 threads): warps 0-3 load (cp.async, 3-stage ring, completion published to the
+// async proxy by fence.proxy.async + mbarrier arrive) and later run the epilogue (tcgen05.ld, one
+// TMEM lane = one output row per thread); warp 4 allocates TMEM and its lane 0 issues the MMAs and
+// the tcgen05.commit that frees a stage / publishes the accumulator.
+// Every mbarrier wait is bounded by a clock64 budget; on expiry the CTA raises FORGE_ERR_TIMEOUT in
+// the status word, drains its copies, frees TMEM and returns.
+#include "common.cuh"
+
+using namespace forge;
+
+namespace {
+
+constexpr int kTile = 256;                    // output tile edge (channels)
+constexpr int kKT = 64;                       // tokens per k-tile
+constexpr int kSubBytes = kKT * 128;          // one 64-channel x 64-token sub-tile: 8 KB
+constexpr int kOperandBytes = 4 * kSubBytes;  // 256 channels: 32 KB
+constexpr int kStageBytes = 2 * kOperandBytes;
+constexpr int kStages = 3;
+constexpr int kLag = 2;                       // cp.async groups in flight per thread
+constexpr int kProducerThreads = 128;
+constexpr int kThreads = 160;
+constexpr long long kWaitBudget = 4000000000LL;  // clock64 ticks (~2 s)
+constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+
+struct HessParams {
+    const __nv_bfloat16 *X;
+    int64_t ldx, C;
+    const int32_t *token_idx;
+    const int64_t *offsets;
+    int nb;
+    float *H;
+    const int64_t *n_prev;
+    int mirror;
+    int32_t *status;
+    int nt;    // tiles per edge
+    int ntri;  // tiles per expert (upper triangle)
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok;
+}
+// Bounded wait: false when the budget ran out or another thread of the CTA already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > kWaitBudget) {
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void *src, bool pred) {
+    const int sz = pred ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// UMMA shared-memory descriptor, MN-major operand, 128-byte swizzle:
+//   bits [0,14)  start address >> 4          bits [16,30) leading byte offset >> 4 (next 64-element
+//   MN block: 8 KB)   bits [32,46) stride byte offset >> 4 (next group of 8 K rows: 1 KB)
+//   bits [46,48) version = 1                  bits [61,64) layout = 2 (SWIZZLE_128B)
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(kSubBytes >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor: D fp32, A/B bf16, both MN-major, N = 256, M = 128.
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) | ((256u >> 3) << 17) |
+                            ((128u >> 4) << 24);
+
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        :
+        : "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(kIdesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void tile_coords(int p, int nt, int &ti, int &tj) {
+    ti = 0;
+    while (p >= nt - ti) { p -= nt - ti; ++ti; }
+    tj = ti + p;
+}
+
+__global__ void __launch_bounds__(kThreads, 1) hessian_tc_kernel(const HessParams P) {
+    extern __shared__ uint8_t smem_raw[];
+    // 1 KB alignment: the swizzle pattern and the descriptors (base_offset = 0) assume it
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *smem_al = smem_raw + (smem_base - smem_u32(smem_raw));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_al + kStages * kStageBytes);
+    // bars[0..2] full, [3..5] empty, [6] acc_full, [7] acc_empty, then tmem base + abort flag
+    uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + 8);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
+    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + 3);
+    const uint32_t bar_acc_full = smem_u32(bars + 6), bar_acc_empty = smem_u32(bars + 7);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(bar_full + 8 * s, kProducerThreads);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        mbar_init(bar_acc_full, 1);
+        mbar_init(bar_acc_empty, kProducerThreads);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 4) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
+                     "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    const int64_t C = P.C;
+    const int total_tiles = P.nb * P.ntri;
+    uint32_t it = 0;         // k-tile counter of this CTA (ring position), same sequence in both roles
+    uint32_t tile_iter = 0;  // tiles done by this CTA
+
+    if (warp < 4) {
+        // ------------------------------ producers + epilogue ------------------------------
+        const int rsub = lane >> 3;   // row within a group of 4
+        const int chunk = lane & 7;   // 16-byte chunk within the 128-byte row
+        int pend = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            const int b = tile / P.ntri;
+            int ti, tj;
+            tile_coords(tile % P.ntri, P.nt, ti, tj);
+            const int64_t off = P.offsets[b];
+            const int64_t n = P.offsets[b + 1] - off;
+            if (n <= 0) continue;
+            const bool diag = (ti == tj);
+            const int nkt = (int)((n + kKT - 1) / kKT);
+            const int32_t *tl = P.token_idx ? P.token_idx + off : nullptr;
+            bool ok = true;
+            for (int kt = 0; kt < nkt && ok; ++kt) {
+                const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                ok = mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag);
+                if (!ok) break;
+                const uint32_t stage = smem_base + s * kStageBytes;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int row = warp * 16 + i * 4 + rsub;  // token row inside the k-tile
+                    const int64_t kidx = (int64_t)kt * kKT + row;
+                    const bool rvalid = kidx < n;
+                    int64_t tok = 0;
+                    if (rvalid) tok = tl ? (int64_t)tl[kidx] : off + kidx;
+                    const __nv_bfloat16 *xrow = P.X + tok * P.ldx;
+                    const uint32_t drow = (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4));
+#pragma unroll
+                    for (int sub = 0; sub < 8; ++sub) {
+                        if (diag && sub >= 4) break;
+                        const int64_t ch = (int64_t)(sub < 4 ? ti : tj) * kTile + (sub & 3) * 64 + chunk * 8;
+                        const bool v = rvalid && (ch < C);
+                        cp_async16_zfill(stage + sub * kSubBytes + drow, v ? (const void *)(xrow + ch) : (const void *)P.X, v);
+                    }
+                }
+                cp_async_commit();
+                ++pend;
+                ++it;
+                if (pend > kLag) {
+                    cp_async_wait<kLag>();
+                    fence_proxy_async();
+                    mbar_arrive(bar_full + 8 * ((it - pend) % kStages));
+                    --pend;
+                }
+            }
+            while (pend > 0) {  // publish the stages still in flight
+                if (pend >= 2) cp_async_wait<1>();
+                else cp_async_wait<0>();
+                fence_proxy_async();
+                mbar_arrive(bar_full + 8 * ((it - pend) % kStages));
+                --pend;
+            }
+            if (!ok) break;
+            // ---- epilogue: TMEM -> registers -> global
+            ok = mbar_wait(bar_acc_full, tile_iter & 1u, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const int64_t np = P.n_prev ? P.n_prev[b] : 0;
+            const double Ntot = (double)(np + n);
+            const float alpha = (float)(2.0 / Ntot);
+            const float beta = (float)((double)np / Ntot);
+            float *Hb = P.H + (int64_t)b * C * C;
+#pragma unroll 1
+            for (int mh = 0; mh < 2; ++mh) {
+                const int64_t m = (int64_t)ti * kTile + mh * 128 + warp * 32 + lane;
+#pragma unroll 1
+                for (int cc = 0; cc < 8; ++cc) {
+                    const int64_t n0 = (int64_t)tj * kTile + cc * 32;
+                    // whole 32x32 sub-block below the diagonal or out of range: nothing to store
+                    const int64_t m_lo = (int64_t)ti * kTile + mh * 128 + warp * 32;
+                    if (n0 + 31 < m_lo || n0 >= C || m_lo >= C) continue;  // warp-uniform
+                    uint32_t v[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(mh * 256 + cc * 32), v);
+                    tmem_ld_wait();
+                    if (m < C) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const int64_t nn = n0 + i;
+                            if (nn < C && nn >= m) {
+                                float val = alpha * __uint_as_float(v[i]);
+                                if (np > 0) val = fmaf(beta, Hb[m * C + nn], val);
+                                Hb[m * C + nn] = val;
+                                if (P.mirror && nn > m) Hb[nn * C + m] = val;
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(bar_acc_empty);
+            ++tile_iter;
+        }
+        cp_async_wait<0>();
+    } else {
+        // ------------------------------ MMA issuer (warp 4) ------------------------------
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            const int b = tile / P.ntri;
+            int ti, tj;
+            tile_coords(tile % P.ntri, P.nt, ti, tj);
+            const int64_t n = P.offsets[b + 1] - P.offsets[b];
+            if (n <= 0) continue;
+            const bool diag = (ti == tj);
+            const int nkt = (int)((n + kKT - 1) / kKT);
+            bool ok = mbar_wait(bar_acc_empty, (tile_iter & 1u) ^ 1u, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            for (int kt = 0; kt < nkt && ok; ++kt) {
+                const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                ok = mbar_wait(bar_full + 8 * s, ph, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t a_base = smem_base + s * kStageBytes;
+                    const uint32_t b_base = diag ? a_base : a_base + kOperandBytes;
+#pragma unroll
+                    for (int kk = 0; kk < kKT / 16; ++kk) {
+                        const uint64_t bdesc = make_desc(b_base + kk * 2048);
+#pragma unroll
+                        for (int mh = 0; mh < 2; ++mh) {
+                            const uint64_t adesc = make_desc(a_base + mh * 2 * kSubBytes + kk * 2048);
+                            umma_bf16(tmem_base + mh * 256, adesc, bdesc, (kt > 0 || kk > 0) ? 1u : 0u);
+                        }
+                    }
+                    umma_commit(bar_empty + 8 * s);  // frees the stage once these MMAs have read it
+                }
+                __syncwarp();
+                ++it;
+            }
+            if (!ok) break;
+            if (lane == 0) umma_commit(bar_acc_full);
+            __syncwarp();
+            ++tile_iter;
+        }
+    }
+    // ------------------------------ teardown ------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && tid == 0 && P.status) atomicExch(P.status, FORGE_ERR_TIMEOUT);
+    if (warp == 4) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+// Plain-FMA validation kernel (same contract, upper triangle + optional mirror): 16x16 outputs per
+// CTA, tokens staged 16 at a time.  Exists so that the tensor-core kernel can be cross-checked on the
+// GPU itself; it is not on the product path unless FORGE_HESS_SIMT is passed.
+__global__ void hessian_simt_kernel(const HessParams P) {
+    __shared__ float xa[16][17], xb[16][17];
+    const int b = blockIdx.z;
+    const int64_t C = P.C;
+    const int64_t m0 = (int64_t)blockIdx.y * 16, n0 = (int64_t)blockIdx.x * 16;
+    if (n0 + 15 < m0) return;
+    const int64_t off = P.offsets[b];
+    const int64_t n = P.offsets[b + 1] - off;
+    if (n <= 0) return;
+    const int32_t *tl = P.token_idx ? P.token_idx + off : nullptr;
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    float acc = 0.0f;
+    for (int64_t k0 = 0; k0 < n; k0 += 16) {
+        const int64_t kidx = k0 + ty;
+        float va = 0.0f, vb = 0.0f;
+        if (kidx < n) {
+            const int64_t tok = tl ? (int64_t)tl[kidx] : off + kidx;
+            if (m0 + tx < C) va = __bfloat162float(P.X[tok * P.ldx + m0 + tx]);
+            if (n0 + tx < C) vb = __bfloat162float(P.X[tok * P.ldx + n0 + tx]);
+        }
+        xa[ty][tx] = va;
+        xb[ty][tx] = vb;
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < 16; ++k) acc = fmaf(xa[k][ty], xb[k][tx], acc);
+        __syncthreads();
+    }
+    const int64_t m = m0 + ty, nn = n0 + tx;
+    if (m < C && nn < C && nn >= m) {
+        const int64_t np = P.n_prev ? P.n_prev[b] : 0;
+        const double Ntot = (double)(np + n);
+        const float alpha = (float)(2.0 / Ntot), beta = (float)((double)np / Ntot);
+        float *Hb = P.H + (int64_t)b * C * C;
+        float val = alpha * acc;
+        if (np > 0) val = fmaf(beta, Hb[m * C + nn], val);
+        Hb[m * C + nn] = val;
+        if (P.mirror && nn > m) Hb[nn * C + m] = val;
+    }
+}
+
+}  // namespace
+
+extern "C" int forge_hessian_grouped(const void *X_bf16, int64_t ldx, int64_t C, const int32_t *token_idx,
+                                     const int64_t *offsets, int nb, float *H, const int64_t *n_prev, int flags,
+                                     int32_t *status, void *stream) {
+    FORGE_REQUIRE(X_bf16 && offsets && H, "null pointer");
+    FORGE_REQUIRE(nb > 0 && C > 0 && ldx >= C, "bad sizes");
+    cudaStream_t st = (cudaStream_t)stream;
+    HessParams P{};
+    P.X = (const __nv_bfloat16 *)X_bf16; P.ldx = ldx; P.C = C; P.token_idx = token_idx; P.offsets = offsets;
+    P.nb = nb; P.H = H; P.n_prev = n_prev; P.mirror = (flags & FORGE_HESS_MIRROR) ? 1 : 0; P.status = status;
+    P.nt = (int)cdiv(C, kTile);
+    P.ntri = P.nt * (P.nt + 1) / 2;
+    if (flags & FORGE_HESS_SIMT) {
+        dim3 grid((unsigned)cdiv(C, 16), (unsigned)cdiv(C, 16), nb);
+        hessian_simt_kernel<<<grid, dim3(16, 16), 0, st>>>(P);
+        return check_launch("forge_hessian_grouped(simt)");
+    }
+    FORGE_REQUIRE(C % 8 == 0 && ldx % 8 == 0, "C and ldx must be multiples of 8 (16-byte row chunks)");
+    FORGE_REQUIRE((uintptr_t)X_bf16 % 16 == 0, "X must be 16-byte aligned");
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(hessian_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)kSmemBytes);
+        if (e != cudaSuccess) {
+            set_error("forge_hessian_grouped: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+            return FORGE_ERR_LAUNCH;
+        }
+        attr_done = true;
+    }
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int64_t total = (int64_t)nb * P.ntri;
+    const int grid = (int)imin64(total, sms);
+    hessian_tc_kernel<<<grid, kThreads, kSmemBytes, st>>>(P);
+    return check_launch("forge_hessian_grouped");
+}

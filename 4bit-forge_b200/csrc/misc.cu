@@ -1,0 +1,490 @@
+// HBM-bandwidth kernels of the path: fp8 block de-quantisation, routing lists, Hessian
+// preparation (NaN scan, pruning, permutation gather + damping), code de-quantisation, and the
+// two bit-exact packers.  All are plain coalesced SIMT kernels; none is GEMM-shaped.
+#include "common.cuh"
+#include <stdarg.h>
+
+namespace forge {
+static thread_local char g_err[512] = "";
+void set_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+}  // namespace forge
+using namespace forge;
+
+extern "C" int forge_version(void) { return 100; }
+extern "C" const char *forge_last_error(void) { return g_err; }
+
+// --------------------------------------------------------------------------------------------
+// fp8 e4m3 block de-quantisation
+// --------------------------------------------------------------------------------------------
+__device__ __forceinline__ float fp8_e4m3_to_f32(uint8_t v) {
+    __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)v, __NV_E4M3);
+    return __half2float(__half(h));
+}
+
+// One thread converts 16 consecutive elements of a row (16 B in, 32 B out).
+__global__ void fp8_dequant_vec16(const uint8_t *__restrict__ w, const float *__restrict__ sinv,
+                                  __nv_bfloat16 *__restrict__ out, int64_t O, int64_t I, int64_t nI,
+                                  int64_t so, int64_t si) {
+    const int64_t vec_per_row = I / 16;
+    const int64_t total = O * vec_per_row;
+    for (int64_t v = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < total;
+         v += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t o = v / vec_per_row, i0 = (v % vec_per_row) * 16;
+        const uint4 raw = *reinterpret_cast<const uint4 *>(w + o * I + i0);
+        const uint8_t *b = reinterpret_cast<const uint8_t *>(&raw);
+        const float *srow = sinv + (o / so) * nI;
+        __align__(16) __nv_bfloat16 r[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+            const float s = srow[(i0 + e) / si];
+            r[e] = __float2bfloat16_rn(fp8_e4m3_to_f32(b[e]) * s);
+        }
+        uint4 *dst = reinterpret_cast<uint4 *>(out + o * I + i0);
+        dst[0] = reinterpret_cast<uint4 *>(r)[0];
+        dst[1] = reinterpret_cast<uint4 *>(r)[1];
+    }
+}
+
+__global__ void fp8_dequant_scalar(const uint8_t *__restrict__ w, const float *__restrict__ sinv,
+                                   __nv_bfloat16 *__restrict__ out, int64_t O, int64_t I, int64_t nI,
+                                   int64_t so, int64_t si) {
+    const int64_t total = O * I;
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+         e += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t o = e / I, i = e % I;
+        out[e] = __float2bfloat16_rn(fp8_e4m3_to_f32(w[e]) * sinv[(o / so) * nI + i / si]);
+    }
+}
+
+extern "C" int forge_fp8_block_dequant(const void *w_fp8, const float *scale_inv, void *out_bf16, int64_t O,
+                                       int64_t I, int64_t nO, int64_t nI, void *stream) {
+    FORGE_REQUIRE(w_fp8 && scale_inv && out_bf16, "null pointer");
+    FORGE_REQUIRE(O > 0 && I > 0 && nO > 0 && nI > 0, "empty shape");
+    FORGE_REQUIRE(I % nI == 0, "I must be a multiple of the number of column tiles");
+    const int64_t si = I / nI;
+    const int64_t so = (cdiv(O, si) == nO) ? si : cdiv(O, nO);
+    FORGE_REQUIRE(cdiv(O, so) <= nO, "scale grid has too few row tiles");
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool vec = (I % 16 == 0) && ((uintptr_t)w_fp8 % 16 == 0) && ((uintptr_t)out_bf16 % 16 == 0);
+    const int64_t work = vec ? O * (I / 16) : O * I;
+    const int threads = 256;
+    const int blocks = (int)imin64(cdiv(work, threads), 148 * 16);
+    if (vec)
+        fp8_dequant_vec16<<<blocks, threads, 0, st>>>((const uint8_t *)w_fp8, scale_inv,
+                                                      (__nv_bfloat16 *)out_bf16, O, I, nI, so, si);
+    else
+        fp8_dequant_scalar<<<blocks, threads, 0, st>>>((const uint8_t *)w_fp8, scale_inv,
+                                                       (__nv_bfloat16 *)out_bf16, O, I, nI, so, si);
+    return check_launch("forge_fp8_block_dequant");
+}
+
+// --------------------------------------------------------------------------------------------
+// routing lists: one CTA per local expert scans the [T,k] id table twice (count, then fill), so the
+// tokens of an expert come out in ascending order without a sort.
+// --------------------------------------------------------------------------------------------
+template <bool FILL>
+__global__ void route_scan_kernel(const int32_t *__restrict__ ids, int64_t T, int k, int e_begin,
+                                  int32_t *__restrict__ counts, const int64_t *__restrict__ offsets,
+                                  int32_t *__restrict__ lists) {
+    const int e_local = blockIdx.x;
+    const int e = e_begin + e_local;
+    __shared__ int warp_tot[32];
+    __shared__ int base_s;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    if (threadIdx.x == 0) base_s = 0;
+    __syncthreads();
+    const int64_t out0 = FILL ? offsets[e_local] : 0;
+    for (int64_t t0 = 0; t0 < T; t0 += blockDim.x) {
+        const int64_t t = t0 + threadIdx.x;
+        int hit = 0;
+        if (t < T) {
+            for (int j = 0; j < k; ++j) hit |= (ids[t * k + j] == e);
+        }
+        const unsigned bal = __ballot_sync(0xffffffffu, hit);
+        if (lane == 0) warp_tot[warp] = __popc(bal);
+        __syncthreads();
+        int before = 0, total = 0;
+        for (int w = 0; w < nwarp; ++w) {
+            const int c = warp_tot[w];
+            if (w < warp) before += c;
+            total += c;
+        }
+        if (FILL && hit) {
+            const int pos = base_s + before + __popc(bal & ((1u << lane) - 1u));
+            lists[out0 + pos] = (int32_t)t;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) base_s += total;
+        __syncthreads();
+    }
+    if (!FILL && threadIdx.x == 0) counts[e_local] = base_s;
+}
+
+__global__ void route_offsets_kernel(const int32_t *__restrict__ counts, int n, int64_t *__restrict__ offsets) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        int64_t acc = 0;
+        for (int i = 0; i < n; ++i) {
+            offsets[i] = acc;
+            acc += counts[i];
+        }
+        offsets[n] = acc;
+    }
+}
+
+extern "C" int forge_route_build_lists(const int32_t *topk_ids, int64_t T, int k, int e_begin, int e_count,
+                                       int32_t *counts, int64_t *offsets, int32_t *token_lists, void *stream) {
+    FORGE_REQUIRE(topk_ids && counts && offsets && token_lists, "null pointer");
+    FORGE_REQUIRE(T >= 0 && k > 0 && e_count > 0 && e_begin >= 0, "bad sizes");
+    cudaStream_t st = (cudaStream_t)stream;
+    route_scan_kernel<false><<<e_count, 512, 0, st>>>(topk_ids, T, k, e_begin, counts, nullptr, nullptr);
+    route_offsets_kernel<<<1, 32, 0, st>>>(counts, e_count, offsets);
+    route_scan_kernel<true><<<e_count, 512, 0, st>>>(topk_ids, T, k, e_begin, counts, offsets, token_lists);
+    return check_launch("forge_route_build_lists");
+}
+
+__global__ void counts_add_kernel(int64_t *n_prev, const int64_t *offsets, int nb) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < nb) n_prev[b] += offsets[b + 1] - offsets[b];
+}
+extern "C" int forge_counts_add(int64_t *n_prev, const int64_t *offsets, int nb, void *stream) {
+    FORGE_REQUIRE(n_prev && offsets && nb > 0, "bad arguments");
+    counts_add_kernel<<<(nb + 127) / 128, 128, 0, (cudaStream_t)stream>>>(n_prev, offsets, nb);
+    return check_launch("forge_counts_add");
+}
+
+// --------------------------------------------------------------------------------------------
+// Hessian preparation
+// --------------------------------------------------------------------------------------------
+__global__ void scan_init_kernel(const int64_t *n_samples, int32_t *invalid, int nb) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < nb) invalid[b] = (n_samples != nullptr && n_samples[b] == 0) ? 1 : 0;
+}
+
+__global__ void scan_nan_kernel(const float *__restrict__ H, int64_t elems, int32_t *invalid) {
+    const int b = blockIdx.y;
+    const float *Hb = H + (int64_t)b * elems;
+    int bad = 0;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    if ((elems % 4 == 0) && ((uintptr_t)Hb % 16 == 0)) {
+        const float4 *H4 = reinterpret_cast<const float4 *>(Hb);
+        for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < elems / 4; i += stride) {
+            const float4 v = H4[i];
+            bad |= (v.x != v.x) | (v.y != v.y) | (v.z != v.z) | (v.w != v.w);
+        }
+    } else {
+        for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < elems; i += stride) {
+            const float v = Hb[i];
+            bad |= (v != v);
+        }
+    }
+    bad = __any_sync(0xffffffffu, bad);
+    if (bad && (threadIdx.x & 31) == 0) atomicOr(invalid + b, 1);
+}
+
+__global__ void scan_diag_kernel(const float *__restrict__ H, int64_t C, const int32_t *__restrict__ invalid,
+                                 float *__restrict__ diag, uint8_t *__restrict__ pruned) {
+    const int b = blockIdx.y;
+    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const bool inv = invalid[b] != 0;
+    const float d = inv ? 1.0f : H[(int64_t)b * C * C + c * C + c];
+    const bool pr = (!inv) && (d == 0.0f);
+    diag[(int64_t)b * C + c] = pr ? 1.0f : d;
+    pruned[(int64_t)b * C + c] = pr ? 1 : 0;
+}
+
+extern "C" int forge_hessian_scan(const float *H, int nb, int64_t C, const int64_t *n_samples, float *diag,
+                                  uint8_t *pruned, int32_t *invalid, void *stream) {
+    FORGE_REQUIRE(H && diag && pruned && invalid, "null pointer");
+    FORGE_REQUIRE(nb > 0 && C > 0, "empty batch");
+    cudaStream_t st = (cudaStream_t)stream;
+    scan_init_kernel<<<(nb + 127) / 128, 128, 0, st>>>(n_samples, invalid, nb);
+    const int64_t elems = C * C;
+    const int bx = (int)imin64(cdiv(elems / 4 + 1, 256), 64);
+    scan_nan_kernel<<<dim3(bx, nb), 256, 0, st>>>(H, elems, invalid);
+    scan_diag_kernel<<<dim3((unsigned)cdiv(C, 256), nb), 256, 0, st>>>(H, C, invalid, diag, pruned);
+    return check_launch("forge_hessian_scan");
+}
+
+// W[b,:,c] = 0 for the pruned columns c of Hessian slot u_map[b]   (forge/gptq.py:115)
+__global__ void apply_pruned_kernel(void *W, int dtype, int64_t R, int64_t C, const uint8_t *__restrict__ pruned,
+                                    const int32_t *__restrict__ u_map) {
+    const int b = blockIdx.z;
+    const int u = u_map ? u_map[b] : b;
+    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C || !pruned[(int64_t)u * C + c]) return;
+    for (int64_t r = blockIdx.y; r < R; r += gridDim.y) {
+        const int64_t i = ((int64_t)b * R + r) * C + c;
+        if (dtype == FORGE_DTYPE_BF16) reinterpret_cast<__nv_bfloat16 *>(W)[i] = __float2bfloat16_rn(0.0f);
+        else reinterpret_cast<float *>(W)[i] = 0.0f;
+    }
+}
+extern "C" int forge_weight_apply_pruned(void *W, int w_dtype, int nb, int64_t R, int64_t C,
+                                         const uint8_t *pruned, const int32_t *u_map, void *stream) {
+    FORGE_REQUIRE(W && pruned && nb > 0 && R > 0 && C > 0, "bad arguments");
+    dim3 grid((unsigned)cdiv(C, 128), (unsigned)imin64(R, 64), nb);
+    apply_pruned_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(W, w_dtype, R, C, pruned, u_map);
+    return check_launch("forge_weight_apply_pruned");
+}
+
+// wzero[b,c] = all_r W[b,r,c] == 0.  One thread per column, coalesced across columns; almost every
+// thread leaves at r = 0.
+__global__ void zero_cols_kernel(const void *__restrict__ W, int dtype, int64_t R, int64_t C,
+                                 uint8_t *__restrict__ wzero) {
+    const int b = blockIdx.y;
+    const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    int allz = 1;
+    for (int64_t r = 0; r < R; ++r) {
+        if (ld_as_f32(W, dtype, ((int64_t)b * R + r) * C + c) != 0.0f) { allz = 0; break; }
+    }
+    wzero[(int64_t)b * C + c] = (uint8_t)allz;
+}
+extern "C" int forge_weight_zero_cols(const void *W, int w_dtype, int nb, int64_t R, int64_t C, uint8_t *wzero,
+                                      void *stream) {
+    FORGE_REQUIRE(W && wzero && nb > 0 && R > 0 && C > 0, "bad arguments");
+    zero_cols_kernel<<<dim3((unsigned)cdiv(C, 128), nb), 128, 0, (cudaStream_t)stream>>>(W, w_dtype, R, C, wzero);
+    return check_launch("forge_weight_zero_cols");
+}
+
+__device__ __forceinline__ float hp_diag_value(const float *Hb, int64_t C, int64_t i, const int32_t *perm_b,
+                                               const uint8_t *pruned_b, const uint8_t *wzero_b, bool inv) {
+    if (wzero_b && wzero_b[i]) return 1.0f;
+    if (inv) return 1.0f;
+    const int64_t pi = perm_b ? perm_b[i] : i;
+    if (pruned_b && pruned_b[pi]) return 1.0f;
+    return Hb[pi * C + pi];
+}
+
+__global__ void damp_kernel(const float *__restrict__ H, int64_t C, const int32_t *__restrict__ perm,
+                            const uint8_t *__restrict__ pruned, const uint8_t *__restrict__ wzero,
+                            const int32_t *__restrict__ invalid, float rel_damp, float *__restrict__ damp_out) {
+    const int b = blockIdx.x;
+    const float *Hb = H + (int64_t)b * C * C;
+    const int32_t *pb = perm ? perm + (int64_t)b * C : nullptr;
+    const uint8_t *prb = pruned ? pruned + (int64_t)b * C : nullptr;
+    const uint8_t *wzb = wzero ? wzero + (int64_t)b * C : nullptr;
+    const bool inv = invalid ? invalid[b] != 0 : false;
+    double acc = 0.0;
+    for (int64_t i = threadIdx.x; i < C; i += blockDim.x) acc += (double)hp_diag_value(Hb, C, i, pb, prb, wzb, inv);
+    __shared__ double red[32];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += red[w];
+        const float mean = (float)(t / (double)C);
+        damp_out[b] = rel_damp * mean;
+    }
+}
+
+// One CTA per (output row i, matrix b): stage row perm[i] of H in shared memory, then emit
+// Hp[i, :] through the permutation, index-reversed, with the fix-ups and the damping applied.
+__global__ void gather_damp_kernel(const float *__restrict__ H, int64_t C, const int32_t *__restrict__ perm,
+                                   const uint8_t *__restrict__ pruned, const uint8_t *__restrict__ wzero,
+                                   const int32_t *__restrict__ invalid, const float *__restrict__ damp,
+                                   float *__restrict__ A, float *__restrict__ Hp_out) {
+    extern __shared__ float row[];
+    const int b = blockIdx.y;
+    const int64_t i = blockIdx.x;
+    const float *Hb = H + (int64_t)b * C * C;
+    const int32_t *pb = perm ? perm + (int64_t)b * C : nullptr;
+    const uint8_t *prb = pruned ? pruned + (int64_t)b * C : nullptr;
+    const uint8_t *wzb = wzero ? wzero + (int64_t)b * C : nullptr;
+    const bool inv = invalid ? invalid[b] != 0 : false;
+    const int64_t pi = pb ? pb[i] : i;
+    const bool row_dead = inv || (prb && prb[pi]);
+    const bool row_wz = wzb && wzb[i];
+    if (!row_dead && !row_wz) {
+        for (int64_t c = threadIdx.x; c < C; c += blockDim.x) row[c] = Hb[pi * C + c];
+    }
+    __syncthreads();
+    const float dmp = damp[b];
+    float *Arow = A + (int64_t)b * C * C + (C - 1 - i) * C;
+    float *Hrow = Hp_out ? Hp_out + (int64_t)b * C * C + i * C : nullptr;
+    for (int64_t jo = threadIdx.x; jo < C; jo += blockDim.x) {
+        const int64_t j = C - 1 - jo;  // output column jo of the reversed matrix <-> position j
+        float v;
+        if (row_wz || (wzb && wzb[j])) v = (i == j) ? 1.0f : 0.0f;
+        else {
+            const int64_t pj = pb ? pb[j] : j;
+            if (row_dead || (prb && prb[pj])) v = (pi == pj) ? 1.0f : 0.0f;
+            else v = row[pj];
+        }
+        if (i == j) v += dmp;
+        Arow[jo] = v;
+        if (Hrow) Hrow[j] = v;
+    }
+}
+
+extern "C" int forge_hessian_gather_damp(const float *H, int nb, int64_t C, const int32_t *perm,
+                                         const uint8_t *pruned, const uint8_t *wzero, const int32_t *invalid,
+                                         float rel_damp, float *A, float *Hp_out, float *damp_out, void *stream) {
+    FORGE_REQUIRE(H && A && damp_out, "null pointer");
+    FORGE_REQUIRE(nb > 0 && C > 0, "empty batch");
+    FORGE_REQUIRE(C * 4 <= 200 * 1024, "C too large for the row staging buffer");
+    FORGE_REQUIRE(A != H, "A must not alias H");
+    cudaStream_t st = (cudaStream_t)stream;
+    damp_kernel<<<nb, 256, 0, st>>>(H, C, perm, pruned, wzero, invalid, rel_damp, damp_out);
+    const size_t smem = (size_t)C * 4;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaFuncSetAttribute(gather_damp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        attr_done = true;
+    }
+    gather_damp_kernel<<<dim3((unsigned)C, nb), 256, smem, st>>>(H, C, perm, pruned, wzero, invalid, damp_out, A,
+                                                                Hp_out);
+    return check_launch("forge_hessian_gather_damp");
+}
+
+// --------------------------------------------------------------------------------------------
+// de-quantise codes: out = (q - q0) * s in fp32   (forge/utils/engine.py:93-96)
+// --------------------------------------------------------------------------------------------
+__global__ void dequant_kernel(const uint8_t *__restrict__ q, const float *__restrict__ scales,
+                               const float *__restrict__ qzeros, int64_t rows, int64_t C, int gs, int64_t G,
+                               void *__restrict__ out, int out_dtype) {
+    const int64_t total = rows * C;
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total;
+         e += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = e / C, c = e % C;
+        const int64_t g = r * G + c / gs;
+        const float w = ((float)q[e] - qzeros[g]) * scales[g];
+        if (out_dtype == FORGE_DTYPE_BF16) reinterpret_cast<__nv_bfloat16 *>(out)[e] = __float2bfloat16_rn(w);
+        else reinterpret_cast<float *>(out)[e] = w;
+    }
+}
+extern "C" int forge_dequantize(const uint8_t *q, const float *scales, const float *qzeros, int64_t rows,
+                                int64_t C, int gs, void *out, int out_dtype, void *stream) {
+    FORGE_REQUIRE(q && scales && qzeros && out, "null pointer");
+    FORGE_REQUIRE(rows > 0 && C > 0 && gs > 0, "bad sizes");
+    const int64_t G = cdiv(C, gs);
+    const int blocks = (int)imin64(cdiv(rows * C, 256), 148 * 32);
+    dequant_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(q, scales, qzeros, rows, C, gs, G, out, out_dtype);
+    return check_launch("forge_dequantize");
+}
+
+// --------------------------------------------------------------------------------------------
+// dense int4 packer: one thread per output word (8 codes)
+// --------------------------------------------------------------------------------------------
+__global__ void pack_int4_kernel(const uint8_t *__restrict__ q, const float *__restrict__ qzeros, int64_t rows,
+                                 int64_t C, int gs, int64_t G, int64_t CP, int32_t *__restrict__ packed,
+                                 int aligned8) {
+    const int64_t total = rows * CP;
+    for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < total;
+         w += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = w / CP, j = w % CP;
+        const int64_t c0 = j * 8;
+        uint8_t b[8];
+        if (aligned8 && c0 + 8 <= C) {
+            const uint2 raw = *reinterpret_cast<const uint2 *>(q + r * C + c0);
+            *reinterpret_cast<uint2 *>(b) = raw;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) b[i] = (c0 + i < C) ? q[r * C + c0 + i] : 0;
+        }
+        uint32_t acc = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (c0 + i < C) {
+                const int8_t z = (int8_t)(int)qzeros[r * G + (c0 + i) / gs];
+                const int8_t v = (int8_t)((int8_t)b[i] - z);
+                const uint8_t u = (uint8_t)(int8_t)(v + 8);
+                acc += ((uint32_t)u) << (4 * i);
+            }
+        }
+        packed[w] = (int32_t)acc;
+    }
+}
+extern "C" int forge_pack_int4(const uint8_t *q, const float *qzeros, int64_t rows, int64_t C, int gs,
+                               int32_t *packed, void *stream) {
+    FORGE_REQUIRE(q && qzeros && packed, "null pointer");
+    FORGE_REQUIRE(rows > 0 && C > 0 && gs > 0, "bad sizes");
+    const int64_t G = cdiv(C, gs), CP = cdiv(C, 8);
+    const int aligned8 = (C % 8 == 0) && ((uintptr_t)q % 8 == 0);
+    const int blocks = (int)imin64(cdiv(rows * CP, 256), 148 * 32);
+    pack_int4_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(q, qzeros, rows, C, gs, G, CP, packed, aligned8);
+    return check_launch("forge_pack_int4");
+}
+
+// --------------------------------------------------------------------------------------------
+// sparse 1:4 packer.  One thread per (pair of 32-column groups, row); rows are the fast index so
+// that M, scales and the 16-byte output are coalesced.  Each 4-column group of the row is one
+// 32-bit word of codes, so the kept code is a byte select inside a register.
+// --------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint64_t pack_one_group(const uint32_t words[8], uint32_t bitmask, float scale,
+                                                   int64_t col0, int64_t C) {
+    uint32_t idx16 = 0, qw32 = 0x88888888u;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t sub = (bitmask >> (4 * i)) & 0xFu;
+        if (sub == 0u) continue;
+        const int c = __ffs(sub) - 1;
+        idx16 |= (uint32_t)(c & 3) << (2 * i);
+        if (col0 + i * 4 + c < C) {
+            const uint32_t qv = (words[i] >> (8 * c)) & 0xFu;
+            qw32 = (qw32 & ~(0xFu << (4 * i))) | (qv << (4 * i));
+        }
+    }
+    const __nv_bfloat16 sb = __float2bfloat16_rn(scale);
+    const uint16_t sbits = *reinterpret_cast<const uint16_t *>(&sb);
+    return ((uint64_t)sbits << 48) | ((uint64_t)(idx16 & 0xFFFFu) << 32) | (uint64_t)qw32;
+}
+
+__global__ void pack_sparse14_kernel(const uint8_t *__restrict__ q, const uint32_t *__restrict__ M,
+                                     const float *__restrict__ scales, int64_t R, int64_t C, int64_t G32,
+                                     int64_t G2, ulonglong2 *__restrict__ out, int vec_ok) {
+    const int64_t total = G2 * R;
+    for (int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; tid < total;
+         tid += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = tid % R, g2 = tid / R;
+        ulonglong2 o;
+        uint64_t halves[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int64_t gid = 2 * g2 + h;
+            if (gid >= G32) { halves[h] = 0ull; continue; }
+            const int64_t col0 = gid * 32;
+            uint32_t words[8];
+            if (vec_ok && col0 + 32 <= C) {
+                const uint4 *src = reinterpret_cast<const uint4 *>(q + r * C + col0);
+                const uint4 a = src[0], bq = src[1];
+                words[0] = a.x; words[1] = a.y; words[2] = a.z; words[3] = a.w;
+                words[4] = bq.x; words[5] = bq.y; words[6] = bq.z; words[7] = bq.w;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    uint32_t w = 0;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int64_t cid = col0 + i * 4 + c;
+                        if (cid < C) w |= (uint32_t)q[r * C + cid] << (8 * c);
+                    }
+                    words[i] = w;
+                }
+            }
+            halves[h] = pack_one_group(words, M[gid * R + r], scales[gid * R + r], col0, C);
+        }
+        o.x = halves[0];
+        o.y = halves[1];
+        out[g2 * R + r] = o;
+    }
+}
+extern "C" int forge_pack_sparse14(const uint8_t *q, const uint32_t *M, const float *scales32, int64_t R,
+                                   int64_t C, uint64_t *out, void *stream) {
+    FORGE_REQUIRE(q && M && scales32 && out, "null pointer");
+    FORGE_REQUIRE(R > 0 && C > 0, "bad sizes");
+    FORGE_REQUIRE((uintptr_t)out % 16 == 0, "output must be 16-byte aligned");
+    const int64_t G32 = cdiv(C, 32), G2 = (G32 + 1) >> 1;
+    const int vec_ok = (C % 16 == 0) && ((uintptr_t)q % 16 == 0);
+    const int blocks = (int)imin64(cdiv(G2 * R, 256), 148 * 32);
+    pack_sparse14_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(q, M, scales32, R, C, G32, G2,
+                                                                 (ulonglong2 *)out, vec_ok);
+    return check_launch("forge_pack_sparse14");
+}

@@ -1,0 +1,180 @@
+"""Torch-tensor wrappers over the C ABI.  PyTorch supplies device memory and the stream; every
+computation happens in libforge_b200.so.  Shapes follow include/forge_b200.h."""
+from __future__ import annotations
+
+import torch
+
+from . import _abi
+from ._abi import call, ptr, stream_ptr, dtype_code, query
+
+
+def _dev(t):
+    return t.device
+
+
+def fp8_block_dequant(w_fp8: torch.Tensor, scale_inv: torch.Tensor) -> torch.Tensor:
+    """bf16( fp32(w_fp8) * scale_inv[tile] ) — forge/utils/io.py:533-563, :864-874 on the device."""
+    O, I = w_fp8.shape
+    nO, nI = scale_inv.shape
+    w8 = w_fp8.contiguous().view(torch.uint8)
+    out = torch.empty((O, I), dtype=torch.bfloat16, device=_dev(w_fp8))
+    call("forge_fp8_block_dequant", ptr(w8), ptr(scale_inv.to(torch.float32).contiguous()), ptr(out), O, I, nO, nI,
+         stream_ptr())
+    return out
+
+
+def route_build_lists(topk_ids: torch.Tensor, e_begin: int, e_count: int):
+    """topk_ids [T,k] int32 -> (counts int32 [e_count], offsets int64 [e_count+1], token_lists int32 [T*k])."""
+    T, k = topk_ids.shape
+    ids = topk_ids.to(torch.int32).contiguous()
+    dev = _dev(ids)
+    counts = torch.empty(e_count, dtype=torch.int32, device=dev)
+    offsets = torch.empty(e_count + 1, dtype=torch.int64, device=dev)
+    lists = torch.empty(max(T * k, 1), dtype=torch.int32, device=dev)
+    call("forge_route_build_lists", ptr(ids), T, k, e_begin, e_count, ptr(counts), ptr(offsets), ptr(lists),
+         stream_ptr())
+    return counts, offsets, lists
+
+
+def hessian_grouped(X: torch.Tensor, C: int, token_idx, offsets: torch.Tensor, H: torch.Tensor, n_prev=None,
+                    mirror: bool = True, simt: bool = False, status=None):
+    """H[b] = beta*H[b] + alpha * X_b^T X_b (see forge_hessian_grouped).  X bf16 [T, ldx>=C]; H fp32 [nb,C,C]."""
+    assert X.dtype == torch.bfloat16 and X.dim() == 2 and H.dtype == torch.float32
+    nb = H.shape[0]
+    assert offsets.dtype == torch.int64 and offsets.numel() == nb + 1
+    flags = (_abi.HESS_MIRROR if mirror else 0) | (_abi.HESS_SIMT if simt else 0)
+    own_status = status is None
+    if own_status:
+        status = torch.zeros(1, dtype=torch.int32, device=_dev(X))
+    call("forge_hessian_grouped", ptr(X), X.stride(0), C, ptr(token_idx), ptr(offsets), nb, ptr(H), ptr(n_prev), flags,
+         ptr(status), stream_ptr())
+    return status
+
+
+def counts_add(n_prev: torch.Tensor, offsets: torch.Tensor):
+    call("forge_counts_add", ptr(n_prev), ptr(offsets), n_prev.numel(), stream_ptr())
+
+
+def hessian_scan(H: torch.Tensor, n_samples=None):
+    nb, C, _ = H.shape
+    dev = _dev(H)
+    diag = torch.empty((nb, C), dtype=torch.float32, device=dev)
+    pruned = torch.empty((nb, C), dtype=torch.uint8, device=dev)
+    invalid = torch.empty(nb, dtype=torch.int32, device=dev)
+    call("forge_hessian_scan", ptr(H), nb, C, ptr(n_samples), ptr(diag), ptr(pruned), ptr(invalid), stream_ptr())
+    return diag, pruned, invalid
+
+
+def weight_apply_pruned(W: torch.Tensor, pruned: torch.Tensor, u_map=None):
+    nb, R, C = W.shape
+    call("forge_weight_apply_pruned", ptr(W), dtype_code(W), nb, R, C, ptr(pruned), ptr(u_map), stream_ptr())
+
+
+def weight_zero_cols(W: torch.Tensor) -> torch.Tensor:
+    nb, R, C = W.shape
+    wz = torch.empty((nb, C), dtype=torch.uint8, device=_dev(W))
+    call("forge_weight_zero_cols", ptr(W), dtype_code(W), nb, R, C, ptr(wz), stream_ptr())
+    return wz
+
+
+def hessian_gather_damp(H, perm, pruned, wzero, invalid, rel_damp: float, A=None, want_hp: bool = False):
+    nb, C, _ = H.shape
+    dev = _dev(H)
+    if A is None:
+        A = torch.empty_like(H)
+    Hp = torch.empty_like(H) if want_hp else None
+    damp = torch.empty(nb, dtype=torch.float32, device=dev)
+    call("forge_hessian_gather_damp", ptr(H), nb, C, ptr(perm), ptr(pruned), ptr(wzero), ptr(invalid), float(rel_damp),
+         ptr(A), ptr(Hp), ptr(damp), stream_ptr())
+    return A, Hp, damp
+
+
+def chol_inv_upper(A: torch.Tensor, U=None, zero_lower: bool = True):
+    """A [nb,C,C] (index-reversed damped Hessian, destroyed) -> (U, udiag, info)."""
+    nb, C, _ = A.shape
+    dev = _dev(A)
+    if U is None:
+        U = torch.empty_like(A)
+    udiag = torch.empty((nb, C), dtype=torch.float32, device=dev)
+    info = torch.empty(nb, dtype=torch.int32, device=dev)
+    ws = torch.empty(query("forge_chol_workspace_bytes", nb, C), dtype=torch.uint8, device=dev)
+    call("forge_chol_inv_upper_batched", ptr(A), nb, C, ptr(U), ptr(udiag), ptr(info), int(zero_lower), ptr(ws),
+         stream_ptr())
+    return U, udiag, info
+
+
+def quant_grid(W: torch.Tensor, gs: int, bits: int, symmetric: bool, candidates=None, norm: float = 2.4):
+    """W [rows, C] (bf16/fp32) -> (scales, qzeros) fp32 [rows*G]; candidates given = MSE search fused in."""
+    rows, C = W.shape
+    G = (C + gs - 1) // gs
+    dev = _dev(W)
+    scales = torch.empty(rows * G, dtype=torch.float32, device=dev)
+    qzeros = torch.empty(rows * G, dtype=torch.float32, device=dev)
+    n_cand = 0 if candidates is None else candidates.numel()
+    call("forge_quant_grid", ptr(W), dtype_code(W), rows, C, gs, bits, int(bool(symmetric)), ptr(candidates), n_cand,
+         float(norm), ptr(scales), ptr(qzeros), stream_ptr())
+    return scales, qzeros
+
+
+def quant_grid_mse(W, gs, bits, symmetric, candidates, norm, scales, qzeros):
+    rows, C = W.shape
+    call("forge_quant_grid_mse", ptr(W), dtype_code(W), rows, C, gs, bits, int(bool(symmetric)), ptr(candidates),
+         candidates.numel(), float(norm), ptr(scales), ptr(qzeros), stream_ptr())
+    return scales, qzeros
+
+
+def gptq_solve_cr(Wt, U, scales_el, qzeros_el, bits: int, uinv=None):
+    """Reference operator layout: Wt [C,R] fp32 (mutated -> dequantised), per-element scales [C,R]."""
+    C, R = Wt.shape
+    dev = _dev(Wt)
+    q = torch.empty((C, R), dtype=torch.uint8, device=dev)
+    sparse = uinv is not None
+    M = torch.zeros(((C + 31) // 32, R), dtype=torch.int32, device=dev) if sparse else None
+    ws = torch.empty(query("forge_solve_workspace_bytes", 1, R, C), dtype=torch.uint8, device=dev)
+    call("forge_gptq_solve_cr", ptr(Wt), ptr(U), ptr(uinv), ptr(scales_el), ptr(qzeros_el), bits, R, C, int(sparse),
+         ptr(q), ptr(M), ptr(ws), stream_ptr())
+    return (q, M) if sparse else q
+
+
+def gptq_solve_batched(W, U, scales, qzeros, gs: int, bits: int, perm=None, u_map=None, udiag=None,
+                       sparse14: bool = False, ws=None):
+    """W [nb,R,C] original order; U [nu,C,C]; scales/qzeros [nb*R*G] -> qweight [nb,R,C] (+ M [nb,G32,R])."""
+    nb, R, C = W.shape
+    dev = _dev(W)
+    nu = U.shape[0]
+    q = torch.empty((nb, R, C), dtype=torch.uint8, device=dev)
+    M = torch.zeros((nb, (C + 31) // 32, R), dtype=torch.int32, device=dev) if sparse14 else None
+    if ws is None:
+        ws = torch.empty(query("forge_solve_workspace_bytes", nb, R, C), dtype=torch.uint8, device=dev)
+    call("forge_gptq_solve_batched", ptr(W), dtype_code(W), nb, R, C, ptr(U), ptr(udiag), ptr(u_map), ptr(perm), nu,
+         ptr(scales), ptr(qzeros), gs, bits, int(sparse14), ptr(q), ptr(M), ptr(ws), stream_ptr())
+    return (q, M) if sparse14 else q
+
+
+def dequantize(q, scales, qzeros, gs: int, dtype=torch.float32):
+    """(q - q0) * s in fp32 -> dtype; q [..., C] uint8, scales/qzeros flat per (row, group)."""
+    C = q.shape[-1]
+    rows = q.numel() // C
+    out = torch.empty(q.shape, dtype=dtype, device=_dev(q))
+    code = _abi.BF16 if dtype == torch.bfloat16 else _abi.F32
+    assert dtype in (torch.float32, torch.bfloat16)
+    call("forge_dequantize", ptr(q), ptr(scales), ptr(qzeros), rows, C, gs, ptr(out), code, stream_ptr())
+    return out
+
+
+def pack_int4(q, qzeros, gs: int):
+    """weight_packed int32 [..., ceil(C/8)] of the compressed-tensors pack-quantized format."""
+    C = q.shape[-1]
+    rows = q.numel() // C
+    out = torch.empty((*q.shape[:-1], (C + 7) // 8), dtype=torch.int32, device=_dev(q))
+    call("forge_pack_int4", ptr(q), ptr(qzeros), rows, C, gs, ptr(out), stream_ptr())
+    return out
+
+
+def pack_sparse14(q_rc, M, scales32):
+    """q [R,C] u8, M [G32,R], scales32 [G32,R] fp32 -> Wpair int64 bit pattern [G2,R,2]."""
+    R, C = q_rc.shape
+    G32 = (C + 31) // 32
+    out = torch.empty(((G32 + 1) // 2, R, 2), dtype=torch.int64, device=_dev(q_rc))
+    call("forge_pack_sparse14", ptr(q_rc), ptr(M), ptr(scales32), R, C, ptr(out), stream_ptr())
+    return out

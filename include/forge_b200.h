@@ -1,0 +1,191 @@
+/*
+ * forge_b200 — C ABI of the sm_100a GPTQ / SparseGPT solver engine.
+ *
+ * Every entry point
+ *   - is extern "C", takes plain device pointers, sizes and a CUDA stream
+ *     (passed as void*; 0 = the legacy default stream),
+ *   - returns FORGE_OK (0) or a FORGE_ERR_* code and never throws,
+ *   - is asynchronous on `stream` and never synchronises the device,
+ *   - allocates nothing: outputs and workspaces belong to the caller
+ *     (forge_*_workspace_bytes() give the sizes).
+ * forge_last_error() returns a per-thread description of the last failure.
+ *
+ * Citations name the reference interface each function replaces (paths inside
+ * the reference project, Pranshu-Bahadur/4Bit-Forge).
+ *
+ * Notation: R = out_features, C = in_features, gs = group size,
+ * G = ceil(C/gs), nb = matrices in the batch.
+ */
+#ifndef FORGE_B200_H
+#define FORGE_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    FORGE_OK = 0,
+    FORGE_ERR_INVALID = 1,     /* bad argument (null pointer, unsupported size) */
+    FORGE_ERR_LAUNCH = 2,      /* CUDA reported an error at launch */
+    FORGE_ERR_TIMEOUT = 3,     /* a bounded device-side wait ran out (status word) */
+    FORGE_ERR_UNSUPPORTED = 4  /* shape / option outside what the kernels cover */
+};
+
+enum { FORGE_DTYPE_F32 = 0, FORGE_DTYPE_BF16 = 1 };
+
+/* flags of forge_hessian_grouped */
+enum {
+    FORGE_HESS_MIRROR = 1,   /* also write the lower triangle (full symmetric H) */
+    FORGE_HESS_SIMT = 2      /* plain-FMA validation kernel instead of tcgen05 */
+};
+
+int forge_version(void);
+const char *forge_last_error(void);
+
+/* ---- A0: DeepSeek fp8 block de-quantisation ------------------------------
+ * out_bf16[o,i] = bf16( fp32(w_fp8_e4m3[o,i]) * scale_inv[o/so, i/si] ),
+ * si = I/nI, so = si if ceil(O/si)==nO else ceil(O/nO).
+ * Replaces forge/utils/io.py:533-563 (_apply_block_scale_inv_2d) and the fp8
+ * branch of materialize_block_weights_to_fp, forge/utils/io.py:864-874. */
+int forge_fp8_block_dequant(const void *w_fp8, const float *scale_inv, void *out_bf16,
+                            int64_t O, int64_t I, int64_t nO, int64_t nI, void *stream);
+
+/* ---- routing: top-k ids -> per-expert token lists ------------------------
+ * topk_ids [T,k] int32 (expert id per slot).  For the experts
+ * [e_begin, e_begin+e_count) writes counts[e_count], offsets[e_count+1]
+ * (exclusive prefix sum) and token_lists (token indices grouped by expert,
+ * ascending inside each expert; capacity T*k).  Stands in for the gather the
+ * HF MoE block performs before each expert's forward hook fires
+ * (quant.py:398-406; the in-repo statement is forge/utils/engine.py:228-238). */
+int forge_route_build_lists(const int32_t *topk_ids, int64_t T, int k, int e_begin, int e_count,
+                            int32_t *counts, int64_t *offsets, int32_t *token_lists, void *stream);
+
+/* ---- A2: per-expert Hessian accumulation ---------------------------------
+ * For b in [0,nb):  n = offsets[b+1]-offsets[b];  N = n_prev[b] + n;
+ *   H[b] = (n_prev[b]/N) * H[b] + (2/N) * sum_{t in list b} x_t^T x_t   (n > 0)
+ * x_t = row token_idx[offsets[b]+j] of X (bf16, row stride ldx elements), or
+ * row offsets[b]+j when token_idx is NULL.  fp32 accumulation of exact bf16
+ * products on the tcgen05 tensor cores.  n_prev may be NULL (= 0; H is then
+ * overwritten, not read).  When n == 0 H[b] is left untouched.  n_prev is NOT
+ * updated (forge_counts_add does that).  C must be a multiple of 8.
+ * `status` (device int32, may be NULL) receives FORGE_ERR_TIMEOUT if a bounded
+ * wait inside the kernel ran out.
+ * Replaces GPTQ.update, forge/gptq.py:62-80 (H.addmm_ at :76-79). */
+int forge_hessian_grouped(const void *X_bf16, int64_t ldx, int64_t C, const int32_t *token_idx,
+                          const int64_t *offsets, int nb, float *H, const int64_t *n_prev,
+                          int flags, int32_t *status, void *stream);
+
+/* n_prev[b] += offsets[b+1]-offsets[b]  (GPTQ.update's num_samples.add_, forge/gptq.py:80) */
+int forge_counts_add(int64_t *n_prev, const int64_t *offsets, int nb, void *stream);
+
+/* ---- A3: Hessian preparation ---------------------------------------------
+ * forge_hessian_scan: for each b, invalid[b] = (n_samples[b]==0) or any NaN in
+ * H[b]  (n_samples may be NULL = "has samples"); diag[b,c] = 1 if invalid or
+ * H[b,c,c]==0 else H[b,c,c]; pruned[b,c] = !invalid && H[b,c,c]==0.
+ * The caller sorts diag (descending) to get the activation order.
+ * Replaces the checks of GPTQ._prep, forge/gptq.py:96-103. */
+int forge_hessian_scan(const float *H, int nb, int64_t C, const int64_t *n_samples, float *diag,
+                       uint8_t *pruned, int32_t *invalid, void *stream);
+
+/* W[b,:,c] = 0 for every column c pruned in Hessian slot u_map[b] (u_map NULL = b); in place.
+ * Replaces `self.W[:, self.pruned_ids] = 0`, forge/gptq.py:91,115,124. */
+int forge_weight_apply_pruned(void *W, int w_dtype, int nb, int64_t R, int64_t C, const uint8_t *pruned,
+                              const int32_t *u_map, void *stream);
+
+/* wzero[b,c] = 1 iff column c of W[b] is all zero.
+ * Replaces `self.W.clone().eq(0).all(dim=0)`, forge/gptq.py:145. */
+int forge_weight_zero_cols(const void *W, int w_dtype, int nb, int64_t R, int64_t C, uint8_t *wzero,
+                           void *stream);
+
+/* forge_hessian_gather_damp: builds, per Hessian b, the matrix the factorisation consumes.
+ *   H'  = I if invalid[b] else H[b] with pruned rows/cols zeroed and their diagonal set to 1
+ *   Hp[i,j] = H'[perm[i], perm[j]]                       (perm NULL = identity)
+ *   if wzero[b,i] or wzero[b,j]: Hp[i,j] = (i==j)        (indexed by POSITION i, as the reference does)
+ *   damp = rel_damp * mean(diag Hp);  Hp[i,i] += damp
+ *   A[b, C-1-i, C-1-j] = Hp[i,j]                         (index-reversed copy)
+ * Hp_out (optional, [nb,C,C]) receives Hp itself; damp_out [nb] (required) receives damp.
+ * A must not alias H.
+ * Replaces the gather of GPTQ._prep (forge/gptq.py:117) and the damping of
+ * GPTQ._h_factor (forge/gptq.py:145-154). */
+int forge_hessian_gather_damp(const float *H, int nb, int64_t C, const int32_t *perm,
+                              const uint8_t *pruned, const uint8_t *wzero, const int32_t *invalid,
+                              float rel_damp, float *A, float *Hp_out, float *damp_out, void *stream);
+
+/* ---- A4: batched Cholesky -> unit-diagonal upper factor of the inverse ---
+ * A [nb,C,C] is the index-reversed damped Hessian from forge_hessian_gather_damp and is destroyed.
+ * On return U[b] (fp32 [C,C]) is upper triangular with unit diagonal, U = diag(T)^-1 T where
+ * T^T T = Hp^-1 (T upper, the reference's cholesky(cholesky_inverse(cholesky(Hp))), upper=True),
+ * udiag[b,c] = T[c,c], and info[b] = 0, or > 0 when a pivot was not positive: then U[b] = I and
+ * udiag = 1 (the reference's issue_non_invertible fallback).  With zero_lower != 0 the strict lower
+ * triangle of U is zero-filled, otherwise it holds scratch values.
+ * ws: forge_chol_workspace_bytes(nb, C) bytes.
+ * Replaces GPTQ._h_factor, forge/gptq.py:156-177. */
+int64_t forge_chol_workspace_bytes(int nb, int64_t C);
+int forge_chol_inv_upper_batched(float *A, int nb, int64_t C, float *U, float *udiag, int32_t *info,
+                                 int zero_lower, void *ws, void *stream);
+
+/* ---- A5/A6: per-group scale / zero grid -----------------------------------
+ * W [nb*R, C] (bf16 or fp32, row-major, groups of gs consecutive columns, the last one zero padded).
+ * scales,qzeros [nb*R*G] fp32.  symmetric: s = 2/maxq*max|w| + 1e-12, q0 = (maxq+1)/2;  else
+ * s = (max-min)/maxq + 1e-12, q0 = clamp(rint(-min/s)).  With n_cand > 0 the L^norm error of every
+ * shrink factor candidates[p] is evaluated and the first best (s, q0) is kept.  gs in {32,64,128}.
+ * Replaces kernels.build_group_meta_packed (forge/backend/cuda/quant_grid.cu:42-99,186-224) and
+ * kernels.mse_scale_groups_packed (quant_grid.cu:101-183,227-287), called from forge/gptq.py:181-227. */
+int forge_quant_grid(const void *W, int w_dtype, int64_t rows, int64_t C, int gs, int bits, int symmetric,
+                     const float *candidates, int n_cand, float norm, float *scales, float *qzeros,
+                     void *stream);
+/* MSE refinement only, on scales/qzeros computed earlier (in place). */
+int forge_quant_grid_mse(const void *W, int w_dtype, int64_t rows, int64_t C, int gs, int bits,
+                         int symmetric, const float *candidates, int n_cand, float norm,
+                         float *scales, float *qzeros, void *stream);
+
+/* ---- A7-A9: fused column solver -------------------------------------------
+ * forge_gptq_solve_cr is the reference's operator: Wt [C,R] fp32 (columns already permuted), U [C,C]
+ * unit-diagonal upper, scales/qzeros per ELEMENT [C,R]; writes codes q [C,R] uint8, overwrites Wt with
+ * the de-quantised weights; sparse14 != 0 selects the SparseGPT 1:4 variant (uinv [C] = 1/diag of the
+ * un-normalised factor; M [ceil(C/32),R] uint32 keep-mask).  ws: forge_solve_workspace_bytes(1,R,C).
+ * Replaces kernels.gptq_solver (forge/backend/cuda/solver.cu:99-154) and kernels.sparsegptq14_solver
+ * (forge/backend/cuda/solver_sparsegptq14.cu:142-200). */
+int64_t forge_solve_workspace_bytes(int nb, int64_t R, int64_t C);
+int forge_gptq_solve_cr(float *Wt, const float *U, const float *uinv, const float *scales,
+                        const float *qzeros, int bits, int64_t R, int64_t C, int sparse14,
+                        uint8_t *q, uint32_t *M, void *ws, void *stream);
+
+/* forge_gptq_solve_batched is the batched fast path: nb weights W[b] [R,C] (bf16 or fp32) in ORIGINAL
+ * column order, solved against U[u_map[b]] (u_map NULL = b) with per-GROUP scales/qzeros [nb,R,G]
+ * (group of a column = original index / gs, as forge/gptq.py:251-252 expands them), perm [nu,C] per
+ * Hessian slot (NULL = identity; nu = number of slots), udiag [nu,C] from the factorisation (sparse14).  Outputs codes qweight [nb,R,C] uint8 in ORIGINAL
+ * column order (forge/gptq.py:139) and, for sparse14, M [nb, ceil(C/32), R] in PERMUTED order like the
+ * reference.  ws: forge_solve_workspace_bytes(nb,R,C).  Replaces the glue of GPTQ.quantize/_solver,
+ * forge/gptq.py:129-139,231-276, together with the two solvers above. */
+int forge_gptq_solve_batched(const void *W, int w_dtype, int nb, int64_t R, int64_t C, const float *U,
+                             const float *udiag, const int32_t *u_map, const int32_t *perm, int nu,
+                             const float *scales, const float *qzeros, int gs, int bits, int sparse14,
+                             uint8_t *qweight, uint32_t *M, void *ws, void *stream);
+
+/* ---- A12: de-quantise codes ------------------------------------------------
+ * out[r,c] = dtype( (q[r,c] - qzeros[r,c/gs]) * scales[r,c/gs] )   (fp32 arithmetic)
+ * Replaces dequantize_forge_full, forge/utils/engine.py:72-97. */
+int forge_dequantize(const uint8_t *q, const float *scales, const float *qzeros, int64_t rows, int64_t C,
+                     int gs, void *out, int out_dtype, void *stream);
+
+/* ---- A11: dense int4 "pack-quantized" layout -------------------------------
+ * packed[r, j] = sum_{i<8} uint8(int8(q[r,8j+i]) - int8(zero[r,(8j+i)/gs]) + 8) << 4i   (int32 wrap;
+ * columns past C contribute 0) — bit-exact with compressed_tensors.pack_to_int32 as called by
+ * pack_weight, pack_quantized.py:279-313.  packed is [rows, ceil(C/8)] int32. */
+int forge_pack_int4(const uint8_t *q, const float *qzeros, int64_t rows, int64_t C, int gs,
+                    int32_t *packed, void *stream);
+
+/* ---- A10: sparse 1:4 + int4 "Wpair" layout ----------------------------------
+ * q [R,C] uint8 (original layout), M [G32,R] uint32, scales32 [G32,R] fp32 (one scale per 32 columns)
+ * -> out [G2=ceil(G32/2), R, 2] uint64:  bf16(scale)<<48 | idx16<<32 | eight 4-bit codes.
+ * Replaces kernels.pack_sparsegptq14_to_u64x2, forge/backend/cuda/bitpacking_sparsegptq14.cu:58-175. */
+int forge_pack_sparse14(const uint8_t *q, const uint32_t *M, const float *scales32, int64_t R, int64_t C,
+                        uint64_t *out, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FORGE_B200_H */
