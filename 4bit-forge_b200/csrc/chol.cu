@@ -350,23 +350,23 @@ extern "C" int forge_chol_inv_upper_batched(float *A, int nb, int64_t C, float *
     const int nblk = (int)cdiv(C, NB);
     float *dinv = (float *)ws;
     const int vec = (C % 4 == 0) && ((uintptr_t)A % 16 == 0) && ((uintptr_t)U % 16 == 0);
-    info_clear_kernel<<<(nb + 127) / 128, 128, 0, st>>>(info, nb);
+    info_clear_kernel<<<(nb + 127) / 128, 128, 0, st>>>(info, nb); FORGE_NOTE_LAUNCH();
     for (int k = 0; k < nblk; ++k) {
-        chol_diag_kernel<<<nb, 256, 0, st>>>(A, C, k, nblk, dinv, U, udiag, info);
+        chol_diag_kernel<<<nb, 256, 0, st>>>(A, C, k, nblk, dinv, U, udiag, info); FORGE_NOTE_LAUNCH();
         const int64_t m = C - (int64_t)(k + 1) * NB;
         if (m > 0) {
             const unsigned nt = (unsigned)cdiv(m, TM);
-            chol_panel_kernel<<<dim3(nt, nb), 256, 0, st>>>(A, C, k, nblk, dinv, vec);
-            chol_syrk_kernel<<<dim3(nt, nt, nb), 256, 0, st>>>(A, C, k, vec);
+            chol_panel_kernel<<<dim3(nt, nb), 256, 0, st>>>(A, C, k, nblk, dinv, vec); FORGE_NOTE_LAUNCH();
+            chol_syrk_kernel<<<dim3(nt, nt, nb), 256, 0, st>>>(A, C, k, vec); FORGE_NOTE_LAUNCH();
         }
     }
     for (int j = nblk - 2; j >= 0; --j) {
         const int64_t m = C - (int64_t)(j + 1) * NB;
         const unsigned nt = (unsigned)cdiv(m, TM);
-        trtri_step_kernel<<<dim3(nt, nb), 256, 0, st>>>(A, U, C, j, nblk, dinv, vec);
+        trtri_step_kernel<<<dim3(nt, nb), 256, 0, st>>>(A, U, C, j, nblk, dinv, vec); FORGE_NOTE_LAUNCH();
     }
     dim3 g2((unsigned)cdiv(C, 32), (unsigned)cdiv(C, 8), nb);
-    rotate_upper_kernel<<<g2, dim3(32, 8), 0, st>>>(U, C, info, udiag);
-    if (zero_lower) zero_lower_kernel<<<g2, dim3(32, 8), 0, st>>>(U, C);
+    rotate_upper_kernel<<<g2, dim3(32, 8), 0, st>>>(U, C, info, udiag); FORGE_NOTE_LAUNCH();
+    if (zero_lower) { zero_lower_kernel<<<g2, dim3(32, 8), 0, st>>>(U, C); FORGE_NOTE_LAUNCH(); }
     return check_launch("forge_chol_inv_upper_batched");
 }

@@ -10,6 +10,8 @@
 namespace forge {
 
 void set_error(const char *fmt, ...);
+void note_launch();
+#define FORGE_NOTE_LAUNCH() ::forge::note_launch()
 
 inline int check_launch(const char *what) {
     cudaError_t e = cudaGetLastError();

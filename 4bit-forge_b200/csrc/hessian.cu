@@ -384,7 +384,7 @@ extern "C" int forge_hessian_grouped(const void *X_bf16, int64_t ldx, int64_t C,
     P.ntri = P.nt * (P.nt + 1) / 2;
     if (flags & FORGE_HESS_SIMT) {
         dim3 grid((unsigned)cdiv(C, 16), (unsigned)cdiv(C, 16), nb);
-        hessian_simt_kernel<<<grid, dim3(16, 16), 0, st>>>(P);
+        hessian_simt_kernel<<<grid, dim3(16, 16), 0, st>>>(P); FORGE_NOTE_LAUNCH();
         return check_launch("forge_hessian_grouped(simt)");
     }
     FORGE_REQUIRE(C % 8 == 0 && ldx % 8 == 0, "C and ldx must be multiples of 8 (16-byte row chunks)");
@@ -404,6 +404,6 @@ extern "C" int forge_hessian_grouped(const void *X_bf16, int64_t ldx, int64_t C,
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int64_t total = (int64_t)nb * P.ntri;
     const int grid = (int)imin64(total, sms);
-    hessian_tc_kernel<<<grid, kThreads, kSmemBytes, st>>>(P);
+    hessian_tc_kernel<<<grid, kThreads, kSmemBytes, st>>>(P); FORGE_NOTE_LAUNCH();
     return check_launch("forge_hessian_grouped");
 }

@@ -12,8 +12,12 @@ void set_error(const char *fmt, ...) {
     vsnprintf(g_err, sizeof(g_err), fmt, ap);
     va_end(ap);
 }
+static long long g_launches = 0;
+void note_launch() { __atomic_fetch_add(&g_launches, 1, __ATOMIC_RELAXED); }
 }  // namespace forge
 using namespace forge;
+
+extern "C" long long forge_launch_count(void) { return __atomic_load_n(&forge::g_launches, __ATOMIC_RELAXED); }
 
 extern "C" int forge_version(void) { return 100; }
 extern "C" const char *forge_last_error(void) { return g_err; }
@@ -74,12 +78,9 @@ extern "C" int forge_fp8_block_dequant(const void *w_fp8, const float *scale_inv
     const int64_t work = vec ? O * (I / 16) : O * I;
     const int threads = 256;
     const int blocks = (int)imin64(cdiv(work, threads), 148 * 16);
-    if (vec)
-        fp8_dequant_vec16<<<blocks, threads, 0, st>>>((const uint8_t *)w_fp8, scale_inv,
-                                                      (__nv_bfloat16 *)out_bf16, O, I, nI, so, si);
-    else
-        fp8_dequant_scalar<<<blocks, threads, 0, st>>>((const uint8_t *)w_fp8, scale_inv,
-                                                       (__nv_bfloat16 *)out_bf16, O, I, nI, so, si);
+    if (vec) { fp8_dequant_vec16<<<blocks, threads, 0, st>>>((const uint8_t *)w_fp8, scale_inv,
+                                                      (__nv_bfloat16 *)out_bf16, O, I, nI, so, si); FORGE_NOTE_LAUNCH(); } else { fp8_dequant_scalar<<<blocks, threads, 0, st>>>((const uint8_t *)w_fp8, scale_inv,
+                                                       (__nv_bfloat16 *)out_bf16, O, I, nI, so, si); FORGE_NOTE_LAUNCH(); }
     return check_launch("forge_fp8_block_dequant");
 }
 
@@ -141,9 +142,9 @@ extern "C" int forge_route_build_lists(const int32_t *topk_ids, int64_t T, int k
     FORGE_REQUIRE(topk_ids && counts && offsets && token_lists, "null pointer");
     FORGE_REQUIRE(T >= 0 && k > 0 && e_count > 0 && e_begin >= 0, "bad sizes");
     cudaStream_t st = (cudaStream_t)stream;
-    route_scan_kernel<false><<<e_count, 512, 0, st>>>(topk_ids, T, k, e_begin, counts, nullptr, nullptr);
-    route_offsets_kernel<<<1, 32, 0, st>>>(counts, e_count, offsets);
-    route_scan_kernel<true><<<e_count, 512, 0, st>>>(topk_ids, T, k, e_begin, counts, offsets, token_lists);
+    route_scan_kernel<false><<<e_count, 512, 0, st>>>(topk_ids, T, k, e_begin, counts, nullptr, nullptr); FORGE_NOTE_LAUNCH();
+    route_offsets_kernel<<<1, 32, 0, st>>>(counts, e_count, offsets); FORGE_NOTE_LAUNCH();
+    route_scan_kernel<true><<<e_count, 512, 0, st>>>(topk_ids, T, k, e_begin, counts, offsets, token_lists); FORGE_NOTE_LAUNCH();
     return check_launch("forge_route_build_lists");
 }
 
@@ -153,7 +154,7 @@ __global__ void counts_add_kernel(int64_t *n_prev, const int64_t *offsets, int n
 }
 extern "C" int forge_counts_add(int64_t *n_prev, const int64_t *offsets, int nb, void *stream) {
     FORGE_REQUIRE(n_prev && offsets && nb > 0, "bad arguments");
-    counts_add_kernel<<<(nb + 127) / 128, 128, 0, (cudaStream_t)stream>>>(n_prev, offsets, nb);
+    counts_add_kernel<<<(nb + 127) / 128, 128, 0, (cudaStream_t)stream>>>(n_prev, offsets, nb); FORGE_NOTE_LAUNCH();
     return check_launch("forge_counts_add");
 }
 
@@ -203,11 +204,11 @@ extern "C" int forge_hessian_scan(const float *H, int nb, int64_t C, const int64
     FORGE_REQUIRE(H && diag && pruned && invalid, "null pointer");
     FORGE_REQUIRE(nb > 0 && C > 0, "empty batch");
     cudaStream_t st = (cudaStream_t)stream;
-    scan_init_kernel<<<(nb + 127) / 128, 128, 0, st>>>(n_samples, invalid, nb);
+    scan_init_kernel<<<(nb + 127) / 128, 128, 0, st>>>(n_samples, invalid, nb); FORGE_NOTE_LAUNCH();
     const int64_t elems = C * C;
     const int bx = (int)imin64(cdiv(elems / 4 + 1, 256), 64);
-    scan_nan_kernel<<<dim3(bx, nb), 256, 0, st>>>(H, elems, invalid);
-    scan_diag_kernel<<<dim3((unsigned)cdiv(C, 256), nb), 256, 0, st>>>(H, C, invalid, diag, pruned);
+    scan_nan_kernel<<<dim3(bx, nb), 256, 0, st>>>(H, elems, invalid); FORGE_NOTE_LAUNCH();
+    scan_diag_kernel<<<dim3((unsigned)cdiv(C, 256), nb), 256, 0, st>>>(H, C, invalid, diag, pruned); FORGE_NOTE_LAUNCH();
     return check_launch("forge_hessian_scan");
 }
 
@@ -228,7 +229,7 @@ extern "C" int forge_weight_apply_pruned(void *W, int w_dtype, int nb, int64_t R
                                          const uint8_t *pruned, const int32_t *u_map, void *stream) {
     FORGE_REQUIRE(W && pruned && nb > 0 && R > 0 && C > 0, "bad arguments");
     dim3 grid((unsigned)cdiv(C, 128), (unsigned)imin64(R, 64), nb);
-    apply_pruned_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(W, w_dtype, R, C, pruned, u_map);
+    apply_pruned_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(W, w_dtype, R, C, pruned, u_map); FORGE_NOTE_LAUNCH();
     return check_launch("forge_weight_apply_pruned");
 }
 
@@ -248,7 +249,7 @@ __global__ void zero_cols_kernel(const void *__restrict__ W, int dtype, int64_t 
 extern "C" int forge_weight_zero_cols(const void *W, int w_dtype, int nb, int64_t R, int64_t C, uint8_t *wzero,
                                       void *stream) {
     FORGE_REQUIRE(W && wzero && nb > 0 && R > 0 && C > 0, "bad arguments");
-    zero_cols_kernel<<<dim3((unsigned)cdiv(C, 128), nb), 128, 0, (cudaStream_t)stream>>>(W, w_dtype, R, C, wzero);
+    zero_cols_kernel<<<dim3((unsigned)cdiv(C, 128), nb), 128, 0, (cudaStream_t)stream>>>(W, w_dtype, R, C, wzero); FORGE_NOTE_LAUNCH();
     return check_launch("forge_weight_zero_cols");
 }
 
@@ -332,7 +333,7 @@ extern "C" int forge_hessian_gather_damp(const float *H, int nb, int64_t C, cons
     FORGE_REQUIRE(C * 4 <= 200 * 1024, "C too large for the row staging buffer");
     FORGE_REQUIRE(A != H, "A must not alias H");
     cudaStream_t st = (cudaStream_t)stream;
-    damp_kernel<<<nb, 256, 0, st>>>(H, C, perm, pruned, wzero, invalid, rel_damp, damp_out);
+    damp_kernel<<<nb, 256, 0, st>>>(H, C, perm, pruned, wzero, invalid, rel_damp, damp_out); FORGE_NOTE_LAUNCH();
     const size_t smem = (size_t)C * 4;
     static bool attr_done = false;
     if (!attr_done) {
@@ -340,7 +341,7 @@ extern "C" int forge_hessian_gather_damp(const float *H, int nb, int64_t C, cons
         attr_done = true;
     }
     gather_damp_kernel<<<dim3((unsigned)C, nb), 256, smem, st>>>(H, C, perm, pruned, wzero, invalid, damp_out, A,
-                                                                Hp_out);
+                                                                Hp_out); FORGE_NOTE_LAUNCH();
     return check_launch("forge_hessian_gather_damp");
 }
 
@@ -366,7 +367,7 @@ extern "C" int forge_dequantize(const uint8_t *q, const float *scales, const flo
     FORGE_REQUIRE(rows > 0 && C > 0 && gs > 0, "bad sizes");
     const int64_t G = cdiv(C, gs);
     const int blocks = (int)imin64(cdiv(rows * C, 256), 148 * 32);
-    dequant_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(q, scales, qzeros, rows, C, gs, G, out, out_dtype);
+    dequant_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(q, scales, qzeros, rows, C, gs, G, out, out_dtype); FORGE_NOTE_LAUNCH();
     return check_launch("forge_dequantize");
 }
 
@@ -409,7 +410,7 @@ extern "C" int forge_pack_int4(const uint8_t *q, const float *qzeros, int64_t ro
     const int64_t G = cdiv(C, gs), CP = cdiv(C, 8);
     const int aligned8 = (C % 8 == 0) && ((uintptr_t)q % 8 == 0);
     const int blocks = (int)imin64(cdiv(rows * CP, 256), 148 * 32);
-    pack_int4_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(q, qzeros, rows, C, gs, G, CP, packed, aligned8);
+    pack_int4_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(q, qzeros, rows, C, gs, G, CP, packed, aligned8); FORGE_NOTE_LAUNCH();
     return check_launch("forge_pack_int4");
 }
 
@@ -485,6 +486,6 @@ extern "C" int forge_pack_sparse14(const uint8_t *q, const uint32_t *M, const fl
     const int vec_ok = (C % 16 == 0) && ((uintptr_t)q % 16 == 0);
     const int blocks = (int)imin64(cdiv(G2 * R, 256), 148 * 32);
     pack_sparse14_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(q, M, scales32, R, C, G32, G2,
-                                                                 (ulonglong2 *)out, vec_ok);
+                                                                 (ulonglong2 *)out, vec_ok); FORGE_NOTE_LAUNCH();
     return check_launch("forge_pack_sparse14");
 }

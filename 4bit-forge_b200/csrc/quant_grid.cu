@@ -146,10 +146,9 @@ int launch_grid(const void *W, int w_dtype, int64_t rows, int64_t C, int gs, int
     const bool bf = (w_dtype == FORGE_DTYPE_BF16);
 #define FORGE_LAUNCH_GRID(GSV)                                                                               \
     do {                                                                                                     \
-        if (bf) quant_grid_kernel<GSV, true, ABSMAX><<<blocks, threads, 0, st>>>(                            \
-                    W, rows, C, G, gs, bits, symmetric, cand, n_cand, norm, scales, qzeros);                 \
-        else quant_grid_kernel<GSV, false, ABSMAX><<<blocks, threads, 0, st>>>(                              \
-                    W, rows, C, G, gs, bits, symmetric, cand, n_cand, norm, scales, qzeros);                 \
+        if (bf) { quant_grid_kernel<GSV, true, ABSMAX><<<blocks, threads, 0, st>>>(                            \
+                    W, rows, C, G, gs, bits, symmetric, cand, n_cand, norm, scales, qzeros); FORGE_NOTE_LAUNCH(); } else { quant_grid_kernel<GSV, false, ABSMAX><<<blocks, threads, 0, st>>>(                              \
+                    W, rows, C, G, gs, bits, symmetric, cand, n_cand, norm, scales, qzeros); FORGE_NOTE_LAUNCH(); }                 \
     } while (0)
     switch (gs) {
         case 32: FORGE_LAUNCH_GRID(32); break;

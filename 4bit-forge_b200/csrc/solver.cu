@@ -343,7 +343,7 @@ int launch_solve(const SolveParams &p, int nb, cudaStream_t st) {
         attr_done = true;
     }
     dim3 grid((unsigned)cdiv(p.R, kBlk), (unsigned)nb);
-    solve_kernel<MODE, SPARSE><<<grid, kBlk, kSolveSmem, st>>>(p);
+    solve_kernel<MODE, SPARSE><<<grid, kBlk, kSolveSmem, st>>>(p); FORGE_NOTE_LAUNCH();
     return check_launch("forge_gptq_solve");
 }
 
@@ -389,16 +389,16 @@ extern "C" int forge_gptq_solve_batched(const void *W, int w_dtype, int nb, int6
     if (perm) {
         FORGE_REQUIRE(nu > 0 && nu <= nb, "nu must be in [1, nb]");
         perm_inv = (int32_t *)wsp;
-        perm_inverse_kernel<<<dim3((unsigned)cdiv(C, 256), nu), 256, 0, st>>>(perm, C, perm_inv);
+        perm_inverse_kernel<<<dim3((unsigned)cdiv(C, 256), nu), 256, 0, st>>>(perm, C, perm_inv); FORGE_NOTE_LAUNCH();
     }
     dim3 tgrid((unsigned)cdiv(C, 32), (unsigned)cdiv(R, 32), nb);
-    transpose_gather_kernel<<<tgrid, dim3(32, 8), 0, st>>>(W, w_dtype, R, C, perm_inv, u_map, Wt);
+    transpose_gather_kernel<<<tgrid, dim3(32, 8), 0, st>>>(W, w_dtype, R, C, perm_inv, u_map, Wt); FORGE_NOTE_LAUNCH();
     SolveParams p{};
     p.Wt = Wt; p.E = Wt; p.U = U; p.uvec = udiag; p.u_map = u_map;
     p.scales = scales; p.qzeros = qzeros; p.perm = perm; p.q = qt; p.M = M;
     p.R = R; p.C = C; p.G = cdiv(C, gs); p.gs = gs; p.maxq = (1 << bits) - 1; p.write_deq = 0; p.uvec_is_diag = 1;
     int rc = sparse14 ? launch_solve<0, true>(p, nb, st) : launch_solve<0, false>(p, nb, st);
     if (rc != FORGE_OK) return rc;
-    untranspose_codes_kernel<<<tgrid, dim3(32, 8), 0, st>>>(qt, R, C, perm_inv, u_map, qweight);
+    untranspose_codes_kernel<<<tgrid, dim3(32, 8), 0, st>>>(qt, R, C, perm_inv, u_map, qweight); FORGE_NOTE_LAUNCH();
     return check_launch("forge_gptq_solve_batched");
 }

@@ -27,6 +27,7 @@ _ptr = ctypes.c_void_p
 _PROTOS = {
     "forge_version": (_c_int, []),
     "forge_last_error": (ctypes.c_char_p, []),
+    "forge_launch_count": (ctypes.c_longlong, []),
     "forge_fp8_block_dequant": (_c_int, [_ptr, _ptr, _ptr, _c_i64, _c_i64, _c_i64, _c_i64, _ptr]),
     "forge_route_build_lists": (_c_int, [_ptr, _c_i64, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr]),
     "forge_hessian_grouped": (_c_int, [_ptr, _c_i64, _c_i64, _ptr, _ptr, _c_int, _ptr, _ptr, _c_int, _ptr, _ptr]),
@@ -80,7 +81,9 @@ def _require_cuda():
 def ptr(t):
     if t is None:
         return None
-    assert t.is_cuda and t.is_contiguous(), "forge_b200 expects contiguous CUDA tensors"
+    _require_cuda()
+    if not (t.is_cuda and t.is_contiguous()):
+        raise RuntimeError("forge_b200 expects contiguous CUDA tensors (there is no CPU path)")
     return t.data_ptr()
 
 

@@ -1,0 +1,445 @@
+"""Benchmark: experts GPTQ'd per second for one MoE layer.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config NAME] [--impl ours|reference]
+
+A step is one full pass of the solver path over one synthetic MoE layer: (broadcast) -> routing lists ->
+per-expert Hessians of the layer input and of the down-projection input (incl. the expert forward that
+produces it) -> scan / permutation / damping -> batched Cholesky -> scale grid -> fused column solver ->
+packing -> (gather).  Experts are sharded over the ranks; the layer is fixed, so scaling is strong.
+Rank 0 prints one JSON line.  `--impl reference` times the CPU restatement of the reference path
+(oracle/) on the host cores over a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (os.path.join(ROOT, "4bit-forge_b200"), os.path.join(ROOT, "oracle")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import torch  # noqa: E402
+
+METRIC = "experts_gptq_per_sec_per_moe_layer"
+UNIT = "experts/s"
+
+# quantisation recipe per benchmark configuration
+RECIPES = {
+    "qwen3_30b_a3b": dict(symmetric=False, quantization_scale="mse", quantization_order="default", algorithm="gptq"),
+    "deepseek_v3": dict(symmetric=True, quantization_scale="absmax", quantization_order="activation", algorithm="gptq"),
+    "minimax_m2": dict(symmetric=True, quantization_scale="absmax", quantization_order="default", algorithm="sparsegptq"),
+    "kimi_k2": dict(symmetric=True, quantization_scale="absmax", quantization_order="default", algorithm="gptq"),
+}
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--config", default="qwen3_30b_a3b", choices=sorted(RECIPES))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=0, help="override the calibration token count (smaller runs)")
+    ap.add_argument("--experts", type=int, default=0, help="override the routed expert count (smaller runs)")
+    ap.add_argument("--expert-chunk", type=int, default=0)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def layer_shape(args):
+    from forge import synth
+    import dataclasses
+    shape = synth.CONFIGS[args.config]
+    if args.tokens:
+        shape = dataclasses.replace(shape, tokens=args.tokens)
+    if args.experts:
+        shape = dataclasses.replace(shape, n_experts=args.experts)
+    return shape
+
+
+def workload_name(shape, recipe):
+    return (f"{shape.name}: {shape.n_experts}+{shape.n_shared} experts, hidden {shape.hidden}, inter {shape.inter}, "
+            f"{shape.tokens} tokens top-{shape.top_k}, W4 g128 "
+            f"{'sym' if recipe['symmetric'] else 'asym'} {recipe['quantization_scale']} {recipe['algorithm']}"
+            f"{' act-order' if recipe['quantization_order'] == 'activation' else ''}")
+
+
+# ------------------------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.idx)], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        self.t.join(timeout=2)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------------ CPU arm
+def cpu_sample(shape, recipe, n_tokens_list, seed=0):
+    """Oracle (reference restatement) on the host cores for the listed per-expert token counts; full matrix
+    shapes, gate/up share one Hessian (the reference's --owner_gptq_handles mode) but are factorised per
+    handle as the reference does.  Returns seconds."""
+    import ref_port as O
+    from forge import synth
+    torch.set_num_threads(os.cpu_count() or 1)
+    kw = dict(bits=4, group_size=128, rel_damp=0.01, **recipe)
+    t_total = 0.0
+    for i, n in enumerate(n_tokens_list):
+        Wg, Wu, Wd = synth.expert_weights(shape, [i], seed=seed + 1)
+        x = synth.student_t_activations(max(n, 1), shape.hidden, seed=seed + 2 + i)[:n]
+        t0 = time.perf_counter()
+        hg = O.OracleGPTQ(Wg[0], **kw)
+        hg.update(x)
+        hu = O.OracleGPTQ(Wu[0], **kw)
+        hu.H, hu.num_samples = hg.H.clone() if hg.H is not None else None, hg.num_samples
+        act = O.swiglu_down_input(x, Wg[0], Wu[0])
+        hd = O.OracleGPTQ(Wd[0], **kw)
+        hd.update(act)
+        for h in (hg, hu, hd):
+            out = h.quantize()
+            if recipe["algorithm"] == "sparsegptq":
+                G32 = h.W.shape[1] // 32
+                O.pack_sparsegptq14_to_u64x2(out[0], out[3], out[1].view(-1, h.G).repeat_interleave(4, 1)[:, :G32].T.contiguous())
+            else:
+                O.pack_int4(out[0], out[2].view(-1, h.G), 128)
+        t_total += time.perf_counter() - t0
+    return t_total
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    shape = layer_shape(args)
+    recipe = RECIPES[args.config]
+    mean_tokens = max(1, shape.tokens * shape.top_k // shape.n_experts)
+    import ref_port as O
+    O.lib()
+    for _ in range(args.warmup):
+        cpu_sample(shape, recipe, [mean_tokens])
+    t = 0.0
+    for _ in range(args.steps):
+        t += cpu_sample(shape, recipe, [mean_tokens])
+    value = args.steps / t
+    cores = os.cpu_count() or 1
+    sample = f"per step: 1 expert (3 matrices, full shape) with the mean routed token count {mean_tokens}; extrapolated to experts/s"
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": 1e3 * t / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": workload_name(shape, recipe), "inputs": "larger than L2 / CPU resident"},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------ GPU arm
+class PhaseTimer:
+    """Wraps forge._abi.call with CUDA events to attribute device time to each C-ABI entry point."""
+
+    def __init__(self):
+        self.records = []
+        self.enabled = False
+
+    def install(self):
+        from forge import _abi, ops
+        orig = _abi.call
+        timer = self
+
+        def timed_call(name, *a):
+            if not timer.enabled:
+                return orig(name, *a)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            rc = orig(name, *a)
+            e1.record()
+            timer.records.append((name, e0, e1))
+            return rc
+        _abi.call = timed_call
+        ops.call = timed_call
+
+    def summary(self):
+        torch.cuda.synchronize()
+        out = {}
+        for name, e0, e1 in self.records:
+            out[name] = out.get(name, 0.0) + e0.elapsed_time(e1)
+        return out
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch.distributed as dist
+    from forge import _abi, synth, moe, ops, dist as fdist
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    _abi.load_library()
+    shape = layer_shape(args)
+    recipe = RECIPES[args.config]
+    cfg = moe.MoEQuantConfig(bits=4, group_size=128, rel_damp=0.01, expert_chunk=args.expert_chunk, **recipe)
+    qz = moe.MoELayerQuantizer(cfg)
+    E = shape.n_experts
+    e0, e1 = fdist.shard_experts(E, world, rank)
+
+    # ---- inputs resident in HBM: X and routing on rank 0, each rank's own expert weights
+    T, Hd, I = shape.tokens, shape.hidden, shape.inter
+    if rank == 0:
+        X = synth.student_t_activations(T, Hd, seed=11, device=dev)
+        ids = synth.route(shape, T, seed=11, device=dev)
+    else:
+        X = torch.empty((T, Hd), dtype=torch.bfloat16, device=dev)
+        ids = torch.empty((T, shape.top_k), dtype=torch.int32, device=dev)
+    if world > 1:
+        dist.broadcast(ids, src=0)  # only to place the shared expert; the timed step broadcasts again
+    owner = fdist.shared_expert_owner(ids.cpu(), E, world) if shape.n_shared else -1
+    n_tail = shape.n_shared if rank == owner else 0
+    my_ids = list(range(e0, e1)) + [E + j for j in range(n_tail)]
+    Wg, Wu, Wd = synth.expert_weights(shape, my_ids, seed=12, device=dev)
+    fp8 = None
+    if shape.fp8_weights:
+        fp8 = [[synth.fp8_block_encode(w) for w in Wm] for Wm in (Wg, Wu, Wd)]
+
+    def shapes_of_rank(r):
+        b, e = fdist.shard_experts(E, world, r)
+        n = (e - b) + (shape.n_shared if r == owner else 0)
+        meta = {}
+        for nm, (R, C) in (("gate", (I, Hd)), ("up", (I, Hd)), ("down", (Hd, I))):
+            if cfg.algorithm == "sparsegptq":
+                meta[f"{nm}.wpair"] = ((n, (C // 32 + 1) // 2, R, 2), torch.int64)
+            else:
+                meta[f"{nm}.weight_packed"] = ((n, R, C // 8), torch.int32)
+                meta[f"{nm}.weight_scale"] = ((n, R, C // 128), torch.float16)
+                if not cfg.symmetric:
+                    meta[f"{nm}.weight_zero_point"] = ((n, R, C // 128), torch.uint8)
+        return meta
+
+    def step(Xs, idss, Wgs, Wus, Wds):
+        if world > 1:
+            fdist.broadcast_inputs(Xs, idss, src=0)
+        if fp8 is not None:
+            for Wm, enc in zip((Wgs, Wus, Wds), fp8):
+                for i, (q8, sinv) in enumerate(enc):
+                    Wm[i].copy_(ops.fp8_block_dequant(q8, sinv))
+        out = qz.quantize_experts(Xs, idss, Wgs, Wus, Wds, e_begin=e0, dense_tail=n_tail)
+        local = {}
+        for nm in ("gate", "up", "down"):
+            r = out[nm]
+            if cfg.algorithm == "sparsegptq":
+                local[f"{nm}.wpair"] = r["wpair"]
+            else:
+                local[f"{nm}.weight_packed"] = r["weight_packed"]
+                local[f"{nm}.weight_scale"] = r["weight_scale"]
+                if not cfg.symmetric:
+                    local[f"{nm}.weight_zero_point"] = r["qzeros"].to(torch.uint8)
+        gathered = fdist.gather_to_rank0(local, shapes_of_rank) if world > 1 else {k: [v] for k, v in local.items()}
+        return out, gathered
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    def max_over_ranks(ms):
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        return ms
+
+    def timed(fn, steps):
+        barrier()
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(steps):
+            fn()
+        ev1.record()
+        torch.cuda.synchronize()
+        barrier()
+        return max_over_ranks(ev0.elapsed_time(ev1))
+
+    # ---- device-resident timing
+    for _ in range(args.warmup):
+        out, _ = step(X, ids, Wg, Wu, Wd)
+    torch.cuda.synchronize()
+    status = int(out["status"].item())
+    if status != 0:
+        raise RuntimeError(f"forge_hessian_grouped reported status {status}")
+    clocks = ClockSampler(local_rank)
+    if rank == 0:
+        clocks.start()
+    n0 = _abi.query("forge_launch_count")
+    ms = timed(lambda: step(X, ids, Wg, Wu, Wd), args.steps)
+    launches = _abi.query("forge_launch_count") - n0
+    clk = clocks.stop() if rank == 0 else None
+    n_total = E + shape.n_shared
+    value = n_total * args.steps / (ms / 1e3)
+
+    # ---- end to end: host buffers in, packed results out (pinned memory, copies inside the timed region)
+    e2e = None
+    if not args.no_e2e:
+        hX = X.cpu().pin_memory() if rank == 0 else None
+        hids = ids.cpu().pin_memory() if rank == 0 else None
+        hW = [w.cpu().pin_memory() for w in (Wg, Wu, Wd)]
+        dW = [torch.empty_like(w) for w in (Wg, Wu, Wd)]
+        bytes_in = sum(w.numel() * w.element_size() for w in hW)
+        if rank == 0:
+            bytes_in += hX.numel() * 2 + hids.numel() * 4
+        host_out = {}
+        d2h = [0]
+
+        def step_e2e():
+            if rank == 0:
+                X.copy_(hX, non_blocking=True)
+                ids.copy_(hids, non_blocking=True)
+            for d, h in zip(dW, hW):
+                d.copy_(h, non_blocking=True)
+            _, gathered = step(X, ids, dW[0], dW[1], dW[2])
+            if rank == 0:
+                tot = 0
+                for k, parts in gathered.items():
+                    for j, p in enumerate(parts):
+                        key = (k, j)
+                        if key not in host_out:
+                            host_out[key] = torch.empty(p.shape, dtype=p.dtype).pin_memory()
+                        host_out[key].copy_(p, non_blocking=True)
+                        tot += p.numel() * p.element_size()
+                d2h[0] = tot
+            torch.cuda.current_stream().synchronize()
+
+        for _ in range(min(args.warmup, 2)):
+            step_e2e()
+        ms_e2e = timed(step_e2e, args.steps)
+        h2d_total = bytes_in
+        if world > 1:
+            t = torch.tensor([float(bytes_in)], dtype=torch.float64, device=dev)
+            dist.all_reduce(t)
+            h2d_total = int(t.item())
+        e2e = {"value": n_total * args.steps / (ms_e2e / 1e3), "unit": UNIT, "h2d_bytes_per_step": int(h2d_total),
+               "d2h_bytes_per_step": int(d2h[0]), "ms_per_step": ms_e2e / args.steps}
+
+    # ---- per-entry-point device time of one more step (rank 0's slice) and the roofline of the top kernel
+    pt = PhaseTimer()
+    pt.install()
+    pt.enabled = True
+    out, _ = step(X, ids, Wg, Wu, Wd)
+    phases = pt.summary()
+    pt.enabled = False
+    counts = out["counts"].cpu().double()
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    hbm_peak, hbm_src = (peaks.get("hbm_gbs"), "measured") if peaks.get("hbm_gbs") else (6650.0, "fallback")
+    tf_peak, tf_src = ((peaks.get("bf16_tflops_sustained"), "measured sustained") if peaks.get("bf16_tflops_sustained")
+                       else (1400.0, "fallback sustained"))
+    n_loc = len(my_ids)
+    hess_flops = float((2.0 * counts * (Hd * Hd + I * I)).sum())
+    elems = n_loc * 3 * I * Hd
+    alg_bytes = {
+        "forge_hessian_grouped": None,
+        "forge_quant_grid": elems * 2 + 8 * elems / 128,
+        "forge_gptq_solve_batched": elems * (2 + 1),
+        "forge_chol_inv_upper_batched": n_loc * (2 * Hd * Hd + I * I) * 4 * 2,
+        "forge_hessian_gather_damp": n_loc * (2 * Hd * Hd + I * I) * 4 * 2,
+        "forge_hessian_scan": n_loc * (Hd * Hd + I * I) * 4,
+        "forge_pack_int4": elems * 1.5,
+    }
+    top = max(phases, key=phases.get) if phases else None
+    roofline = None
+    if top is not None:
+        t_s = phases[top] / 1e3
+        if top == "forge_hessian_grouped":
+            ach = hess_flops / t_s / 1e12
+            roofline = {"kernel": top, "bound": "tensor", "achieved": ach, "peak": tf_peak, "unit": "TFLOP/s",
+                        "frac": ach / tf_peak, "traffic": None, "peak_source": tf_src}
+        else:
+            ab = alg_bytes.get(top) or 0.0
+            ach = ab / t_s / 1e9
+            roofline = {"kernel": top, "bound": "hbm", "achieved": ach, "peak": hbm_peak, "unit": "GB/s",
+                        "frac": ach / hbm_peak, "traffic": None, "peak_source": hbm_src,
+                        "note": "fp32-FMA / MUFU issue bound kernel; algorithmic bytes over its device time"}
+        t_h = phases.get("forge_hessian_grouped", 0.0) / 1e3
+        roofline["hessian_tflops"] = hess_flops / t_h / 1e12 if t_h > 0 else None
+        roofline["hessian_frac_of_bf16_peak"] = (hess_flops / t_h / 1e12 / tf_peak) if t_h > 0 else None
+
+    cpu_base = None
+    if rank == 0 and not args.no_cpu_baseline:
+        c = sorted(int(v) for v in counts.tolist()[: max(1, e1 - e0)])
+        hot, cold = c[-1], c[0]
+        secs = cpu_sample(shape, recipe, [hot, cold])
+        cpu_base = {"value": 2.0 / secs, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
+                    "sample": f"2 experts at full matrix shape: hottest ({hot} tokens) and coldest ({cold} tokens) "
+                              f"of rank 0's slice; experts/s extrapolated from their mean time"}
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "bf16 inputs / f32 accumulate and solve", "data": "synthetic",
+                "config": {"workload": workload_name(shape, recipe), "parallelism": f"ep{world}",
+                           "l2": "inputs larger than L2 (X, weights and Hessians >> 126 MB)"},
+                "clocks": clk, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline,
+                "cpu_baseline": cpu_base,
+                "phases_ms_rank0": {k: round(v, 3) for k, v in sorted(phases.items(), key=lambda kv: -kv[1])}}
+        print(json.dumps(line), flush=True)
+
+
+def main():
+    args = parse()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

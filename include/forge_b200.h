@@ -43,6 +43,8 @@ enum {
 
 int forge_version(void);
 const char *forge_last_error(void);
+/* number of kernels this library has launched in the calling process so far */
+long long forge_launch_count(void);
 
 /* ---- A0: DeepSeek fp8 block de-quantisation ------------------------------
  * out_bf16[o,i] = bf16( fp32(w_fp8_e4m3[o,i]) * scale_inv[o/so, i/si] ),

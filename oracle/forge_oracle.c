@@ -69,7 +69,7 @@ void fo_absmax_grid(const float *X, int64_t RG, int64_t gs, int bits, int sym,
         float s, q0;
         if (sym) {                                    /* quant_grid.cu:81-84 */
             float amax = fmaxf(fabsf(mn), fabsf(mx));
-            s = (2.0f / maxq) * amax + FO_EPS;
+            s = fmaf(2.0f / maxq, amax, FO_EPS);  /* a*b+c: one FMA under nvcc's default -fmad=true */
             q0 = 0.5f * (maxq + 1.0f);
         } else {                                      /* quant_grid.cu:85-92 */
             s = (mx - mn) / maxq + FO_EPS;

@@ -1,0 +1,79 @@
+"""Expert-parallel host logic with world_size-2 gloo ranks on the CPU."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from forge import dist as fdist
+from forge import synth
+
+
+def test_shard_experts_partitions_everything():
+    for E in (1, 7, 128, 257, 385):
+        for world in (1, 2, 4, 8):
+            spans = [fdist.shard_experts(E, world, r) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == E
+            for (a, b), (c, d) in zip(spans, spans[1:]):
+                assert b == c
+            sizes = [b - a for a, b in spans]
+            assert max(sizes) - min(sizes) <= 1
+    assert fdist.shard_experts(384, 8, 3) == (144, 192)  # 48 experts per GPU
+
+
+def test_shared_expert_goes_to_least_loaded_rank():
+    ids = torch.tensor([[0, 1], [0, 1], [2, 3], [0, 2]], dtype=torch.int32)
+    # experts 0-1 -> rank 0 (5 tokens), experts 2-3 -> rank 1 (3 tokens)
+    assert fdist.shared_expert_owner(ids, 4, 2) == 1
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, fail_rank):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        E, T, Hd = 5, 64, 16
+        if rank == 0:
+            X = synth.student_t_activations(T, Hd, seed=3)
+            ids = synth.route(synth.LayerShape("t", E, 0, Hd, 8, T, 2), T, seed=3)
+        else:
+            X = torch.zeros((T, Hd), dtype=torch.bfloat16)
+            ids = torch.zeros((T, 2), dtype=torch.int32)
+        X, ids = fdist.broadcast_inputs(X, ids, src=0, chunks=4)
+        X_ref = synth.student_t_activations(T, Hd, seed=3)
+        assert torch.equal(X.view(torch.int16), X_ref.view(torch.int16))
+        b, e = fdist.shard_experts(E, world, rank)
+        # every rank "packs" its slice: value = expert id, so the gathered result is checkable
+        local = {"packed": torch.stack([torch.full((3, 2), i, dtype=torch.int32) for i in range(b, e)]),
+                 "scale": torch.arange(b, e, dtype=torch.float16)}
+
+        def shapes(r):
+            bb, ee = fdist.shard_experts(E, world, r)
+            return {"packed": ((ee - bb, 3, 2), torch.int32), "scale": ((ee - bb,), torch.float16)}
+
+        got = fdist.gather_to_rank0(local, shapes)
+        if rank == 0:
+            packed = torch.cat(got["packed"])
+            assert packed.shape == (E, 3, 2)
+            assert torch.equal(packed[:, 0, 0], torch.arange(E, dtype=torch.int32))
+            assert torch.equal(torch.cat(got["scale"]), torch.arange(E, dtype=torch.float16))
+        else:
+            assert got == {}
+        assert fdist.shared_expert_owner(ids, E, world) in range(world)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_broadcast_and_gather_two_ranks():
+    port = _free_port()
+    mp.spawn(_worker, args=(2, port, -1), nprocs=2, join=True)

@@ -1,0 +1,441 @@
+"""Parity of every sm_100a kernel with the CPU oracle, through the C ABI (forge.ops -> libforge_b200.so).
+
+Tolerances (from the acceptance rules of the path): integer / byte outputs bit-exact; Hessians within 1e-4
+relative Frobenius error of the fp32 torch path; solver codes >= 99.5 % equal to the oracle's.
+"""
+import numpy as np
+import pytest
+import torch
+
+import ref_port as O
+from helpers import rel_fro, random_spd, golden_case, case_inputs
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _need_cuda():
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    from forge import _abi
+    _abi.load_library()
+
+
+def _ops():
+    from forge import ops
+    return ops
+
+
+# ------------------------------------------------------------------------------------------------ A0
+@pytest.mark.parametrize("shape", [(256, 256), (200, 384), (130, 136)])
+def test_fp8_block_dequant_bit_exact(shape):
+    from forge import synth
+    ops = _ops()
+    g = torch.Generator().manual_seed(1)
+    w = torch.randn(shape, generator=g) * 0.02
+    if shape[1] % 128:
+        q = w.to(torch.float8_e4m3fn)
+        sinv = torch.rand((2, 1), generator=g) + 0.5  # one column tile, two row tiles
+    else:
+        q, sinv = synth.fp8_block_encode(w)
+    ref = O.fp8_block_dequant(q, sinv)
+    got = ops.fp8_block_dequant(q.to(DEV), sinv.to(DEV)).cpu()
+    assert torch.equal(ref.view(torch.int16), got.view(torch.int16))
+
+
+# ------------------------------------------------------------------------------------------- routing
+def test_route_lists_match_torch():
+    from forge import synth
+    ops = _ops()
+    shape = synth.LayerShape("t", 16, 0, 16, 8, 3000, 4)
+    ids = synth.route(shape, 3000, seed=2)
+    for (e0, n) in [(0, 16), (5, 7), (15, 1)]:
+        counts, offsets, lists = ops.route_build_lists(ids.to(DEV), e0, n)
+        counts, offsets, lists = counts.cpu(), offsets.cpu(), lists.cpu()
+        for j in range(n):
+            want = torch.nonzero((ids == e0 + j).any(dim=1)).flatten().to(torch.int32)
+            assert int(counts[j]) == want.numel()
+            got = lists[int(offsets[j]):int(offsets[j + 1])]
+            assert torch.equal(got, want)
+
+
+# ------------------------------------------------------------------------------------------------ A2
+def _hessian_ref(X, idx_lists, n_prev=None, H_prev=None):
+    outs = []
+    for b, idx in enumerate(idx_lists):
+        xb = X[idx].float()
+        n = xb.shape[0]
+        npv = 0 if n_prev is None else int(n_prev[b])
+        if n == 0:
+            outs.append(H_prev[b] if H_prev is not None else None)
+            continue
+        tot = npv + n
+        H = (2.0 / tot) * (xb.T @ xb)
+        if npv > 0:
+            H = H + (npv / tot) * H_prev[b]
+        outs.append(H)
+    return outs
+
+
+@pytest.mark.parametrize("simt", [True, False])
+@pytest.mark.parametrize("C,counts", [(64, [5]), (256, [64, 1, 0, 130]), (320, [200, 63]), (512, [700, 65, 129])])
+def test_hessian_grouped_matches_fp32_torch(simt, C, counts):
+    ops = _ops()
+    g = torch.Generator().manual_seed(3)
+    T = 1024
+    X = (torch.randn(T, C, generator=g) * torch.exp(torch.randn(C, generator=g))).to(torch.bfloat16)
+    lists = [torch.randperm(T, generator=g)[:n].sort().values for n in counts]
+    offsets = torch.tensor([0] + list(np.cumsum(counts)), dtype=torch.int64)
+    tok = torch.cat(lists).to(torch.int32) if sum(counts) else torch.zeros(1, dtype=torch.int32)
+    nb = len(counts)
+    H = torch.full((nb, C, C), float("nan"), device=DEV)
+    status = ops.hessian_grouped(X.to(DEV), C, tok.to(DEV), offsets.to(DEV), H, mirror=True, simt=simt)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    ref = _hessian_ref(X, lists)
+    for b in range(nb):
+        if counts[b] == 0:
+            assert torch.isnan(H[b]).all()  # untouched
+            continue
+        assert rel_fro(H[b].cpu(), ref[b]) < 1e-4
+        assert torch.equal(H[b], H[b].T)
+
+
+def test_hessian_running_mean_and_contiguous_rows():
+    """Second batch: H = (N_old/N) H + (2/N) X^T X with token_idx = NULL (rows offsets[b] ..)."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(4)
+    C = 256
+    X1 = (torch.randn(300, C, generator=g)).to(torch.bfloat16)
+    X2 = (torch.randn(200, C, generator=g)).to(torch.bfloat16)
+    H = torch.empty((2, C, C), device=DEV)
+    n_prev = torch.zeros(2, dtype=torch.int64, device=DEV)
+    off1 = torch.tensor([0, 100, 300], dtype=torch.int64, device=DEV)
+    off2 = torch.tensor([0, 150, 200], dtype=torch.int64, device=DEV)
+    st = ops.hessian_grouped(X1.to(DEV), C, None, off1, H, n_prev=n_prev, mirror=True)
+    ops.counts_add(n_prev, off1)
+    ops.hessian_grouped(X2.to(DEV), C, None, off2, H, n_prev=n_prev, mirror=True, status=st)
+    ops.counts_add(n_prev, off2)
+    assert int(st.item()) == 0
+    assert n_prev.tolist() == [250, 250]
+    h = O.OracleGPTQ(torch.zeros(4, C, dtype=torch.bfloat16))
+    h.update(X1[:100]); h.update(X2[:150])
+    assert rel_fro(H[0].cpu(), h.H) < 1e-4
+    h = O.OracleGPTQ(torch.zeros(4, C, dtype=torch.bfloat16))
+    h.update(X1[100:300]); h.update(X2[150:200])
+    assert rel_fro(H[1].cpu(), h.H) < 1e-4
+
+
+def test_hessian_upper_only_flag_leaves_lower_untouched():
+    ops = _ops()
+    g = torch.Generator().manual_seed(5)
+    C = 256
+    X = torch.randn(128, C, generator=g).to(torch.bfloat16)
+    H = torch.full((1, C, C), -7.0, device=DEV)
+    off = torch.tensor([0, 128], dtype=torch.int64, device=DEV)
+    ops.hessian_grouped(X.to(DEV), C, None, off, H, mirror=False)
+    ref = (2.0 / 128) * (X.float().T @ X.float())
+    Hc = H[0].cpu()
+    assert rel_fro(torch.triu(Hc), torch.triu(ref)) < 1e-4
+    assert torch.all(torch.tril(Hc, -1)[torch.tril(torch.ones(C, C), -1).bool()] == -7.0)
+
+
+# ------------------------------------------------------------------------------------------------ A3
+def test_scan_gather_damp_semantics():
+    ops = _ops()
+    g = torch.Generator().manual_seed(6)
+    C = 96
+    Hs = torch.stack([random_spd(C, 7), random_spd(C, 8), random_spd(C, 9), random_spd(C, 10)])
+    Hs[1, 5, :] = 0; Hs[1, :, 5] = 0           # dead channel 5
+    Hs[2, 3, 4] = float("nan")                  # NaN -> identity
+    n_samples = torch.tensor([10, 10, 10, 0])   # expert 3 saw no token -> identity
+    diag, pruned, invalid = ops.hessian_scan(Hs.to(DEV), n_samples.to(DEV))
+    assert invalid.tolist() == [0, 0, 1, 1]
+    assert pruned[1].nonzero().flatten().tolist() == [5] and int(pruned.sum()) == 1
+    assert torch.equal(diag[2].cpu(), torch.ones(C)) and float(diag[1, 5]) == 1.0
+    perm = torch.argsort(diag, dim=1, descending=True).to(torch.int32).contiguous()
+    wzero = torch.zeros((4, C), dtype=torch.uint8)
+    wzero[0, 9] = 1
+    A, Hp, damp = ops.hessian_gather_damp(Hs.to(DEV), perm, pruned, wzero.to(DEV), invalid, 0.01, want_hp=True)
+    for b in range(4):
+        H = Hs[b].clone()
+        if invalid[b]:
+            H = torch.eye(C)
+        pr = torch.diag(H) == 0
+        H[pr, :] = 0; H[:, pr] = 0; H[pr, pr] = 1
+        p = perm[b].cpu().long()
+        H = H[p][:, p]
+        zc = wzero[b].bool()
+        H[zc, :] = 0; H[:, zc] = 0; H[zc, zc] = 1.0
+        d = 0.01 * torch.diag(H).mean()
+        H[range(C), range(C)] += d
+        assert abs(float(damp[b]) - float(d)) <= 1e-6 * float(d)
+        got = Hp[b].cpu()
+        off = ~torch.eye(C, dtype=torch.bool)
+        assert torch.equal(got[off], H[off])
+        assert torch.allclose(got.diag(), H.diag(), rtol=1e-6)
+        assert torch.equal(A[b].cpu(), torch.flip(got, (0, 1)))
+
+
+def test_weight_column_helpers():
+    ops = _ops()
+    W = torch.randn(2, 12, 40).to(torch.bfloat16)
+    W[0, :, 7] = 0
+    pruned = torch.zeros((2, 40), dtype=torch.uint8)
+    pruned[1, 3] = 1
+    Wd = W.to(DEV)
+    ops.weight_apply_pruned(Wd, pruned.to(DEV))
+    wz = ops.weight_zero_cols(Wd).cpu()
+    assert wz[0].nonzero().flatten().tolist() == [7]
+    assert wz[1].nonzero().flatten().tolist() == [3]
+    assert float(Wd[1, :, 3].abs().max()) == 0.0
+
+
+# ------------------------------------------------------------------------------------------------ A4
+def _factor_ref(Hd):
+    L = torch.linalg.cholesky(Hd)
+    T = torch.linalg.cholesky(torch.cholesky_inverse(L), upper=True)
+    return T / T.diag()[:, None], T.diag()
+
+
+@pytest.mark.parametrize("C", [32, 64, 96, 200, 512, 1100])
+def test_cholesky_inverse_factor(C):
+    ops = _ops()
+    nb = 3
+    Hs = torch.stack([random_spd(C, 20 + b) for b in range(nb)])
+    for b in range(nb):
+        Hs[b][range(C), range(C)] += 0.01 * Hs[b].diag().mean()
+    A = torch.flip(Hs, (1, 2)).contiguous().to(DEV)
+    U, udiag, info = ops.chol_inv_upper(A, zero_lower=True)
+    assert info.tolist() == [0] * nb
+    for b in range(nb):
+        Ur, dr = _factor_ref(Hs[b].double())
+        assert float(torch.tril(U[b].cpu(), -1).abs().max()) == 0.0
+        assert torch.equal(U[b].diagonal().cpu(), torch.ones(C))
+        assert rel_fro(U[b].cpu(), Ur) < 2e-4
+        assert rel_fro(udiag[b].cpu(), dr) < 2e-4
+        # and against the reference's own fp32 three-step path
+        h = O.OracleGPTQ(torch.ones(2, C, dtype=torch.bfloat16), rel_damp=0.0)
+        h.H = Hs[b].clone()
+        assert rel_fro(U[b].cpu(), h._h_factor()) < 5e-4
+
+
+def test_cholesky_flags_indefinite_matrix_and_falls_back_to_identity():
+    ops = _ops()
+    C = 128
+    good = random_spd(C, 30)
+    good[range(C), range(C)] += 0.01 * good.diag().mean()
+    bad = good.clone()
+    bad[70, 70] = -1.0
+    A = torch.flip(torch.stack([good, bad]), (1, 2)).contiguous().to(DEV)
+    U, udiag, info = ops.chol_inv_upper(A, zero_lower=True)
+    assert int(info[0]) == 0 and int(info[1]) > 0
+    assert torch.equal(U[1].cpu(), torch.eye(C)) and torch.equal(udiag[1].cpu(), torch.ones(C))
+    assert rel_fro(U[0].cpu(), _factor_ref(good.double())[0]) < 2e-4
+
+
+@pytest.mark.parametrize("name", ["plain", "actorder_multibatch", "deadcol_zerow", "sparse_unnormalised"])
+def test_factor_against_reference_golden(golden, name):
+    """U from the CUDA path vs the reference's own _h_factor output on its own prepared Hessian."""
+    ops = _ops()
+    c = golden_case(golden, name)
+    inp = case_inputs(c)
+    C = inp["C"]
+    Hp = torch.from_numpy(c["H_prep"])
+    Wp = torch.from_numpy(np.ascontiguousarray(c["W_prep_bits"])).view(torch.bfloat16).view(inp["R"], C)
+    wz = ops.weight_zero_cols(Wp.to(DEV).view(1, inp["R"], C))
+    A, _, _ = ops.hessian_gather_damp(Hp.to(DEV).view(1, C, C), None, None, wz, None, inp["rel_damp"])
+    U, udiag, info = ops.chol_inv_upper(A, zero_lower=True)
+    Uref = torch.from_numpy(c["U"])
+    assert int(info[0]) == 0
+    if inp["algorithm"] == "sparsegptq":
+        got = U[0].cpu() * udiag[0].cpu()[:, None]
+    else:
+        got = U[0].cpu()
+    assert rel_fro(got, Uref) < 5e-4
+
+
+# ------------------------------------------------------------------------------------------- A5 / A6
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("sym", [True, False])
+@pytest.mark.parametrize("C,gs", [(256, 128), (200, 64), (96, 32), (120, 40)])
+def test_absmax_grid_bit_exact(dtype, sym, C, gs):
+    ops = _ops()
+    g = torch.Generator().manual_seed(40)
+    W = (torch.randn(33, C, generator=g) * 0.02).to(dtype)
+    W[3] = 0
+    s, z = ops.quant_grid(W.to(DEV), gs, 4, sym)
+    G = (C + gs - 1) // gs
+    Wp = torch.nn.functional.pad(W.float(), (0, G * gs - C)).reshape(33 * G, gs)
+    sr, zr = O.build_group_meta_packed(Wp, 4, sym)
+    assert torch.equal(s.cpu(), sr) and torch.equal(z.cpu(), zr)
+
+
+@pytest.mark.parametrize("sym", [True, False])
+@pytest.mark.parametrize("gs", [32, 64, 128])
+def test_mse_grid_agrees_with_oracle(sym, gs):
+    ops = _ops()
+    g = torch.Generator().manual_seed(41)
+    R, C = 64, 512
+    W = (torch.randn(R, C, generator=g) * 0.02)
+    W[torch.rand(R, C, generator=g) < 0.01] *= 8
+    W = W.to(torch.bfloat16)
+    cand = torch.linspace(1.0, 0.2, 100, dtype=torch.float32)
+    s, z = ops.quant_grid(W.to(DEV), gs, 4, sym, cand.to(DEV), 2.4)
+    Wg = W.float().reshape(-1, gs)
+    s0, z0 = O.build_group_meta_packed(Wg, 4, sym)
+    sr, zr = O.mse_scale_groups_packed(Wg, s0, z0, cand, 2.4, 4, sym)
+    same = (s.cpu() == sr) & (z.cpu() == zr)
+    # the kernel uses the hardware's approximate log/exp; only near-tied candidates may differ
+    assert float(same.float().mean()) >= 0.995
+    # two-call form (refine in place) gives the same answer as the fused call
+    s2, z2 = ops.quant_grid(W.to(DEV), gs, 4, sym)
+    ops.quant_grid_mse(W.to(DEV), gs, 4, sym, cand.to(DEV), 2.4, s2, z2)
+    assert torch.equal(s2, s) and torch.equal(z2, z)
+
+
+# ------------------------------------------------------------------------------------------- A7 - A9
+def _solver_case(C, R, seed, gs=32, sym=True):
+    g = torch.Generator().manual_seed(seed)
+    W = (torch.randn(R, C, generator=g) * 0.02).to(torch.bfloat16)
+    H = random_spd(C, seed + 1)
+    H[range(C), range(C)] += 0.01 * H.diag().mean()
+    T = torch.linalg.cholesky(torch.cholesky_inverse(torch.linalg.cholesky(H)), upper=True)
+    G = (C + gs - 1) // gs
+    Wp = torch.nn.functional.pad(W.float(), (0, G * gs - C)).reshape(R * G, gs)
+    s, z = O.build_group_meta_packed(Wp, 4, sym)
+    return W, T.contiguous(), s, z, G
+
+
+def _expand(t, R, G, gs, C, perm):
+    return t.view(R, G).repeat_interleave(gs, dim=1)[:, :C].T[perm].contiguous()
+
+
+@pytest.mark.parametrize("C,R", [(32, 7), (96, 130), (128, 128), (200, 50), (512, 300)])
+@pytest.mark.parametrize("sym", [True, False])
+def test_gptq_solver_reference_operator(C, R, sym):
+    ops = _ops()
+    W, T, s, z, G = _solver_case(C, R, 50 + C, sym=sym)
+    U = (T / T.diag()[:, None]).contiguous()
+    perm = torch.arange(C)
+    S, Z = _expand(s, R, G, 32, C, perm), _expand(z, R, G, 32, C, perm)
+    Wt = W.float().T.contiguous()
+    Wo = Wt.clone()
+    q_ref = O.gptq_solver(Wo, U, S, Z, 4)
+    Wd = Wt.to(DEV)
+    q = ops.gptq_solve_cr(Wd, U.to(DEV), S.to(DEV), Z.to(DEV), 4)
+    agree = float((q.cpu() == q_ref).float().mean())
+    assert agree >= 0.995, agree
+    same = q.cpu() == q_ref
+    assert torch.allclose(Wd.cpu()[same], Wo[same], atol=1e-6)  # de-quantised weights written back in place
+
+
+@pytest.mark.parametrize("C,R", [(64, 24), (160, 129), (512, 64)])
+def test_sparse14_solver_reference_operator(C, R):
+    ops = _ops()
+    W, T, s, z, G = _solver_case(C, R, 60 + C)
+    perm = torch.arange(C)
+    S, Z = _expand(s, R, G, 32, C, perm), _expand(z, R, G, 32, C, perm)
+    Wt = W.float().T.contiguous()
+    Wo = Wt.clone()
+    q_ref, M_ref = O.sparsegptq14_solver(Wo, T.clone(), S, Z, 4)
+    from forge.backend.cuda import kernels
+    Td = T.clone().to(DEV)
+    q, M = kernels.sparsegptq14_solver(Wt.to(DEV), Td, S.to(DEV), Z.to(DEV), 4)
+    Mi, Mr = M.view(torch.int32).cpu(), M_ref.view(torch.int32)
+    assert float((Mi == Mr).float().mean()) >= 0.99
+    assert float((q.cpu() == q_ref).float().mean()) >= 0.995
+    # U was row-normalised in place like the reference does
+    assert rel_fro(Td.cpu(), T / T.diag()[:, None]) < 1e-6
+    # exactly one kept weight per group of four
+    m = Mi.numpy().astype(np.uint32)
+    for i in range(8):
+        nib = (m >> (4 * i)) & 0xF
+        valid = np.isin(nib, [1, 2, 4, 8])
+        assert valid.all()
+
+
+@pytest.mark.parametrize("order", ["default", "activation"])
+@pytest.mark.parametrize("sparse", [False, True])
+def test_batched_solver_equals_reference_operator_form(order, sparse):
+    """The batched entry point (bf16 W [R,C], per-group scales, permutation) and the reference-operator
+    entry point run the same arithmetic: identical codes."""
+    ops = _ops()
+    C, R, gs, nb = 256, 140, 64, 3
+    g = torch.Generator().manual_seed(70)
+    Ws, Us, uds, perms, ss, zs = [], [], [], [], [], []
+    for b in range(nb):
+        W, T, _, _, _ = _solver_case(C, R, 71 + b, gs=gs)
+        G = C // gs
+        s, z = O.build_group_meta_packed(W.float().reshape(R * G, gs), 4, not sparse and b == 1)
+        Ws.append(W); Us.append(T / T.diag()[:, None]); uds.append(T.diag().clone())
+        perms.append(torch.randperm(C, generator=g) if order == "activation" else torch.arange(C))
+        ss.append(s); zs.append(z)
+    Wb = torch.stack(Ws).to(DEV)
+    Ub = torch.stack(Us).contiguous().to(DEV)
+    udb = torch.stack(uds).contiguous().to(DEV)
+    pb = torch.stack(perms).to(torch.int32).contiguous().to(DEV)
+    sb, zb = torch.cat(ss).to(DEV), torch.cat(zs).to(DEV)
+    out = ops.gptq_solve_batched(Wb, Ub, sb, zb, gs, 4, perm=pb if order == "activation" else None,
+                                 udiag=udb if sparse else None, sparse14=sparse)
+    qb, Mb = out if sparse else (out, None)
+    for b in range(nb):
+        G = C // gs
+        p = perms[b]
+        S, Z = _expand(ss[b], R, G, gs, C, p), _expand(zs[b], R, G, gs, C, p)
+        Wt = Ws[b].float().T[p].contiguous().to(DEV)
+        if sparse:
+            q, M = ops.gptq_solve_cr(Wt, Us[b].contiguous().to(DEV), S.to(DEV), Z.to(DEV), 4,
+                                     uinv=(1.0 / uds[b]).to(DEV))
+            assert torch.equal(M, Mb[b])
+        else:
+            q = ops.gptq_solve_cr(Wt, Us[b].contiguous().to(DEV), S.to(DEV), Z.to(DEV), 4)
+        q_rc = q[torch.argsort(p).to(DEV)].T.contiguous()  # forge/gptq.py:139
+        assert torch.equal(q_rc, qb[b])
+
+
+# ------------------------------------------------------------------------------------------ A10 - A12
+def test_dequantize_matches_reference_formula():
+    ops = _ops()
+    g = torch.Generator().manual_seed(80)
+    R, C, gs = 20, 200, 64
+    q = torch.randint(0, 16, (R, C), generator=g, dtype=torch.uint8)
+    G = (C + gs - 1) // gs
+    s = torch.rand(R * G, generator=g) * 0.01
+    z = torch.randint(0, 16, (R * G,), generator=g).float()
+    for dt in (torch.float32, torch.bfloat16):
+        ref = O.dequantize_forge_full(dt, q, s, z, gs)
+        got = ops.dequantize(q.to(DEV), s.to(DEV), z.to(DEV), gs, dt).cpu()
+        assert torch.equal(ref.view(torch.int32 if dt == torch.float32 else torch.int16),
+                           got.view(torch.int32 if dt == torch.float32 else torch.int16))
+
+
+@pytest.mark.parametrize("R,C,gs,sym", [(8, 64, 32, True), (5, 100, 32, False), (3, 24, 8, False), (768, 2048, 128, True)])
+def test_pack_int4_bit_exact(R, C, gs, sym):
+    ops = _ops()
+    g = torch.Generator().manual_seed(81)
+    q = torch.randint(0, 16, (R, C), generator=g, dtype=torch.uint8)
+    G = (C + gs - 1) // gs
+    zero = torch.full((R, G), 8.0) if sym else torch.randint(0, 16, (R, G), generator=g).float()
+    ref = O.pack_weight({"qweight": q, "scale": torch.ones(R, G), "zero": zero}, 4, sym, gs)["weight_packed"]
+    got = ops.pack_int4(q.to(DEV), zero.reshape(-1).to(DEV), gs).cpu()
+    assert torch.equal(ref, got)
+    assert torch.equal(O.pack_int4(q, zero, gs), got)
+
+
+@pytest.mark.parametrize("R,C", [(6, 96), (33, 64), (130, 256), (7, 40), (1536, 3072)])
+def test_pack_sparse14_bit_exact(R, C):
+    ops = _ops()
+    g = torch.Generator().manual_seed(82)
+    q = torch.randint(0, 16, (R, C), generator=g, dtype=torch.uint8)
+    G32 = (C + 31) // 32
+    keep = torch.randint(0, 4, (G32 * 8, R), generator=g)
+    shifts = (torch.arange(G32 * 8) % 8 * 4).view(-1, 1)
+    bits = (torch.ones_like(keep) << (keep + shifts)).view(G32, 8, R).sum(1)
+    bits[0, 0] &= ~0xF  # a group of four with nothing kept keeps the default nibble 8
+    M = torch.from_numpy(bits.numpy().astype(np.uint32).view(np.int32).copy())
+    sc = torch.rand(G32, R, generator=g) * 0.01 + 1e-4
+    ref = O.pack_sparsegptq14_to_u64x2(q, M, sc)
+    got = ops.pack_sparse14(q.to(DEV), M.to(DEV), sc.to(DEV)).cpu()
+    assert torch.equal(ref, got)
