@@ -102,8 +102,10 @@ quant_grid_kernel(const void *__restrict__ Wv, int64_t rows, int64_t C, int64_t 
 #pragma unroll
                     for (int i = 0; i < VPL; ++i) {
                         const float v = vals[i];
-                        float q = rintf(fmaf(v, rcp, q0));
-                        q = fminf(fmaxf(q, 0.0f), maxq);
+                        // clamp(rint(x), 0, maxq) == rint(clamp(x, 0, maxq)); in [0, 2^22) the
+                        // round-half-even of rint is the rounding of an fp32 add of 1.5 * 2^23
+                        float q = fminf(fmaxf(fmaf(v, rcp, q0), 0.0f), maxq);
+                        q = __fsub_rn(__fadd_rn(q, 12582912.0f), 12582912.0f);
                         const float diff = fmaf(__fsub_rn(q, q0), s, -v);
                         const float e = fmaxf(fabsf(diff), 1e-20f);
                         const float val = __expf(__fmul_rn(__logf(e), norm));

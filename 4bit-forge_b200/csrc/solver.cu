@@ -98,8 +98,9 @@ __device__ __forceinline__ void load_chunk(float *us, float *es, const float *U,
 __device__ __forceinline__ void quantize_scalar(float x, float s, float q0, float maxq, float &err, float &deq,
                                                 uint8_t &qb) {
     const float inv_s = __fdiv_rn(1.0f, __fadd_rn(s, kEps));
-    float q = rintf(fmaf(x, inv_s, q0));
-    q = fminf(fmaxf(q, 0.0f), maxq);
+    // clamp(rint(b), 0, maxq) == rint(clamp(b, 0, maxq)), and rint on [0, 2^22) is an add of 1.5 * 2^23
+    float q = fminf(fmaxf(fmaf(x, inv_s, q0), 0.0f), maxq);
+    q = __fsub_rn(__fadd_rn(q, 12582912.0f), 12582912.0f);
     deq = fmaf(q, s, -__fmul_rn(q0, s));
     err = __fsub_rn(x, deq);
     qb = (uint8_t)(int)q;
