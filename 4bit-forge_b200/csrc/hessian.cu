@@ -21,8 +21,10 @@
 // Every mbarrier wait is bounded by a clock64 budget; on expiry the CTA raises FORGE_ERR_TIMEOUT in
 // the status word, drains its copies, frees TMEM and returns.
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 using namespace forge;
+using namespace forge::tc;
 
 namespace {
 
@@ -35,7 +37,6 @@ constexpr int kStages = 3;
 constexpr int kLag = 2;                       // cp.async groups in flight per thread
 constexpr int kProducerThreads = 128;
 constexpr int kThreads = 160;
-constexpr long long kWaitBudget = 4000000000LL;  // clock64 ticks (~2 s)
 constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
 
 struct HessParams {
@@ -51,50 +52,6 @@ struct HessParams {
     int nt;    // tiles per edge
     int ntri;  // tiles per expert (upper triangle)
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok;
-}
-// Bounded wait: false when the budget ran out or another thread of the CTA already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (clock64() - t0 > kWaitBudget) {
-            *abort_flag = 1;
-            return false;
-        }
-    }
-}
-
-__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void *src, bool pred) {
-    const int sz = pred ? 16 : 0;
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
 // UMMA shared-memory descriptor, MN-major operand, 128-byte swizzle:
 //   bits [0,14)  start address >> 4          bits [16,30) leading byte offset >> 4 (next 64-element
@@ -117,23 +74,6 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint6
         : "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(kIdesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
         : "memory");
 }
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
 __device__ __forceinline__ void tile_coords(int p, int nt, int &ti, int &tj) {
     ti = 0;
     while (p >= nt - ti) { p -= nt - ti; ++ti; }
@@ -237,6 +177,7 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_tc_kernel(const HessParam
             if (!ok) break;
             // ---- epilogue: TMEM -> registers -> global
             ok = mbar_wait(bar_acc_full, tile_iter & 1u, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below is warp-aligned: the whole warp goes or none
             if (!ok) break;
             tc_fence_after();
             const int64_t np = P.n_prev ? P.n_prev[b] : 0;

@@ -21,6 +21,9 @@
 // access is coalesced across the 128 row-threads; the batched entry point builds Wt from W [R,C] with
 // a tiled transpose-gather and scatters the codes back to [R,C] in the original column order.
 #include "common.cuh"
+#include "tcgen05.cuh"
+#include <stdlib.h>
+#include <string.h>
 
 using namespace forge;
 
@@ -106,6 +109,25 @@ __device__ __forceinline__ void quantize_scalar(float x, float s, float q0, floa
     qb = (uint8_t)(int)q;
 }
 
+// Scale / zero of (row r, column c).  MODE 0: per-group tables [nb][R][G], the group follows the ORIGINAL
+// column index (forge/gptq.py:251-252); MODE 1: per-element tables [nb][C][R].
+template <int MODE>
+__device__ __forceinline__ void load_meta(const SolveParams &p, int b, int u, int64_t r, int64_t c, bool active,
+                                          float &s, float &q0) {
+    s = 1.0f;
+    q0 = 0.0f;
+    if (!active || c >= p.C) return;
+    int64_t gi;
+    if (MODE == 0) {
+        const int64_t oc = p.perm ? (int64_t)p.perm[(int64_t)u * p.C + c] : c;
+        gi = ((int64_t)b * p.R + r) * p.G + oc / p.gs;
+    } else {
+        gi = ((int64_t)b * p.C + c) * p.R + r;
+    }
+    s = __ldg(p.scales + gi);
+    q0 = __ldg(p.qzeros + gi);
+}
+
 template <int MODE, bool SPARSE, int S>
 __device__ __forceinline__ void solve_subblock(float (&x)[kBlk], const float *us, float *es,
                                                const float *uinv_s, const SolveParams &p, int b, int u,
@@ -113,10 +135,26 @@ __device__ __forceinline__ void solve_subblock(float (&x)[kBlk], const float *us
     const int64_t R = p.R, C = p.C;
     const float maxq = (float)p.maxq;
     uint32_t maskbits = 0u;
+    // When the columns are not permuted and a group spans whole sub-blocks, one (scale, zero) pair serves
+    // the 32 columns; otherwise the pair of the NEXT column is fetched while the current one is solved.
+    const bool uniform_meta = (MODE == 0) && (p.perm == nullptr) && (p.gs % kSub == 0);
+    float s_nx, q0_nx;
+    load_meta<MODE>(p, b, u, r, bs + S * kSub, active, s_nx, q0_nx);
+    // Output pointers advance by one column (R elements) per step.  The empty asm makes each advance opaque:
+    // otherwise the 32 x 3 addresses of the unrolled loop are all formed up front and, at two registers
+    // each, evict the row's values to local memory.
+    uint8_t *qp = p.q + ((int64_t)b * C + bs + S * kSub) * R + r;
+    float *ep = E + (bs + S * kSub) * R + r;
+    float *wp = Wt + (bs + S * kSub) * R + r;
 #pragma unroll
     for (int t = 0; t < kSub; ++t) {
+        // keep the loads of later columns from being hoisted over this point: fully unrolled, they would
+        // otherwise all be issued up front and push the row's 128 values out of the register file
+        asm volatile("" ::: "memory");
         const int kk = S * kSub + t;
         const int64_t c = bs + kk;
+        const float s = s_nx, q0 = q0_nx;
+        if (!uniform_meta && t + 1 < kSub) load_meta<MODE>(p, b, u, r, c + 1, active, s_nx, q0_nx);
         float err = 0.0f;
         if (c < C) {
             if (SPARSE && (t % 4 == 0)) {
@@ -135,29 +173,18 @@ __device__ __forceinline__ void solve_subblock(float (&x)[kBlk], const float *us
             uint8_t qb = 0;
             const bool keep = SPARSE ? (((maskbits >> t) & 1u) != 0u) : true;
             if (keep && (active || !SPARSE)) {
-                float s = 1.0f, q0 = 0.0f;
-                if (active) {
-                    if (MODE == 0) {
-                        const int64_t oc = p.perm ? (int64_t)p.perm[(int64_t)u * C + c] : c;
-                        const int64_t gi = ((int64_t)b * R + r) * p.G + oc / p.gs;
-                        s = __ldg(p.scales + gi);
-                        q0 = __ldg(p.qzeros + gi);
-                    } else {
-                        const int64_t gi = ((int64_t)b * C + c) * R + r;
-                        s = __ldg(p.scales + gi);
-                        q0 = __ldg(p.qzeros + gi);
-                    }
-                }
                 quantize_scalar(x[kk], s, q0, maxq, err, deq, qb);
             } else {
                 err = x[kk];  // pruned weight: the whole value is the error (solver_sparsegptq14.cu:118-120)
             }
             if (active) {
-                p.q[((int64_t)b * C + c) * R + r] = qb;
-                if (p.write_deq) Wt[c * R + r] = deq;
-                E[c * R + r] = err;
+                *qp = qb;
+                if (p.write_deq) *wp = deq;
+                *ep = err;
             }
         }
+        qp += R; ep += R; wp += R;
+        asm volatile("" : "+l"(qp), "+l"(ep), "+l"(wp));
         es[t * kBlk + tid] = err;
         // rank-1 update of the rest of the sub-block; U row t broadcast from shared memory
         const float4 *urow = reinterpret_cast<const float4 *>(us + t * kBlk + S * kSub);
@@ -176,12 +203,14 @@ __device__ __forceinline__ void solve_subblock(float (&x)[kBlk], const float *us
         p.M[((int64_t)b * ((C + 31) / 32) + ((bs + S * kSub) >> 5)) * R + r] = maskbits;
     // the sub-block's errors update the later columns of the block
     if (S < 3) {
-#pragma unroll 2
+#pragma unroll 1
         for (int t = 0; t < kSub; ++t) {
             const float e = es[t * kBlk + tid];
             const float4 *urow = reinterpret_cast<const float4 *>(us + t * kBlk);
 #pragma unroll
             for (int k4 = (S + 1) * (kSub / 4); k4 < kBlk / 4; ++k4) {
+                // at most eight panel loads (32 registers) in flight next to the row's 128 values
+                if ((k4 & 7) == 0) asm volatile("" ::: "memory");
                 const float4 u4 = urow[k4];
                 x[4 * k4 + 0] = fmaf(-u4.x, e, x[4 * k4 + 0]);
                 x[4 * k4 + 1] = fmaf(-u4.y, e, x[4 * k4 + 1]);
@@ -246,12 +275,13 @@ __global__ void __launch_bounds__(128, 3) solve_kernel(const SolveParams p) {
             const float *us = Us + buf * kChunkFloats;
             float *es = Es + buf * kChunkFloats;
             if (ch < nleft) {
-#pragma unroll 2
+#pragma unroll 1
                 for (int jj = 0; jj < kSub; ++jj) {
                     const float e = es[jj * kBlk + tid];
                     const float4 *urow = reinterpret_cast<const float4 *>(us + jj * kBlk);
 #pragma unroll
                     for (int k4 = 0; k4 < kBlk / 4; ++k4) {
+                        if ((k4 & 7) == 0) asm volatile("" ::: "memory");
                         const float4 u4 = urow[k4];
                         x[4 * k4 + 0] = fmaf(-u4.x, e, x[4 * k4 + 0]);
                         x[4 * k4 + 1] = fmaf(-u4.y, e, x[4 * k4 + 1]);
@@ -269,6 +299,269 @@ __global__ void __launch_bounds__(128, 3) solve_kernel(const SolveParams p) {
             }
             __syncthreads();  // the next iteration refills the other buffer, the one after it this one
         }
+    }
+}
+
+
+// ================================================================================================
+// Tensor-core build of the same solver: the lazy update  acc[r, k] = sum_{j<bs} E[j, r] * U[j, bs+k]
+// runs on tcgen05 as a  M=128 (rows) x N=128 (block columns) x K=8  TF32 GEMM per k-step with the fp32
+// accumulator in 128 TMEM columns, so that one TMEM lane is one weight row and tcgen05.ld hands every
+// row-thread its 128 values in registers — the layout the sequential in-block phase wants.
+//
+// fp32 fidelity: an operand v is split as  hi = tf32(v) (round to nearest on the bit pattern),
+// lo = tf32(v - hi);  acc += Ehi*Uhi + Elo*Uhi + Ehi*Ulo  (three MMAs per k-step).  The dropped Elo*Ulo
+// term and the truncation of lo are ~2^-21 relative, the size of fp32 rounding in a dot product.
+//
+// Both operands are "MN-major": E is [C][R] with the 128 rows of the strip contiguous, the U panel is
+// [j][bs..bs+128) with the block columns contiguous.  A k-step piece is [8 j][128] fp32 in the
+// swizzle layout that 32-bit MN-major operands require (see make_desc_tf32).  The four row warps load E and U through registers (prefetched 4 k-steps ahead),
+// split them, store the hi/lo pieces with the swizzle, publish them to the async proxy and arrive on
+// the stage's mbarrier; warp 4 issues the MMAs and commits.  The shared-memory ring is reused for the
+// in-block U panels and the error scratch once the accumulator of the block has been read.
+// ================================================================================================
+constexpr int kTcThreads = 160;
+constexpr int kKS = 8;                              // columns j per k-step
+constexpr int kPieceBytes = kKS * kBlk * 4;         // 4 KB
+constexpr int kTcStageBytes = 4 * kPieceBytes;      // Ehi, Elo, Uhi, Ulo
+constexpr int kTcStages = 4;
+constexpr int kTcPrefetch = 4;                      // k-steps held in registers ahead of the ring
+constexpr size_t kTcSmem = (size_t)kTcStages * kTcStageBytes + 1024 + kBlk * sizeof(float) + 256;
+static_assert(kTcStages * kTcStageBytes >= 3 * kChunkFloats * (int)sizeof(float), "in-block buffers alias the ring");
+
+// Instruction descriptor: D fp32, A/B tf32, both MN-major, N = 128, M = 128.
+constexpr uint32_t kIdescTf32 = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 15) | (1u << 16) |
+                                ((128u >> 3) << 17) | ((128u >> 4) << 24);
+
+// MN-major operands of 32-bit elements must use the "128-byte swizzle with 32-byte base" layout (type 1):
+// an atom is 4 K rows of 128 bytes (32 elements along MN), inside which the 32-byte chunk index is XORed
+// with the row index.  A piece is [MN block (4)][K group (2)][4 rows][128 B]: next MN block 1 KB further
+// (leading byte offset), next group of 4 K rows 512 B further (stride byte offset).
+__device__ __forceinline__ uint64_t make_desc_tf32(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(1024 >> 4) << 16) | ((uint64_t)(512 >> 4) << 32) |
+           (1ull << 46) | (1ull << 61);
+}
+// byte offset inside a piece of the 16-byte chunk c4 (0..31 along MN) of K row j (0..7)
+__device__ __forceinline__ uint32_t piece_offset(int j, int c4) {
+    const int rr = j & 3;
+    return (uint32_t)((c4 >> 3) * 1024 + (j >> 2) * 512 + rr * 128 + (((((c4 & 7) >> 1) ^ rr)) << 5) + ((c4 & 1) << 4));
+}
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        :
+        : "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(kIdescTf32), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void rows_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+__device__ __forceinline__ float tf32_round(float v) {
+    return __uint_as_float((__float_as_uint(v) + 0x1000u) & 0xFFFFE000u);
+}
+__device__ __forceinline__ void split4(const float4 v, float4 &hi, float4 &lo) {
+    hi.x = tf32_round(v.x); hi.y = tf32_round(v.y); hi.z = tf32_round(v.z); hi.w = tf32_round(v.w);
+    lo.x = tf32_round(__fsub_rn(v.x, hi.x)); lo.y = tf32_round(__fsub_rn(v.y, hi.y));
+    lo.z = tf32_round(__fsub_rn(v.z, hi.z)); lo.w = tf32_round(__fsub_rn(v.w, hi.w));
+}
+
+template <int MODE, bool SPARSE>
+__global__ void __launch_bounds__(kTcThreads, 2) solve_tc_kernel(const SolveParams p, int32_t *status) {
+    using namespace forge::tc;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *ring = smem_raw + (smem_base - smem_u32(smem_raw));
+    float *Us = reinterpret_cast<float *>(ring);                 // [2][32][128]   (in-block phase)
+    float *es = Us + 2 * kChunkFloats;                           // [32][128]      (in-block phase)
+    float *uinv_s = reinterpret_cast<float *>(ring + kTcStages * kTcStageBytes);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(uinv_s + kBlk);  // full[4], empty[4], acc_full
+    uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + 9);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
+    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + kTcStages), bar_acc = smem_u32(bars + 8);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (int s = 0; s < kTcStages; ++s) {
+            mbar_init(bar_full + 8 * s, kBlk);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        mbar_init(bar_acc, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 4) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
+                     "r"(128u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    const int b = blockIdx.y;
+    const int u = p.u_map ? p.u_map[b] : b;
+    const int64_t R = p.R, C = p.C;
+    const int64_t r0 = (int64_t)blockIdx.x * kBlk;
+    float *Wt = p.Wt + (int64_t)b * C * R;
+    float *E = p.E + (int64_t)b * C * R;
+    const float *U = p.U + (int64_t)u * C * C;
+    uint32_t it = 0, blk_iter = 0;
+
+    if (warp < 4) {
+        const int64_t r = r0 + tid;
+        const bool active = r < R;
+        // this thread's two E chunks and two U chunks of a k-step: rows j = tid/32 and tid/32 + 4, float4 column c4
+        const int jA = tid >> 5, c4 = tid & 31;
+        const bool e_ok = (r0 + 4 * c4) < R;
+        const uint32_t sw_off[2] = {piece_offset(jA, c4), piece_offset(jA + 4, c4)};
+        bool ok = true;
+        for (int64_t bs = 0; bs < C; bs += kBlk) {
+            float x[kBlk];
+            if (bs == 0) {
+#pragma unroll
+                for (int k = 0; k < kBlk; ++k) x[k] = (active && (k < C)) ? Wt[(int64_t)k * R + r] : 0.0f;
+            } else {
+                const int nks = (int)(bs / kKS);
+                const bool u_ok = (bs + 4 * c4) < C;
+                float4 re[kTcPrefetch][2], ru[kTcPrefetch][2];
+                auto fetch = [&](int d, int ks) {
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int64_t j = (int64_t)ks * kKS + jA + 4 * h;
+                        re[d][h] = e_ok ? *reinterpret_cast<const float4 *>(E + j * R + r0 + 4 * c4)
+                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+                        ru[d][h] = u_ok ? *reinterpret_cast<const float4 *>(U + j * C + bs + 4 * c4)
+                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                };
+#pragma unroll
+                for (int d = 0; d < kTcPrefetch; ++d)
+                    if (d < nks) fetch(d, d);
+                for (int base = 0; base < nks && ok; base += kTcPrefetch) {
+#pragma unroll
+                    for (int d = 0; d < kTcPrefetch; ++d) {
+                        const int ks = base + d;
+                        if (ks < nks && ok) {
+                            const uint32_t s = it % kTcStages, ph = (it / kTcStages) & 1u;
+                            ok = mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag);
+                            if (ok) {
+                                uint8_t *stage = ring + s * kTcStageBytes;
+#pragma unroll
+                                for (int h = 0; h < 2; ++h) {
+                                    float4 hi, lo;
+                                    split4(re[d][h], hi, lo);
+                                    *reinterpret_cast<float4 *>(stage + 0 * kPieceBytes + sw_off[h]) = hi;
+                                    *reinterpret_cast<float4 *>(stage + 1 * kPieceBytes + sw_off[h]) = lo;
+                                    split4(ru[d][h], hi, lo);
+                                    *reinterpret_cast<float4 *>(stage + 2 * kPieceBytes + sw_off[h]) = hi;
+                                    *reinterpret_cast<float4 *>(stage + 3 * kPieceBytes + sw_off[h]) = lo;
+                                }
+                                fence_proxy_async();
+                                mbar_arrive(bar_full + 8 * s);
+                                ++it;
+                                if (ks + kTcPrefetch < nks) fetch(d, ks + kTcPrefetch);
+                            }
+                        }
+                    }
+                }
+                if (ok) ok = mbar_wait(bar_acc, blk_iter & 1u, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld is warp-aligned: the whole warp goes or none
+                if (ok) {
+                    tc_fence_after();
+#pragma unroll
+                    for (int qd = 0; qd < 4; ++qd) {
+                        float w[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const int64_t c = bs + qd * 32 + i;
+                            w[i] = (active && c < C) ? Wt[c * R + r] : 0.0f;
+                        }
+                        uint32_t v[32];
+                        tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(qd * 32), v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) x[qd * 32 + i] = __fsub_rn(w[i], __uint_as_float(v[i]));
+                    }
+                    tc_fence_before();
+                } else {
+#pragma unroll
+                    for (int k = 0; k < kBlk; ++k) x[k] = 0.0f;
+                }
+                ++blk_iter;
+            }
+            // Every row thread passes this barrier, whether its waits succeeded or not; a thread that gave up
+            // raised the abort flag before it, so the decision to leave is the same for all of them.
+            rows_barrier();
+            if (*abort_flag) break;
+            if (SPARSE) {
+                const int64_t c = bs + tid;
+                float v = 1.0f;
+                if (c < C) {
+                    v = p.uvec[(int64_t)u * C + c];
+                    if (p.uvec_is_diag) v = __fdiv_rn(1.0f, v);
+                }
+                uinv_s[tid] = v;
+            }
+            // in-block phase: U rows [bs+32s, +32) x cols [bs, bs+128), double buffered
+            const bool vecU = true;
+            load_chunk(Us, nullptr, U, E, C, R, bs, bs, r0, false, vecU, false, tid);
+            cp_async_commit();
+#pragma unroll
+            for (int sb = 0; sb < 4; ++sb) {
+                const int buf = sb & 1;
+                if (sb + 1 < 4) {
+                    load_chunk(Us + (buf ^ 1) * kChunkFloats, nullptr, U, E, C, R, bs + (int64_t)(sb + 1) * kSub, bs, r0,
+                               false, vecU, false, tid);
+                    cp_async_commit();
+                    cp_async_wait<1>();
+                } else {
+                    cp_async_wait<0>();
+                }
+                rows_barrier();
+                const float *us = Us + buf * kChunkFloats;
+                if (sb == 0) solve_subblock<MODE, SPARSE, 0>(x, us, es, uinv_s, p, b, u, bs, r, active, Wt, E, tid);
+                else if (sb == 1) solve_subblock<MODE, SPARSE, 1>(x, us, es, uinv_s, p, b, u, bs, r, active, Wt, E, tid);
+                else if (sb == 2) solve_subblock<MODE, SPARSE, 2>(x, us, es, uinv_s, p, b, u, bs, r, active, Wt, E, tid);
+                else solve_subblock<MODE, SPARSE, 3>(x, us, es, uinv_s, p, b, u, bs, r, active, Wt, E, tid);
+                rows_barrier();
+            }
+        }
+        cp_async_wait<0>();
+    } else {
+        bool ok = true;
+        for (int64_t bs = kBlk; bs < C && ok; bs += kBlk) {
+            const int nks = (int)(bs / kKS);
+            for (int ks = 0; ks < nks && ok; ++ks) {
+                const uint32_t s = it % kTcStages, ph = (it / kTcStages) & 1u;
+                ok = mbar_wait(bar_full + 8 * s, ph, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t st = smem_base + s * kTcStageBytes;
+                    const uint64_t ehi = make_desc_tf32(st), elo = make_desc_tf32(st + kPieceBytes);
+                    const uint64_t uhi = make_desc_tf32(st + 2 * kPieceBytes), ulo = make_desc_tf32(st + 3 * kPieceBytes);
+                    umma_tf32(tmem_base, ehi, uhi, ks > 0 ? 1u : 0u);
+                    umma_tf32(tmem_base, elo, uhi, 1u);
+                    umma_tf32(tmem_base, ehi, ulo, 1u);
+                    umma_commit(bar_empty + 8 * s);
+                }
+                __syncwarp();
+                ++it;
+            }
+            if (!ok) break;
+            if (lane == 0) umma_commit(bar_acc);
+            __syncwarp();
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && tid == 0 && status) atomicExch(status, FORGE_ERR_TIMEOUT);
+    if (warp == 4) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(128u) : "memory");
     }
 }
 
@@ -335,16 +628,31 @@ __global__ void untranspose_codes_kernel(const uint8_t *__restrict__ qt, int64_t
 
 constexpr size_t kSolveSmem = (4 * kChunkFloats + kBlk) * sizeof(float);
 
+// The tensor-core build needs 16-byte aligned float4 rows (R % 4 == 0, C % 4 == 0); otherwise, or when
+// FORGE_SOLVER_IMPL=simt is set in the environment (cross-checks), the plain-FMA build runs.
+inline bool use_tc_solver(const SolveParams &p) {
+    const char *e = getenv("FORGE_SOLVER_IMPL");
+    if (e && strcmp(e, "simt") == 0) return false;
+    return (p.R % 4 == 0) && (p.C % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.U) & 15) == 0) &&
+           ((reinterpret_cast<uintptr_t>(p.E) & 15) == 0);
+}
+
 template <int MODE, bool SPARSE>
-int launch_solve(const SolveParams &p, int nb, cudaStream_t st) {
+int launch_solve(const SolveParams &p, int nb, int32_t *status, cudaStream_t st) {
     static bool attr_done = false;
     if (!attr_done) {
         cudaFuncSetAttribute(solve_kernel<MODE, SPARSE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)kSolveSmem);
+        cudaFuncSetAttribute(solve_tc_kernel<MODE, SPARSE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)kTcSmem);
         attr_done = true;
     }
     dim3 grid((unsigned)cdiv(p.R, kBlk), (unsigned)nb);
-    solve_kernel<MODE, SPARSE><<<grid, kBlk, kSolveSmem, st>>>(p); FORGE_NOTE_LAUNCH();
+    if (use_tc_solver(p)) {
+        solve_tc_kernel<MODE, SPARSE><<<grid, kTcThreads, kTcSmem, st>>>(p, status); FORGE_NOTE_LAUNCH();
+    } else {
+        solve_kernel<MODE, SPARSE><<<grid, kBlk, kSolveSmem, st>>>(p); FORGE_NOTE_LAUNCH();
+    }
     return check_launch("forge_gptq_solve");
 }
 
@@ -358,7 +666,7 @@ extern "C" int64_t forge_solve_workspace_bytes(int nb, int64_t R, int64_t C) {
 
 extern "C" int forge_gptq_solve_cr(float *Wt, const float *U, const float *uinv, const float *scales,
                                    const float *qzeros, int bits, int64_t R, int64_t C, int sparse14, uint8_t *q,
-                                   uint32_t *M, void *ws, void *stream) {
+                                   uint32_t *M, void *ws, int32_t *status, void *stream) {
     FORGE_REQUIRE(Wt && U && scales && qzeros && q && ws, "null pointer");
     FORGE_REQUIRE(R > 0 && C > 0 && bits >= 1 && bits <= 8, "bad sizes");
     FORGE_REQUIRE(!sparse14 || (uinv && M), "sparse14 needs uinv and M");
@@ -368,13 +676,14 @@ extern "C" int forge_gptq_solve_cr(float *Wt, const float *U, const float *uinv,
     p.scales = scales; p.qzeros = qzeros; p.perm = nullptr; p.q = q; p.M = M;
     p.R = R; p.C = C; p.G = 0; p.gs = 1; p.maxq = (1 << bits) - 1; p.write_deq = 1; p.uvec_is_diag = 0;
     cudaStream_t st = (cudaStream_t)stream;
-    return sparse14 ? launch_solve<1, true>(p, 1, st) : launch_solve<1, false>(p, 1, st);
+    return sparse14 ? launch_solve<1, true>(p, 1, status, st) : launch_solve<1, false>(p, 1, status, st);
 }
 
 extern "C" int forge_gptq_solve_batched(const void *W, int w_dtype, int nb, int64_t R, int64_t C, const float *U,
                                         const float *udiag, const int32_t *u_map, const int32_t *perm, int nu,
                                         const float *scales, const float *qzeros, int gs, int bits, int sparse14,
-                                        uint8_t *qweight, uint32_t *M, void *ws, void *stream) {
+                                        uint8_t *qweight, uint32_t *M, void *ws, int32_t *status,
+                                        void *stream) {
     FORGE_REQUIRE(W && U && scales && qzeros && qweight && ws, "null pointer");
     FORGE_REQUIRE(nb > 0 && R > 0 && C > 0 && gs > 0 && bits >= 1 && bits <= 8, "bad sizes");
     FORGE_REQUIRE(!sparse14 || (udiag && M), "sparse14 needs udiag and M");
@@ -398,7 +707,7 @@ extern "C" int forge_gptq_solve_batched(const void *W, int w_dtype, int nb, int6
     p.Wt = Wt; p.E = Wt; p.U = U; p.uvec = udiag; p.u_map = u_map;
     p.scales = scales; p.qzeros = qzeros; p.perm = perm; p.q = qt; p.M = M;
     p.R = R; p.C = C; p.G = cdiv(C, gs); p.gs = gs; p.maxq = (1 << bits) - 1; p.write_deq = 0; p.uvec_is_diag = 1;
-    int rc = sparse14 ? launch_solve<0, true>(p, nb, st) : launch_solve<0, false>(p, nb, st);
+    int rc = sparse14 ? launch_solve<0, true>(p, nb, status, st) : launch_solve<0, false>(p, nb, status, st);
     if (rc != FORGE_OK) return rc;
     untranspose_codes_kernel<<<tgrid, dim3(32, 8), 0, st>>>(qt, R, C, perm_inv, u_map, qweight); FORGE_NOTE_LAUNCH();
     return check_launch("forge_gptq_solve_batched");

@@ -123,7 +123,7 @@ def quant_grid_mse(W, gs, bits, symmetric, candidates, norm, scales, qzeros):
     return scales, qzeros
 
 
-def gptq_solve_cr(Wt, U, scales_el, qzeros_el, bits: int, uinv=None):
+def gptq_solve_cr(Wt, U, scales_el, qzeros_el, bits: int, uinv=None, status=None):
     """Reference operator layout: Wt [C,R] fp32 (mutated -> dequantised), per-element scales [C,R]."""
     C, R = Wt.shape
     dev = _dev(Wt)
@@ -132,12 +132,12 @@ def gptq_solve_cr(Wt, U, scales_el, qzeros_el, bits: int, uinv=None):
     M = torch.zeros(((C + 31) // 32, R), dtype=torch.int32, device=dev) if sparse else None
     ws = torch.empty(query("forge_solve_workspace_bytes", 1, R, C), dtype=torch.uint8, device=dev)
     call("forge_gptq_solve_cr", ptr(Wt), ptr(U), ptr(uinv), ptr(scales_el), ptr(qzeros_el), bits, R, C, int(sparse),
-         ptr(q), ptr(M), ptr(ws), stream_ptr())
+         ptr(q), ptr(M), ptr(ws), ptr(status), stream_ptr())
     return (q, M) if sparse else q
 
 
 def gptq_solve_batched(W, U, scales, qzeros, gs: int, bits: int, perm=None, u_map=None, udiag=None,
-                       sparse14: bool = False, ws=None):
+                       sparse14: bool = False, ws=None, status=None):
     """W [nb,R,C] original order; U [nu,C,C]; scales/qzeros [nb*R*G] -> qweight [nb,R,C] (+ M [nb,G32,R])."""
     nb, R, C = W.shape
     dev = _dev(W)
@@ -147,7 +147,7 @@ def gptq_solve_batched(W, U, scales, qzeros, gs: int, bits: int, perm=None, u_ma
     if ws is None:
         ws = torch.empty(query("forge_solve_workspace_bytes", nb, R, C), dtype=torch.uint8, device=dev)
     call("forge_gptq_solve_batched", ptr(W), dtype_code(W), nb, R, C, ptr(U), ptr(udiag), ptr(u_map), ptr(perm), nu,
-         ptr(scales), ptr(qzeros), gs, bits, int(sparse14), ptr(q), ptr(M), ptr(ws), stream_ptr())
+         ptr(scales), ptr(qzeros), gs, bits, int(sparse14), ptr(q), ptr(M), ptr(ws), ptr(status), stream_ptr())
     return (q, M) if sparse14 else q
 
 

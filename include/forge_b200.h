@@ -148,12 +148,15 @@ int forge_quant_grid_mse(const void *W, int w_dtype, int64_t rows, int64_t C, in
  * unit-diagonal upper, scales/qzeros per ELEMENT [C,R]; writes codes q [C,R] uint8, overwrites Wt with
  * the de-quantised weights; sparse14 != 0 selects the SparseGPT 1:4 variant (uinv [C] = 1/diag of the
  * un-normalised factor; M [ceil(C/32),R] uint32 keep-mask).  ws: forge_solve_workspace_bytes(1,R,C).
+ * `status` (device int32, may be NULL) receives FORGE_ERR_TIMEOUT if a bounded wait of the tensor-core
+ * build ran out.  With R % 4 == 0 and C % 4 == 0 the lazy update runs on tcgen05 (TF32 x3 split, fp32
+ * accumulate in TMEM), otherwise on the FMA pipe; FORGE_SOLVER_IMPL=simt in the environment forces the latter.
  * Replaces kernels.gptq_solver (forge/backend/cuda/solver.cu:99-154) and kernels.sparsegptq14_solver
  * (forge/backend/cuda/solver_sparsegptq14.cu:142-200). */
 int64_t forge_solve_workspace_bytes(int nb, int64_t R, int64_t C);
 int forge_gptq_solve_cr(float *Wt, const float *U, const float *uinv, const float *scales,
                         const float *qzeros, int bits, int64_t R, int64_t C, int sparse14,
-                        uint8_t *q, uint32_t *M, void *ws, void *stream);
+                        uint8_t *q, uint32_t *M, void *ws, int32_t *status, void *stream);
 
 /* forge_gptq_solve_batched is the batched fast path: nb weights W[b] [R,C] (bf16 or fp32) in ORIGINAL
  * column order, solved against U[u_map[b]] (u_map NULL = b) with per-GROUP scales/qzeros [nb,R,G]
@@ -165,7 +168,7 @@ int forge_gptq_solve_cr(float *Wt, const float *U, const float *uinv, const floa
 int forge_gptq_solve_batched(const void *W, int w_dtype, int nb, int64_t R, int64_t C, const float *U,
                              const float *udiag, const int32_t *u_map, const int32_t *perm, int nu,
                              const float *scales, const float *qzeros, int gs, int bits, int sparse14,
-                             uint8_t *qweight, uint32_t *M, void *ws, void *stream);
+                             uint8_t *qweight, uint32_t *M, void *ws, int32_t *status, void *stream);
 
 /* ---- A12: de-quantise codes ------------------------------------------------
  * out[r,c] = dtype( (q[r,c] - qzeros[r,c/gs]) * scales[r,c/gs] )   (fp32 arithmetic)
