@@ -38,6 +38,8 @@ _PROTOS = {
     "forge_hessian_gather_damp": (_c_int, [_ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _c_f32, _ptr, _ptr, _ptr, _ptr]),
     "forge_chol_workspace_bytes": (_c_i64, [_c_int, _c_i64]),
     "forge_chol_inv_upper_batched": (_c_int, [_ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr]),
+    "forge_noalloc_max_c": (_c_i64, []),
+    "forge_chol_inv_upper_noalloc": (_c_int, [_ptr, _c_i64, _ptr, _ptr, _ptr, _c_int, _ptr]),
     "forge_quant_grid": (_c_int, [_ptr, _c_int, _c_i64, _c_i64, _c_int, _c_int, _c_int, _ptr, _c_int, _c_f32, _ptr, _ptr, _ptr]),
     "forge_quant_grid_mse": (_c_int, [_ptr, _c_int, _c_i64, _c_i64, _c_int, _c_int, _c_int, _ptr, _c_int, _c_f32, _ptr, _ptr, _ptr]),
     "forge_solve_workspace_bytes": (_c_i64, [_c_int, _c_i64, _c_i64]),

@@ -128,6 +128,20 @@ int64_t forge_chol_workspace_bytes(int nb, int64_t C);
 int forge_chol_inv_upper_batched(float *A, int nb, int64_t C, float *U, float *udiag, int32_t *info,
                                  int zero_lower, void *ws, void *stream);
 
+/* Allocation-free variant for ONE matrix; it has no counterpart in the reference.
+ * Same result as forge_chol_inv_upper_batched(A, 1, C, ...), but the workspace is a 2 MiB array that
+ * lives inside the library on every GPU that loads it, for callers that cannot obtain device memory
+ * when they need a factorisation: a layer driver that has already given all of HBM to its Hessian
+ * batches and must redo one expert (info > 0) with a larger damping, or a host application whose memory
+ * manager forbids cudaMalloc (which would also stall its other streams).
+ * C <= forge_noalloc_max_c() (4096), else FORGE_ERR_UNSUPPORTED.  The first call on a device looks up the
+ * array's address (cudaGetSymbolAddress): make that call outside of stream capture.  All calls on a device
+ * share the array, so calls that overlap on the GPU (different streams) race; calls on one stream are safe,
+ * and nothing in the array needs clearing between calls. */
+int64_t forge_noalloc_max_c(void);
+int forge_chol_inv_upper_noalloc(float *A, int64_t C, float *U, float *udiag, int32_t *info,
+                                 int zero_lower, void *stream);
+
 /* ---- A5/A6: per-group scale / zero grid -----------------------------------
  * W [nb*R, C] (bf16 or fp32, row-major, groups of gs consecutive columns, the last one zero padded).
  * scales,qzeros [nb*R*G] fp32.  symmetric: s = 2/maxq*max|w| + 1e-12, q0 = (maxq+1)/2;  else
