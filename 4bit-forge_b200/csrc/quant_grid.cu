@@ -137,11 +137,196 @@ quant_grid_kernel(const void *__restrict__ Wv, int64_t rows, int64_t C, int64_t 
     }
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Shrink-factor search, second layout: one THREAD per (group, candidate pair) instead of one warp per
+// group.  The per-candidate set-up (scale, reciprocal, zero) is then paid once per 128 elements instead
+// of once per 4, and no shuffle is needed: the thread reproduces the reference warp's summation order
+// by itself — 32 "lane" partial sums, each the in-order sum of elements l, l+32, ..., then the
+// shfl_down tree (offsets 16, 8, 4, 2, 1) over those 32 numbers.  The group's values sit in shared
+// memory as [l][i] so that one broadcast LDS.128 feeds four elements of every thread of the group.
+// The per-element arithmetic is the reference's (fma, round-half-even, clamp, fma, |.|^norm through
+// lg2/ex2 approximations); the search is bound by the two MUFU operations per element-candidate.
+// ------------------------------------------------------------------------------------------------
+constexpr int kMseThreads = 256;
+constexpr int kMseCPT = 2;        // candidates per thread
+constexpr int kMseMaxGroups = 8;  // groups per CTA pass
+
+__device__ __forceinline__ float fast_lg2(float x) {
+    float y;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float fast_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <int GS, bool BF16, bool ABSMAX>
+__global__ void __launch_bounds__(kMseThreads, 2)
+mse_grid_kernel(const void *__restrict__ Wv, int64_t rows, int64_t C, int64_t G, int bits, int symmetric,
+                const float *__restrict__ cand, int P, float norm, float *__restrict__ scales,
+                float *__restrict__ qzeros, int tpg, int gpc) {
+    constexpr int VPL = GS / 32;
+    __shared__ __align__(16) float vals_s[kMseMaxGroups][32 * VPL];   // [group][l][i]
+    __shared__ float meta_s[kMseMaxGroups][2];
+    __shared__ float loss_s[kMseMaxGroups][kMseThreads];              // per candidate (P <= 256)
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float maxq = (float)((1 << bits) - 1);
+    const int64_t n_groups = rows * G;
+    const float kMagic = 12582912.0f;  // 1.5 * 2^23: adding it rounds to the nearest integer, ties to even
+
+    for (int64_t g0 = (int64_t)blockIdx.x * gpc; g0 < n_groups; g0 += (int64_t)gridDim.x * gpc) {
+        // ---- stage the values of this pass's groups, element e of a group at [e % 32][e / 32]
+        for (int idx = tid; idx < gpc * GS; idx += kMseThreads) {
+            const int gl = idx / GS, e = idx % GS;
+            const int64_t g = g0 + gl;
+            float x = 0.0f;
+            if (g < n_groups) {
+                const int64_t r = g / G, c = (g % G) * GS + e;
+                if (c < C) {
+                    x = BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(Wv)[r * C + c])
+                             : reinterpret_cast<const float *>(Wv)[r * C + c];
+                }
+            }
+            vals_s[gl][(e & 31) * VPL + (e >> 5)] = x;
+        }
+        __syncthreads();
+        // ---- min-max scale / zero of each group (one warp per group)
+        if (warp < gpc) {
+            const int64_t g = g0 + warp;
+            float sg = 1.0f, q0g = 0.0f;
+            if (g < n_groups) {
+                if (ABSMAX) {
+                    float mn = 1e30f, mx = -1e30f;
+#pragma unroll
+                    for (int i = 0; i < VPL; ++i) {
+                        const float x = vals_s[warp][lane * VPL + i];
+                        mx = fmaxf(mx, x);
+                        mn = fminf(mn, x);
+                    }
+                    mx = warp_max(mx);
+                    mn = warp_min(mn);
+                    if (symmetric) {
+                        sg = fmaf(2.0f / maxq, fmaxf(fabsf(mn), fabsf(mx)), kEps);
+                        q0g = 0.5f * (maxq + 1.0f);
+                    } else {
+                        sg = __fadd_rn(__fdiv_rn(__fsub_rn(mx, mn), maxq), kEps);
+                        q0g = fminf(fmaxf(rintf(__fdiv_rn(-mn, sg)), 0.0f), maxq);
+                    }
+                } else {
+                    sg = scales[g];
+                    q0g = qzeros[g];
+                }
+            }
+            if (lane == 0) { meta_s[warp][0] = sg; meta_s[warp][1] = q0g; }
+        }
+        __syncthreads();
+        // ---- one thread per (group, candidate pair)
+        const int gl = tid / tpg, jt = tid % tpg;
+        if (gl < gpc && g0 + gl < n_groups) {
+            const float sg = meta_s[gl][0], q0g = meta_s[gl][1];
+            const float xmin = symmetric ? 0.0f : -__fmul_rn(sg, q0g);
+            float sc[kMseCPT], rcp[kMseCPT], q0[kMseCPT], hiq[kMseCPT], offq[kMseCPT];
+#pragma unroll
+            for (int c = 0; c < kMseCPT; ++c) {
+                const int p = min(jt + c * tpg, P - 1);
+                sc[c] = __fmul_rn(sg, cand[p]);
+                rcp[c] = __fdiv_rn(1.0f, __fadd_rn(sc[c], kEps));
+                q0[c] = symmetric ? q0g : fminf(fmaxf(rintf(__fmul_rn(-xmin, rcp[c])), 0.0f), maxq);
+                hiq[c] = kMagic + maxq;       // clamp bounds and zero in the "magic" domain (all exact integers)
+                offq[c] = kMagic + q0[c];
+            }
+            float a[kMseCPT][32];
+            const float4 *v4 = reinterpret_cast<const float4 *>(&vals_s[gl][0]);
+#pragma unroll
+            for (int l = 0; l < 32; ++l) {
+                float v[4];
+                if (VPL == 4) {
+                    const float4 t = v4[l];
+                    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < VPL; ++i) v[i] = vals_s[gl][l * VPL + i];
+                }
+#pragma unroll
+                for (int c = 0; c < kMseCPT; ++c) {
+                    float acc = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < VPL; ++i) {
+                        // q = clamp(rint(v*rcp + q0), 0, maxq), carried as q + magic
+                        float t = __fadd_rn(fmaf(v[i], rcp[c], q0[c]), kMagic);
+                        t = fminf(fmaxf(t, kMagic), hiq[c]);
+                        const float diff = fmaf(__fsub_rn(t, offq[c]), sc[c], -v[i]);
+                        const float e = fmaxf(fabsf(diff), 1e-20f);
+                        const float lg = __fmul_rn(fast_lg2(e), 0.693147182f);                  // __logf
+                        const float val = fast_ex2(__fmul_rn(__fmul_rn(lg, norm), 1.44269502f));  // __expf
+                        acc = __fadd_rn(acc, val);
+                    }
+                    a[c][l] = acc;
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < kMseCPT; ++c) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                    for (int l = 0; l < o; ++l) a[c][l] = __fadd_rn(a[c][l], a[c][l + o]);
+                const int p = jt + c * tpg;
+                if (p < P) loss_s[gl][p] = a[c][0];
+            }
+        }
+        __syncthreads();
+        // ---- first strictly smaller loss in candidate order wins
+        if (tid < gpc && g0 + tid < n_groups) {
+            const float sg = meta_s[tid][0], q0g = meta_s[tid][1];
+            float best = FLT_MAX;
+            int bp = -1;
+            for (int p = 0; p < P; ++p) {
+                const float l = loss_s[tid][p];
+                if (l < best) { best = l; bp = p; }
+            }
+            float bs = sg, bq = q0g;
+            if (bp >= 0) {
+                bs = __fmul_rn(sg, cand[bp]);
+                if (!symmetric) {
+                    const float xmin = -__fmul_rn(sg, q0g);
+                    const float rc = __fdiv_rn(1.0f, __fadd_rn(bs, kEps));
+                    bq = fminf(fmaxf(rintf(__fmul_rn(-xmin, rc)), 0.0f), maxq);
+                }
+            }
+            scales[g0 + tid] = bs;
+            qzeros[g0 + tid] = bq;
+        }
+        __syncthreads();
+    }
+}
+
 template <bool ABSMAX>
 int launch_grid(const void *W, int w_dtype, int64_t rows, int64_t C, int gs, int bits, int symmetric,
                 const float *cand, int n_cand, float norm, float *scales, float *qzeros, cudaStream_t st) {
     const int64_t G = cdiv(C, gs);
     const int64_t n_groups = rows * G;
+    if (n_cand > 0 && n_cand <= kMseThreads && (gs == 32 || gs == 64 || gs == 128)) {
+        const int tpg = (n_cand + kMseCPT - 1) / kMseCPT;                 // threads per group
+        int gpc = kMseThreads / tpg;                                       // groups per CTA pass
+        if (gpc > kMseMaxGroups) gpc = kMseMaxGroups;
+        const int blocks = (int)imin64(cdiv(n_groups, gpc), 148 * 2 * 8);
+        const bool bf = (w_dtype == FORGE_DTYPE_BF16);
+#define FORGE_LAUNCH_MSE(GSV)                                                                                  \
+        do {                                                                                                   \
+            if (bf) { mse_grid_kernel<GSV, true, ABSMAX><<<blocks, kMseThreads, 0, st>>>(                      \
+                        W, rows, C, G, bits, symmetric, cand, n_cand, norm, scales, qzeros, tpg, gpc); FORGE_NOTE_LAUNCH(); } \
+            else { mse_grid_kernel<GSV, false, ABSMAX><<<blocks, kMseThreads, 0, st>>>(                        \
+                        W, rows, C, G, bits, symmetric, cand, n_cand, norm, scales, qzeros, tpg, gpc); FORGE_NOTE_LAUNCH(); } \
+        } while (0)
+        if (gs == 32) FORGE_LAUNCH_MSE(32);
+        else if (gs == 64) FORGE_LAUNCH_MSE(64);
+        else FORGE_LAUNCH_MSE(128);
+#undef FORGE_LAUNCH_MSE
+        return check_launch("forge_quant_grid(mse)");
+    }
     const int threads = 256;  // 8 groups per CTA pass
     const int64_t want = cdiv(n_groups, threads / 32);
     const int blocks = (int)imin64(want, 148 * 8);

@@ -304,34 +304,42 @@ __global__ void __launch_bounds__(128, 3) solve_kernel(const SolveParams p) {
 
 
 // ================================================================================================
-// Tensor-core build of the same solver: the lazy update  acc[r, k] = sum_{j<bs} E[j, r] * U[j, bs+k]
-// runs on tcgen05 as a  M=128 (rows) x N=128 (block columns) x K=8  TF32 GEMM per k-step with the fp32
-// accumulator in 128 TMEM columns, so that one TMEM lane is one weight row and tcgen05.ld hands every
-// row-thread its 128 values in registers — the layout the sequential in-block phase wants.
+// Tensor-core build of the same solver.  Every update of a not-yet-solved column by the errors of an
+// earlier column,  x[r, k] -= err[j, r] * U[j, k],  that crosses a 32-column sub-block boundary runs on
+// tcgen05 as a  M=128 (rows) x N (columns) x K=8  TF32 GEMM per k-step, accumulated in 128 TMEM columns
+// (one TMEM lane = one weight row).  Per 128-column block:
+//   far   : acc[:, 0:128]   = sum_{j < bs}           err_j U[j, bs:bs+128]       (bs/8 k-steps, N = 128)
+//   near s: acc[:, 32s:128] += sum_{j in sub-block s-1} err_j U[j, bs+32s:bs+128]  (4 k-steps, N = 128-32s)
+// and a row-thread only ever holds the 32 values of the sub-block it is solving:
+//   x[0:32] = W[:, sub-block] - tcgen05.ld(acc[:, 32s:32s+32]), then the sequential in-register solve with
+//   the 32x32 triangle of U from shared memory.  Nothing but that triangle is left on the FMA pipe.
 //
 // fp32 fidelity: an operand v is split as  hi = tf32(v) (round to nearest on the bit pattern),
 // lo = tf32(v - hi);  acc += Ehi*Uhi + Elo*Uhi + Ehi*Ulo  (three MMAs per k-step).  The dropped Elo*Ulo
 // term and the truncation of lo are ~2^-21 relative, the size of fp32 rounding in a dot product.
 //
-// Both operands are "MN-major": E is [C][R] with the 128 rows of the strip contiguous, the U panel is
-// [j][bs..bs+128) with the block columns contiguous.  A k-step piece is [8 j][128] fp32 in the
-// swizzle layout that 32-bit MN-major operands require (see make_desc_tf32).  The four row warps load E and U through registers (prefetched 4 k-steps ahead),
-// split them, store the hi/lo pieces with the swizzle, publish them to the async proxy and arrive on
-// the stage's mbarrier; warp 4 issues the MMAs and commits.  The shared-memory ring is reused for the
-// in-block U panels and the error scratch once the accumulator of the block has been read.
+// Both operands are "MN-major": the errors are [j][r] with the 128 rows of the strip contiguous, the U
+// panel is [j][bs..bs+128) with the block columns contiguous.  A k-step piece is [8 j][128] fp32 in the
+// swizzle layout that 32-bit MN-major operands require (see make_desc_tf32).  The four row warps are the
+// producers: far k-steps load E and U from global memory through registers (prefetched 4 k-steps ahead),
+// near k-steps take the errors straight from the registers that just produced them; the hi/lo pieces are
+// stored with the swizzle, published to the async proxy, and the stage's mbarrier is arrived on.  Warp 4
+// issues the MMAs and commits.  Every wait is bounded; a CTA that gives up sets the status word.
 // ================================================================================================
 constexpr int kTcThreads = 160;
 constexpr int kKS = 8;                              // columns j per k-step
 constexpr int kPieceBytes = kKS * kBlk * 4;         // 4 KB
 constexpr int kTcStageBytes = 4 * kPieceBytes;      // Ehi, Elo, Uhi, Ulo
 constexpr int kTcStages = 4;
-constexpr int kTcPrefetch = 4;                      // k-steps held in registers ahead of the ring
-constexpr size_t kTcSmem = (size_t)kTcStages * kTcStageBytes + 1024 + kBlk * sizeof(float) + 256;
-static_assert(kTcStages * kTcStageBytes >= 3 * kChunkFloats * (int)sizeof(float), "in-block buffers alias the ring");
+constexpr int kTcPrefetch = 4;                      // far k-steps held in registers ahead of the ring
+constexpr int kUsubFloats = kSub * kSub;            // 32x32 triangle of the sub-block
+constexpr size_t kTcSmem = (size_t)kTcStages * kTcStageBytes + 1024 + 2 * kUsubFloats * sizeof(float) +
+                           kBlk * sizeof(float) + 256;
 
-// Instruction descriptor: D fp32, A/B tf32, both MN-major, N = 128, M = 128.
-constexpr uint32_t kIdescTf32 = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 15) | (1u << 16) |
-                                ((128u >> 3) << 17) | ((128u >> 4) << 24);
+// Instruction descriptor: D fp32, A/B tf32, both MN-major, M = 128, N given.
+__device__ __forceinline__ uint32_t idesc_tf32(uint32_t n) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | (1u << 15) | (1u << 16) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+}
 
 // MN-major operands of 32-bit elements must use the "128-byte swizzle with 32-byte base" layout (type 1):
 // an atom is 4 K rows of 128 bytes (32 elements along MN), inside which the 32-byte chunk index is XORed
@@ -346,13 +354,14 @@ __device__ __forceinline__ uint32_t piece_offset(int j, int c4) {
     const int rr = j & 3;
     return (uint32_t)((c4 >> 3) * 1024 + (j >> 2) * 512 + rr * 128 + (((((c4 & 7) >> 1) ^ rr)) << 5) + ((c4 & 1) << 4));
 }
-__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
         :
-        : "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(kIdescTf32), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
         : "memory");
 }
 __device__ __forceinline__ void rows_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
@@ -367,15 +376,14 @@ __device__ __forceinline__ void split4(const float4 v, float4 &hi, float4 &lo) {
 }
 
 template <int MODE, bool SPARSE>
-__global__ void __launch_bounds__(kTcThreads, 2) solve_tc_kernel(const SolveParams p, int32_t *status) {
+__global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolveParams p, int32_t *status) {
     using namespace forge::tc;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *ring = smem_raw + (smem_base - smem_u32(smem_raw));
-    float *Us = reinterpret_cast<float *>(ring);                 // [2][32][128]   (in-block phase)
-    float *es = Us + 2 * kChunkFloats;                           // [32][128]      (in-block phase)
-    float *uinv_s = reinterpret_cast<float *>(ring + kTcStages * kTcStageBytes);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(uinv_s + kBlk);  // full[4], empty[4], acc_full
+    float *Usub = reinterpret_cast<float *>(ring + kTcStages * kTcStageBytes);  // [2][32][32]
+    float *uinv_s = Usub + 2 * kUsubFloats;                                      // [128]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(uinv_s + kBlk);                // full[4], empty[4], acc
     uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + 9);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
     const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + kTcStages), bar_acc = smem_u32(bars + 8);
@@ -408,38 +416,41 @@ __global__ void __launch_bounds__(kTcThreads, 2) solve_tc_kernel(const SolvePara
     float *Wt = p.Wt + (int64_t)b * C * R;
     float *E = p.E + (int64_t)b * C * R;
     const float *U = p.U + (int64_t)u * C * C;
-    uint32_t it = 0, blk_iter = 0;
+    uint32_t it = 0;       // k-steps pushed through the ring (same sequence in both roles)
+    uint32_t acc_it = 0;   // accumulator hand-overs (commits by warp 4 / waits by the row warps)
 
     if (warp < 4) {
         const int64_t r = r0 + tid;
         const bool active = r < R;
-        // this thread's two E chunks and two U chunks of a k-step: rows j = tid/32 and tid/32 + 4, float4 column c4
+        const float maxq = (float)p.maxq;
+        // float4 slots of this thread inside a [8 j][128] piece: rows j = tid/32 and tid/32 + 4, chunk c4
         const int jA = tid >> 5, c4 = tid & 31;
         const bool e_ok = (r0 + 4 * c4) < R;
         const uint32_t sw_off[2] = {piece_offset(jA, c4), piece_offset(jA + 4, c4)};
+        // scalar slot of this thread's own row in an error piece, for K row jj: piece_offset(jj, tid/4) + (tid%4)*4
+        const bool uniform_meta = (MODE == 0) && (p.perm == nullptr) && (p.gs % kSub == 0);
         bool ok = true;
+        float e32[kSub];
+#pragma unroll
+        for (int i = 0; i < kSub; ++i) e32[i] = 0.0f;
+
         for (int64_t bs = 0; bs < C; bs += kBlk) {
-            float x[kBlk];
-            if (bs == 0) {
-#pragma unroll
-                for (int k = 0; k < kBlk; ++k) x[k] = (active && (k < C)) ? Wt[(int64_t)k * R + r] : 0.0f;
-            } else {
+            const bool u_ok = (bs + 4 * c4) < C;
+            // ---------------- far phase: every column before the block ----------------
+            if (bs > 0 && ok) {
                 const int nks = (int)(bs / kKS);
-                const bool u_ok = (bs + 4 * c4) < C;
                 float4 re[kTcPrefetch][2], ru[kTcPrefetch][2];
-                auto fetch = [&](int d, int ks) {
 #pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        const int64_t j = (int64_t)ks * kKS + jA + 4 * h;
-                        re[d][h] = e_ok ? *reinterpret_cast<const float4 *>(E + j * R + r0 + 4 * c4)
-                                        : make_float4(0.f, 0.f, 0.f, 0.f);
-                        ru[d][h] = u_ok ? *reinterpret_cast<const float4 *>(U + j * C + bs + 4 * c4)
-                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int d = 0; d < kTcPrefetch; ++d) {
+                    if (d < nks) {
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const int64_t j = (int64_t)d * kKS + jA + 4 * h;
+                            re[d][h] = e_ok ? *reinterpret_cast<const float4 *>(E + j * R + r0 + 4 * c4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                            ru[d][h] = u_ok ? *reinterpret_cast<const float4 *>(U + j * C + bs + 4 * c4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
                     }
-                };
-#pragma unroll
-                for (int d = 0; d < kTcPrefetch; ++d)
-                    if (d < nks) fetch(d, d);
+                }
                 for (int base = 0; base < nks && ok; base += kTcPrefetch) {
 #pragma unroll
                     for (int d = 0; d < kTcPrefetch; ++d) {
@@ -462,40 +473,19 @@ __global__ void __launch_bounds__(kTcThreads, 2) solve_tc_kernel(const SolvePara
                                 fence_proxy_async();
                                 mbar_arrive(bar_full + 8 * s);
                                 ++it;
-                                if (ks + kTcPrefetch < nks) fetch(d, ks + kTcPrefetch);
+                                if (ks + kTcPrefetch < nks) {
+#pragma unroll
+                                    for (int h = 0; h < 2; ++h) {
+                                        const int64_t j = (int64_t)(ks + kTcPrefetch) * kKS + jA + 4 * h;
+                                        re[d][h] = e_ok ? *reinterpret_cast<const float4 *>(E + j * R + r0 + 4 * c4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                                        ru[d][h] = u_ok ? *reinterpret_cast<const float4 *>(U + j * C + bs + 4 * c4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                                    }
+                                }
                             }
                         }
                     }
                 }
-                if (ok) ok = mbar_wait(bar_acc, blk_iter & 1u, abort_flag);
-                ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld is warp-aligned: the whole warp goes or none
-                if (ok) {
-                    tc_fence_after();
-#pragma unroll
-                    for (int qd = 0; qd < 4; ++qd) {
-                        float w[32];
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            const int64_t c = bs + qd * 32 + i;
-                            w[i] = (active && c < C) ? Wt[c * R + r] : 0.0f;
-                        }
-                        uint32_t v[32];
-                        tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(qd * 32), v);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) x[qd * 32 + i] = __fsub_rn(w[i], __uint_as_float(v[i]));
-                    }
-                    tc_fence_before();
-                } else {
-#pragma unroll
-                    for (int k = 0; k < kBlk; ++k) x[k] = 0.0f;
-                }
-                ++blk_iter;
             }
-            // Every row thread passes this barrier, whether its waits succeeded or not; a thread that gave up
-            // raised the abort flag before it, so the decision to leave is the same for all of them.
-            rows_barrier();
-            if (*abort_flag) break;
             if (SPARSE) {
                 const int64_t c = bs + tid;
                 float v = 1.0f;
@@ -503,57 +493,201 @@ __global__ void __launch_bounds__(kTcThreads, 2) solve_tc_kernel(const SolvePara
                     v = p.uvec[(int64_t)u * C + c];
                     if (p.uvec_is_diag) v = __fdiv_rn(1.0f, v);
                 }
-                uinv_s[tid] = v;
+                uinv_s[tid] = v;   // read after the next rows_barrier
             }
-            // in-block phase: U rows [bs+32s, +32) x cols [bs, bs+128), double buffered
-            const bool vecU = true;
-            load_chunk(Us, nullptr, U, E, C, R, bs, bs, r0, false, vecU, false, tid);
-            cp_async_commit();
-#pragma unroll
+            // ---------------- the four sub-blocks ----------------
+#pragma unroll 1
             for (int sb = 0; sb < 4; ++sb) {
-                const int buf = sb & 1;
-                if (sb + 1 < 4) {
-                    load_chunk(Us + (buf ^ 1) * kChunkFloats, nullptr, U, E, C, R, bs + (int64_t)(sb + 1) * kSub, bs, r0,
-                               false, vecU, false, tid);
-                    cp_async_commit();
-                    cp_async_wait<1>();
-                } else {
-                    cp_async_wait<0>();
+                const int64_t cs = bs + (int64_t)sb * kSub;
+                float *us = Usub + (sb & 1) * kUsubFloats;
+                // (1) the 32x32 triangle U[cs.., cs..] for the in-register part: 256 float4, two per thread
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const int v = tid + 128 * i;
+                    const int jj = v >> 3, k = (v & 7) * 4;
+                    const bool okl = (cs + jj < C) && (cs + k < C);
+                    cp_async16(us + jj * kSub + k, okl ? (U + (cs + jj) * C + cs + k) : U, okl);
                 }
+                cp_async_commit();
+                // (2) near update: the previous sub-block's errors go to the later columns of the block
+                if (sb > 0 && ok) {
+                    float4 nu[4][2];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const int64_t j = cs - kSub + i * kKS + jA + 4 * h;
+                            nu[i][h] = (u_ok && j < C) ? *reinterpret_cast<const float4 *>(U + j * C + bs + 4 * c4)
+                                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        if (ok) {
+                            const uint32_t s = it % kTcStages, ph = (it / kTcStages) & 1u;
+                            ok = mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag);
+                            if (ok) {
+                                uint8_t *stage = ring + s * kTcStageBytes;
+#pragma unroll
+                                for (int jj = 0; jj < kKS; ++jj) {
+                                    const float v = e32[i * kKS + jj];
+                                    const float hi = tf32_round(v);
+                                    const float lo = tf32_round(__fsub_rn(v, hi));
+                                    const uint32_t off = piece_offset(jj, tid >> 2) + ((tid & 3) << 2);
+                                    *reinterpret_cast<float *>(stage + 0 * kPieceBytes + off) = hi;
+                                    *reinterpret_cast<float *>(stage + 1 * kPieceBytes + off) = lo;
+                                }
+#pragma unroll
+                                for (int h = 0; h < 2; ++h) {
+                                    float4 hi, lo;
+                                    split4(nu[i][h], hi, lo);
+                                    *reinterpret_cast<float4 *>(stage + 2 * kPieceBytes + sw_off[h]) = hi;
+                                    *reinterpret_cast<float4 *>(stage + 3 * kPieceBytes + sw_off[h]) = lo;
+                                }
+                                fence_proxy_async();
+                                mbar_arrive(bar_full + 8 * s);
+                                ++it;
+                            }
+                        }
+                    }
+                }
+                // (3) x = W - acc for the 32 columns of this sub-block
+                float x[kSub];
+#pragma unroll
+                for (int i = 0; i < kSub; ++i) x[i] = (active && (cs + i < C)) ? Wt[(cs + i) * R + r] : 0.0f;
+                if (bs > 0 || sb > 0) {
+                    if (ok) ok = mbar_wait(bar_acc, acc_it & 1u, abort_flag);
+                    ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld is warp-aligned: the whole warp goes or none
+                    if (ok) {
+                        tc_fence_after();
+                        uint32_t v[32];
+                        tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(sb * kSub), v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < kSub; ++i) x[i] = __fsub_rn(x[i], __uint_as_float(v[i]));
+                        tc_fence_before();
+                    }
+                    ++acc_it;
+                }
+                // (4) every row thread passes here, whether its waits succeeded or not; a thread that gave up
+                // raised the abort flag before, so all of them leave together
+                cp_async_wait<0>();
                 rows_barrier();
-                const float *us = Us + buf * kChunkFloats;
-                if (sb == 0) solve_subblock<MODE, SPARSE, 0>(x, us, es, uinv_s, p, b, u, bs, r, active, Wt, E, tid);
-                else if (sb == 1) solve_subblock<MODE, SPARSE, 1>(x, us, es, uinv_s, p, b, u, bs, r, active, Wt, E, tid);
-                else if (sb == 2) solve_subblock<MODE, SPARSE, 2>(x, us, es, uinv_s, p, b, u, bs, r, active, Wt, E, tid);
-                else solve_subblock<MODE, SPARSE, 3>(x, us, es, uinv_s, p, b, u, bs, r, active, Wt, E, tid);
-                rows_barrier();
+                if (*abort_flag) break;
+                // (5) sequential solve of the 32 columns
+                uint32_t maskbits = 0u;
+                float s_nx, q0_nx;
+                load_meta<MODE>(p, b, u, r, cs, active, s_nx, q0_nx);
+                uint8_t *qp = p.q + ((int64_t)b * C + cs) * R + r;
+                float *ep = E + cs * R + r;
+                float *wp = Wt + cs * R + r;
+#pragma unroll
+                for (int t = 0; t < kSub; ++t) {
+                    asm volatile("" ::: "memory");  // keep later columns' loads from being hoisted up here
+                    const int64_t c = cs + t;
+                    const float sc = s_nx, q0 = q0_nx;
+                    if (!uniform_meta && t + 1 < kSub) load_meta<MODE>(p, b, u, r, c + 1, active, s_nx, q0_nx);
+                    float err = 0.0f;
+                    if (c < C) {
+                        if (SPARSE && (t % 4 == 0)) {
+                            float best = -1e30f;
+                            int bidx = -1;
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                if (active && (c + k < C)) {
+                                    const float sv = fabsf(__fmul_rn(x[t + k], uinv_s[sb * kSub + t + k]));
+                                    if (best < sv) { best = sv; bidx = k; }
+                                }
+                            }
+                            if (bidx > -1) maskbits |= (1u << (t + bidx));
+                        }
+                        float deq = 0.0f;
+                        uint8_t qb = 0;
+                        const bool keep = SPARSE ? (((maskbits >> t) & 1u) != 0u) : true;
+                        if (keep && (active || !SPARSE)) quantize_scalar(x[t], sc, q0, maxq, err, deq, qb);
+                        else err = x[t];
+                        if (active) {
+                            *qp = qb;
+                            if (p.write_deq) *wp = deq;
+                            *ep = err;
+                        }
+                    }
+                    qp += R; ep += R; wp += R;
+                    asm volatile("" : "+l"(qp), "+l"(ep), "+l"(wp));
+                    e32[t] = err;
+                    const float4 *urow = reinterpret_cast<const float4 *>(us + t * kSub);
+#pragma unroll
+                    for (int k4 = 0; k4 < kSub / 4; ++k4) {
+                        if (4 * k4 + 3 > t) {
+                            const float4 u4 = urow[k4];
+                            if (4 * k4 + 0 > t) x[4 * k4 + 0] = fmaf(-u4.x, err, x[4 * k4 + 0]);
+                            if (4 * k4 + 1 > t) x[4 * k4 + 1] = fmaf(-u4.y, err, x[4 * k4 + 1]);
+                            if (4 * k4 + 2 > t) x[4 * k4 + 2] = fmaf(-u4.z, err, x[4 * k4 + 2]);
+                            if (4 * k4 + 3 > t) x[4 * k4 + 3] = fmaf(-u4.w, err, x[4 * k4 + 3]);
+                        }
+                    }
+                }
+                if (SPARSE && active && (cs < C)) p.M[((int64_t)b * ((C + 31) / 32) + (cs >> 5)) * R + r] = maskbits;
             }
+            // the errors of this block must be visible to the far-phase loads of the next one
+            rows_barrier();
+            if (*abort_flag) break;
         }
         cp_async_wait<0>();
     } else {
         bool ok = true;
-        for (int64_t bs = kBlk; bs < C && ok; bs += kBlk) {
-            const int nks = (int)(bs / kKS);
-            for (int ks = 0; ks < nks && ok; ++ks) {
-                const uint32_t s = it % kTcStages, ph = (it / kTcStages) & 1u;
-                ok = mbar_wait(bar_full + 8 * s, ph, abort_flag);
-                if (!ok) break;
-                tc_fence_after();
-                if (lane == 0) {
-                    const uint32_t st = smem_base + s * kTcStageBytes;
-                    const uint64_t ehi = make_desc_tf32(st), elo = make_desc_tf32(st + kPieceBytes);
-                    const uint64_t uhi = make_desc_tf32(st + 2 * kPieceBytes), ulo = make_desc_tf32(st + 3 * kPieceBytes);
-                    umma_tf32(tmem_base, ehi, uhi, ks > 0 ? 1u : 0u);
-                    umma_tf32(tmem_base, elo, uhi, 1u);
-                    umma_tf32(tmem_base, ehi, ulo, 1u);
-                    umma_commit(bar_empty + 8 * s);
+        for (int64_t bs = 0; bs < C && ok; bs += kBlk) {
+            if (bs > 0) {
+                const int nks = (int)(bs / kKS);
+                for (int ks = 0; ks < nks && ok; ++ks) {
+                    const uint32_t s = it % kTcStages, ph = (it / kTcStages) & 1u;
+                    ok = mbar_wait(bar_full + 8 * s, ph, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (lane == 0) {
+                        const uint32_t st = smem_base + s * kTcStageBytes;
+                        const uint64_t ehi = make_desc_tf32(st), elo = make_desc_tf32(st + kPieceBytes);
+                        const uint64_t uhi = make_desc_tf32(st + 2 * kPieceBytes), ulo = make_desc_tf32(st + 3 * kPieceBytes);
+                        const uint32_t id = idesc_tf32(128);
+                        umma_tf32(tmem_base, ehi, uhi, id, ks > 0 ? 1u : 0u);
+                        umma_tf32(tmem_base, elo, uhi, id, 1u);
+                        umma_tf32(tmem_base, ehi, ulo, id, 1u);
+                        umma_commit(bar_empty + 8 * s);
+                    }
+                    __syncwarp();
+                    ++it;
                 }
+                if (!ok) break;
+                if (lane == 0) umma_commit(bar_acc);
                 __syncwarp();
-                ++it;
             }
-            if (!ok) break;
-            if (lane == 0) umma_commit(bar_acc);
-            __syncwarp();
+            for (int sb = 1; sb < 4 && ok; ++sb) {
+                for (int i = 0; i < 4 && ok; ++i) {
+                    const uint32_t s = it % kTcStages, ph = (it / kTcStages) & 1u;
+                    ok = mbar_wait(bar_full + 8 * s, ph, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (lane == 0) {
+                        const uint32_t st = smem_base + s * kTcStageBytes;
+                        const uint32_t boff = (uint32_t)sb * 1024u;  // skip the MN blocks of the solved sub-blocks
+                        const uint64_t ehi = make_desc_tf32(st), elo = make_desc_tf32(st + kPieceBytes);
+                        const uint64_t uhi = make_desc_tf32(st + 2 * kPieceBytes + boff);
+                        const uint64_t ulo = make_desc_tf32(st + 3 * kPieceBytes + boff);
+                        const uint32_t id = idesc_tf32((uint32_t)(kBlk - sb * kSub));
+                        const uint32_t d = tmem_base + (uint32_t)(sb * kSub);
+                        // block 0 has no far phase: its first near step starts the accumulator columns it covers
+                        const uint32_t acc = (bs > 0 || sb > 1 || i > 0) ? 1u : 0u;
+                        umma_tf32(d, ehi, uhi, id, acc);
+                        umma_tf32(d, elo, uhi, id, 1u);
+                        umma_tf32(d, ehi, ulo, id, 1u);
+                        umma_commit(bar_empty + 8 * s);
+                    }
+                    __syncwarp();
+                    ++it;
+                }
+                if (!ok) break;
+                if (lane == 0) umma_commit(bar_acc);
+                __syncwarp();
+            }
         }
     }
     tc_fence_before();
