@@ -42,8 +42,9 @@ __device__ __forceinline__ void tile_gemm(float (&acc)[8][TN / 16], const float 
                                           float *Bs) {
     const int tid = threadIdx.x;
     const int ty = tid >> 4, tx = tid & 15;
-    for (int k0 = 0; k0 < K; k0 += KC) {
-        // ---- stage A chunk [TM][KC]
+    // global -> registers for chunk k0 (issued one chunk ahead of its use), registers -> shared memory later
+    float4 ra[2], rb[TN / 64];
+    auto fetch = [&](int k0) {
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int v = tid + 256 * i;
@@ -66,9 +67,8 @@ __device__ __forceinline__ void tile_gemm(float (&acc)[8][TN / 16], const float 
                     if (gk + 3 > gr) val.w = 0.f;
                 }
             }
-            *reinterpret_cast<float4 *>(As + row * AS + kq) = val;
+            ra[i] = val;
         }
-        // ---- stage B chunk [KC][TN]
 #pragma unroll
         for (int i = 0; i < TN / 64; ++i) {
             const int v = tid + 256 * i;
@@ -84,8 +84,22 @@ __device__ __forceinline__ void tile_gemm(float (&acc)[8][TN / 16], const float 
                     if (n4 + 3 < n_valid) val.w = src[3];
                 }
             }
-            *reinterpret_cast<float4 *>(Bs + row * TN + n4) = val;
+            rb[i] = val;
         }
+    };
+    fetch(0);
+    for (int k0 = 0; k0 < K; k0 += KC) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int v = tid + 256 * i;
+            *reinterpret_cast<float4 *>(As + (v >> 2) * AS + (v & 3) * 4) = ra[i];
+        }
+#pragma unroll
+        for (int i = 0; i < TN / 64; ++i) {
+            const int v = tid + 256 * i;
+            *reinterpret_cast<float4 *>(Bs + (v / (TN / 4)) * TN + (v % (TN / 4)) * 4) = rb[i];
+        }
+        if (k0 + KC < K) fetch(k0 + KC);  // in flight while this chunk is multiplied
         __syncthreads();
 #pragma unroll
         for (int kk = 0; kk < KC; ++kk) {
@@ -173,7 +187,7 @@ __global__ void __launch_bounds__(256) chol_diag_kernel(float *__restrict__ Aall
         if (r < nbk && c < nbk) {
             if (c <= r) A[(cb + r) * C + cb + c] = D[r][c];
             // diagonal block of the row-scaled inverse  diag(L) L^-1  (unit diagonal)
-            U[(cb + r) * C + cb + c] = (c < r) ? __fmul_rn(D[r][r], Di[r][c]) : ((c == r) ? 1.0f : 0.0f);
+            if (Uall) U[(cb + r) * C + cb + c] = (c < r) ? __fmul_rn(D[r][r], Di[r][c]) : ((c == r) ? 1.0f : 0.0f);
         }
     }
     if (tid < nbk) udiag[(int64_t)b * C + (C - 1 - (cb + tid))] = __fdiv_rn(1.0f, D[tid][tid]);
@@ -181,7 +195,7 @@ __global__ void __launch_bounds__(256) chol_diag_kernel(float *__restrict__ Aall
 }
 
 // ---- panel: rows below the diagonal block <- rows * Dinv^T; also stored transposed above ------
-__global__ void __launch_bounds__(256) chol_panel_kernel(float *__restrict__ Aall, int64_t C, int k, int nblk,
+__global__ void __launch_bounds__(256, 3) chol_panel_kernel(float *__restrict__ Aall, int64_t C, int k, int nblk,
                                                           const float *__restrict__ dinv_all, int vec) {
     __shared__ __align__(16) float As[TM * AS];
     __shared__ __align__(16) float Bs[KC * 64];
@@ -213,7 +227,7 @@ __global__ void __launch_bounds__(256) chol_panel_kernel(float *__restrict__ Aal
 }
 
 // ---- syrk: trailing lower triangle -= panel * panel^T -----------------------------------------
-__global__ void __launch_bounds__(256) chol_syrk_kernel(float *__restrict__ Aall, int64_t C, int k, int vec) {
+__global__ void __launch_bounds__(256, 2) chol_syrk_kernel(float *__restrict__ Aall, int64_t C, int k, int vec) {
     if (blockIdx.y > blockIdx.x) return;  // upper tiles are not needed
     __shared__ __align__(16) float As[TM * AS];
     __shared__ __align__(16) float Bs[KC * 128];
@@ -254,7 +268,7 @@ __global__ void __launch_bounds__(256) chol_syrk_kernel(float *__restrict__ Aall
 }
 
 // ---- triangular inverse, block column j: M[below,j] = -(M[below,below] L[below,j]) Dinv_j -------
-__global__ void __launch_bounds__(256) trtri_step_kernel(const float *__restrict__ Aall, float *__restrict__ Uall,
+__global__ void __launch_bounds__(256, 3) trtri_step_kernel(const float *__restrict__ Aall, float *__restrict__ Uall,
                                                           int64_t C, int j, int nblk,
                                                           const float *__restrict__ dinv_all, int vec) {
     __shared__ __align__(16) float As[TM * AS];
@@ -320,6 +334,35 @@ __global__ void rotate_upper_kernel(float *__restrict__ Uall, int64_t C, const i
     if (k > t) U[t * C + k] = U[(C - 1 - t) * C + (C - 1 - k)];
 }
 
+// Inversion-free form.  With  J Hp J = L L^T  the matrix  V = J L J  is upper triangular and  Hp = V V^T.
+// Scaling its columns to a unit diagonal gives  Vt = V diag(V)^-1 = (the reference's unit factor U)^-1, and the
+// column solver can work from Vt directly:  x_t = w_t + sum_{s<t} (w_s - deq_s) Vt[s,t]  is the same recurrence
+// as  x_t = w_t - sum_{s<t} err_s U[s,t]  (substitute err = (w - deq) Vt).  So no triangular inverse is needed.
+// This pass writes  out[s][t] = -Vt[s,t] = -L[C-1-s][C-1-t] * udiag[t]  for t > s  (udiag[t] = 1 / L[C-1-t][C-1-t]),
+// 1 on the diagonal.  Sources are on or below the diagonal, destinations above it, so it may run in place.
+__global__ void rotate_scale_neg_kernel(const float *__restrict__ Lall, float *__restrict__ Oall, int64_t C,
+                                        const int32_t *__restrict__ info, float *__restrict__ udiag) {
+    const int b = blockIdx.z;
+    const float *L = Lall + (int64_t)b * C * C;
+    float *O = Oall + (int64_t)b * C * C;
+    const bool bad = info[b] != 0;
+    const int64_t s = (int64_t)blockIdx.y * 8 + threadIdx.y;
+    const int64_t t = (int64_t)blockIdx.x * 32 + threadIdx.x;
+    if (s >= C || t >= C) return;
+    if (bad) {
+        if (t >= s) O[s * C + t] = (t == s) ? 1.0f : 0.0f;
+        if (t == s) udiag[(int64_t)b * C + t] = 1.0f;
+        return;
+    }
+    if (t > s) O[s * C + t] = -__fmul_rn(L[(C - 1 - s) * C + (C - 1 - t)], udiag[(int64_t)b * C + t]);
+}
+
+__global__ void unit_diag_kernel(float *__restrict__ Oall, int64_t C) {
+    const int b = blockIdx.y;
+    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < C) Oall[(int64_t)b * C * C + t * C + t] = 1.0f;
+}
+
 __global__ void zero_lower_kernel(float *__restrict__ Uall, int64_t C) {
     const int b = blockIdx.z;
     float *U = Uall + (int64_t)b * C * C;
@@ -340,16 +383,9 @@ extern "C" int64_t forge_chol_workspace_bytes(int nb, int64_t C) {
     return (int64_t)nb * nblk * 2 * NB * NB * (int64_t)sizeof(float) + 256;
 }
 
-extern "C" int forge_chol_inv_upper_batched(float *A, int nb, int64_t C, float *U, float *udiag, int32_t *info,
-                                            int zero_lower, void *ws, void *stream) {
-    FORGE_REQUIRE(A && U && udiag && info && ws, "null pointer");
-    FORGE_REQUIRE(nb > 0 && C > 0, "empty batch");
-    FORGE_REQUIRE(A != U, "A must not alias U");
-    FORGE_REQUIRE((uintptr_t)ws % 16 == 0, "workspace must be 16-byte aligned");
-    cudaStream_t st = (cudaStream_t)stream;
+static void launch_factor(float *A, int nb, int64_t C, float *U, float *udiag, int32_t *info, float *dinv, int vec,
+                          cudaStream_t st) {
     const int nblk = (int)cdiv(C, NB);
-    float *dinv = (float *)ws;
-    const int vec = (C % 4 == 0) && ((uintptr_t)A % 16 == 0) && ((uintptr_t)U % 16 == 0);
     info_clear_kernel<<<(nb + 127) / 128, 128, 0, st>>>(info, nb); FORGE_NOTE_LAUNCH();
     for (int k = 0; k < nblk; ++k) {
         chol_diag_kernel<<<nb, 256, 0, st>>>(A, C, k, nblk, dinv, U, udiag, info); FORGE_NOTE_LAUNCH();
@@ -360,6 +396,33 @@ extern "C" int forge_chol_inv_upper_batched(float *A, int nb, int64_t C, float *
             chol_syrk_kernel<<<dim3(nt, nt, nb), 256, 0, st>>>(A, C, k, vec); FORGE_NOTE_LAUNCH();
         }
     }
+}
+
+extern "C" int forge_chol_factor_batched(float *A, int nb, int64_t C, float *udiag, int32_t *info, void *ws,
+                                         void *stream) {
+    FORGE_REQUIRE(A && udiag && info && ws, "null pointer");
+    FORGE_REQUIRE(nb > 0 && C > 0, "empty batch");
+    FORGE_REQUIRE((uintptr_t)ws % 16 == 0, "workspace must be 16-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int vec = (C % 4 == 0) && ((uintptr_t)A % 16 == 0);
+    launch_factor(A, nb, C, nullptr, udiag, info, (float *)ws, vec, st);
+    dim3 g2((unsigned)cdiv(C, 32), (unsigned)cdiv(C, 8), nb);
+    rotate_scale_neg_kernel<<<g2, dim3(32, 8), 0, st>>>(A, A, C, info, udiag); FORGE_NOTE_LAUNCH();
+    unit_diag_kernel<<<dim3((unsigned)cdiv(C, 256), nb), 256, 0, st>>>(A, C); FORGE_NOTE_LAUNCH();
+    return check_launch("forge_chol_factor_batched");
+}
+
+extern "C" int forge_chol_inv_upper_batched(float *A, int nb, int64_t C, float *U, float *udiag, int32_t *info,
+                                            int zero_lower, void *ws, void *stream) {
+    FORGE_REQUIRE(A && U && udiag && info && ws, "null pointer");
+    FORGE_REQUIRE(nb > 0 && C > 0, "empty batch");
+    FORGE_REQUIRE(A != U, "A must not alias U");
+    FORGE_REQUIRE((uintptr_t)ws % 16 == 0, "workspace must be 16-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int nblk = (int)cdiv(C, NB);
+    float *dinv = (float *)ws;
+    const int vec = (C % 4 == 0) && ((uintptr_t)A % 16 == 0) && ((uintptr_t)U % 16 == 0);
+    launch_factor(A, nb, C, U, udiag, info, dinv, vec, st);
     for (int j = nblk - 2; j >= 0; --j) {
         const int64_t m = C - (int64_t)(j + 1) * NB;
         const unsigned nt = (unsigned)cdiv(m, TM);

@@ -47,6 +47,7 @@ struct SolveParams {
     uint32_t *M;           // [nb][ceil(C/32)][R]
     int64_t R, C, G;
     int gs, maxq, write_deq, uvec_is_diag;
+    int alt;               // 1: U holds -Vt (inversion-free form) and the propagated quantity is w - deq
 };
 
 __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc, bool pred) {
@@ -551,9 +552,12 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
                     }
                 }
                 // (3) x = W - acc for the 32 columns of this sub-block
-                float x[kSub];
+                float x[kSub], w32[kSub];
 #pragma unroll
-                for (int i = 0; i < kSub; ++i) x[i] = (active && (cs + i < C)) ? Wt[(cs + i) * R + r] : 0.0f;
+                for (int i = 0; i < kSub; ++i) {
+                    w32[i] = (active && (cs + i < C)) ? Wt[(cs + i) * R + r] : 0.0f;
+                    x[i] = w32[i];
+                }
                 if (bs > 0 || sb > 0) {
                     if (ok) ok = mbar_wait(bar_acc, acc_it & 1u, abort_flag);
                     ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld is warp-aligned: the whole warp goes or none
@@ -605,6 +609,7 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
                         const bool keep = SPARSE ? (((maskbits >> t) & 1u) != 0u) : true;
                         if (keep && (active || !SPARSE)) quantize_scalar(x[t], sc, q0, maxq, err, deq, qb);
                         else err = x[t];
+                        if (p.alt) err = __fsub_rn(w32[t], deq);  // inversion-free form propagates w - deq
                         if (active) {
                             *qp = qb;
                             if (p.write_deq) *wp = deq;
@@ -816,7 +821,7 @@ extern "C" int forge_gptq_solve_cr(float *Wt, const float *U, const float *uinv,
 extern "C" int forge_gptq_solve_batched(const void *W, int w_dtype, int nb, int64_t R, int64_t C, const float *U,
                                         const float *udiag, const int32_t *u_map, const int32_t *perm, int nu,
                                         const float *scales, const float *qzeros, int gs, int bits, int sparse14,
-                                        uint8_t *qweight, uint32_t *M, void *ws, int32_t *status,
+                                        int form, uint8_t *qweight, uint32_t *M, void *ws, int32_t *status,
                                         void *stream) {
     FORGE_REQUIRE(W && U && scales && qzeros && qweight && ws, "null pointer");
     FORGE_REQUIRE(nb > 0 && R > 0 && C > 0 && gs > 0 && bits >= 1 && bits <= 8, "bad sizes");
@@ -841,6 +846,11 @@ extern "C" int forge_gptq_solve_batched(const void *W, int w_dtype, int nb, int6
     p.Wt = Wt; p.E = Wt; p.U = U; p.uvec = udiag; p.u_map = u_map;
     p.scales = scales; p.qzeros = qzeros; p.perm = perm; p.q = qt; p.M = M;
     p.R = R; p.C = C; p.G = cdiv(C, gs); p.gs = gs; p.maxq = (1 << bits) - 1; p.write_deq = 0; p.uvec_is_diag = 1;
+    p.alt = form ? 1 : 0;
+    if (p.alt && !use_tc_solver(p)) {
+        set_error("forge_gptq_solve_batched: the inversion-free form needs R %% 4 == 0 and C %% 4 == 0");
+        return FORGE_ERR_UNSUPPORTED;
+    }
     int rc = sparse14 ? launch_solve<0, true>(p, nb, status, st) : launch_solve<0, false>(p, nb, status, st);
     if (rc != FORGE_OK) return rc;
     untranspose_codes_kernel<<<tgrid, dim3(32, 8), 0, st>>>(qt, R, C, perm_inv, u_map, qweight); FORGE_NOTE_LAUNCH();

@@ -37,6 +37,7 @@ _PROTOS = {
     "forge_weight_zero_cols": (_c_int, [_ptr, _c_int, _c_int, _c_i64, _c_i64, _ptr, _ptr]),
     "forge_hessian_gather_damp": (_c_int, [_ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr, _c_f32, _ptr, _ptr, _ptr, _ptr]),
     "forge_chol_workspace_bytes": (_c_i64, [_c_int, _c_i64]),
+    "forge_chol_factor_batched": (_c_int, [_ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _ptr]),
     "forge_chol_inv_upper_batched": (_c_int, [_ptr, _c_int, _c_i64, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr]),
     "forge_noalloc_max_c": (_c_i64, []),
     "forge_chol_inv_upper_noalloc": (_c_int, [_ptr, _c_i64, _ptr, _ptr, _ptr, _c_int, _ptr]),
@@ -45,7 +46,7 @@ _PROTOS = {
     "forge_solve_workspace_bytes": (_c_i64, [_c_int, _c_i64, _c_i64]),
     "forge_gptq_solve_cr": (_c_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_i64, _c_i64, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr]),
     "forge_gptq_solve_batched": (_c_int, [_ptr, _c_int, _c_int, _c_i64, _c_i64, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr,
-                                          _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr]),
+                                          _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr]),
     "forge_dequantize": (_c_int, [_ptr, _ptr, _ptr, _c_i64, _c_i64, _c_int, _ptr, _c_int, _ptr]),
     "forge_pack_int4": (_c_int, [_ptr, _ptr, _c_i64, _c_i64, _c_int, _ptr, _ptr]),
     "forge_pack_sparse14": (_c_int, [_ptr, _ptr, _ptr, _c_i64, _c_i64, _ptr, _ptr]),

@@ -35,6 +35,7 @@ class MoEQuantConfig:
     mse_max_shrink: float = 0.2
     mse_norm: float = 2.4
     expert_chunk: int = 0                  # experts factorised/solved per pass (0 = all at once)
+    inversion_free: bool = True            # solve from the Cholesky factor itself, without the triangular inverse
 
 
 def swiglu_expert_forward(X, token_lists, offsets_host, Wg, Wu):
@@ -59,6 +60,8 @@ class MoELayerQuantizer:
 
     def __init__(self, cfg: MoEQuantConfig):
         self.cfg = cfg
+        self.inversion_free = False
+        self._status = None
 
     # ---- one family of matrices sharing per-slot Hessians -------------------------------------
     def _factor(self, H, n_samples, Ws):
@@ -80,10 +83,14 @@ class MoELayerQuantizer:
         for gi, wzero in enumerate(groups):
             last = gi == len(groups) - 1
             A, _, _ = ops.hessian_gather_damp(H, perm32, pruned, wzero, invalid, cfg.rel_damp)
-            # the last group may overwrite H with U; earlier groups need H intact
-            U, udiag, info = ops.chol_inv_upper(A, U=H if last else None, zero_lower=False)
+            if self.inversion_free:
+                # factor only: the solver works from the scaled reverse-Cholesky factor (form = 1)
+                U, udiag, info = ops.chol_factor(A)
+            else:
+                # the last group may overwrite H with U; earlier groups need H intact
+                U, udiag, info = ops.chol_inv_upper(A, U=H if last else None, zero_lower=False)
+                del A
             outs.append((U, udiag, info))
-            del A
         if shared:
             outs = outs * len(Ws)
         return outs, perm32
@@ -94,6 +101,11 @@ class MoELayerQuantizer:
         cand = None
         if cfg.quantization_scale == "mse":
             cand = torch.linspace(1.0, cfg.mse_max_shrink, cfg.mse_grid, dtype=torch.float32, device=H.device)
+        # the inversion-free form needs 16-byte rows in the solver's work layout
+        # (dense GPTQ only: the 1:4 mask choice of SparseGPT is a near-tie argmax and reacts to the different
+        # rounding of that form, so the sparse path keeps the reference's form)
+        self.inversion_free = (bool(cfg.inversion_free) and not sparse
+                               and all(W.shape[1] % 4 == 0 and W.shape[2] % 4 == 0 for W in Ws))
         factors, perm32 = self._factor(H, n_samples, Ws)
         results = []
         for W, (U, udiag, info) in zip(Ws, factors):
@@ -101,7 +113,8 @@ class MoELayerQuantizer:
             scales, qzeros = ops.quant_grid(W.view(nb * R, C), cfg.group_size, cfg.bits, cfg.symmetric, cand,
                                             cfg.mse_norm)
             out = ops.gptq_solve_batched(W, U, scales, qzeros, cfg.group_size, cfg.bits, perm=perm32,
-                                         udiag=udiag if sparse else None, sparse14=sparse)
+                                         udiag=udiag if sparse else None, sparse14=sparse, status=self._status,
+                                         form=1 if self.inversion_free else 0)
             q, M = out if sparse else (out, None)
             G = (C + cfg.group_size - 1) // cfg.group_size
             res = {"qweight": q, "scales": scales.view(nb, R, G), "qzeros": qzeros.view(nb, R, G), "info": info,
@@ -168,6 +181,7 @@ class MoELayerQuantizer:
         chunk = cfg.expert_chunk if cfg.expert_chunk > 0 else n_local
         res = {"gate": [], "up": [], "down": []}
         status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._status = status
         for c0 in range(0, n_local, chunk):
             c1 = min(n_local, c0 + chunk)
             nb = c1 - c0

@@ -103,6 +103,18 @@ def chol_inv_upper(A: torch.Tensor, U=None, zero_lower: bool = True):
     return U, udiag, info
 
 
+def chol_factor(A: torch.Tensor):
+    """Inversion-free form: A [nb,C,C] (index-reversed damped Hessian) is overwritten; its upper triangle then
+    holds -Vt (see forge_chol_factor_batched).  Returns (A, udiag, info)."""
+    nb, C, _ = A.shape
+    dev = _dev(A)
+    udiag = torch.empty((nb, C), dtype=torch.float32, device=dev)
+    info = torch.empty(nb, dtype=torch.int32, device=dev)
+    ws = torch.empty(query("forge_chol_workspace_bytes", nb, C), dtype=torch.uint8, device=dev)
+    call("forge_chol_factor_batched", ptr(A), nb, C, ptr(udiag), ptr(info), ptr(ws), stream_ptr())
+    return A, udiag, info
+
+
 def quant_grid(W: torch.Tensor, gs: int, bits: int, symmetric: bool, candidates=None, norm: float = 2.4):
     """W [rows, C] (bf16/fp32) -> (scales, qzeros) fp32 [rows*G]; candidates given = MSE search fused in."""
     rows, C = W.shape
@@ -137,7 +149,7 @@ def gptq_solve_cr(Wt, U, scales_el, qzeros_el, bits: int, uinv=None, status=None
 
 
 def gptq_solve_batched(W, U, scales, qzeros, gs: int, bits: int, perm=None, u_map=None, udiag=None,
-                       sparse14: bool = False, ws=None, status=None):
+                       sparse14: bool = False, ws=None, status=None, form: int = 0):
     """W [nb,R,C] original order; U [nu,C,C]; scales/qzeros [nb*R*G] -> qweight [nb,R,C] (+ M [nb,G32,R])."""
     nb, R, C = W.shape
     dev = _dev(W)
@@ -147,7 +159,7 @@ def gptq_solve_batched(W, U, scales, qzeros, gs: int, bits: int, perm=None, u_ma
     if ws is None:
         ws = torch.empty(query("forge_solve_workspace_bytes", nb, R, C), dtype=torch.uint8, device=dev)
     call("forge_gptq_solve_batched", ptr(W), dtype_code(W), nb, R, C, ptr(U), ptr(udiag), ptr(u_map), ptr(perm), nu,
-         ptr(scales), ptr(qzeros), gs, bits, int(sparse14), ptr(q), ptr(M), ptr(ws), ptr(status), stream_ptr())
+         ptr(scales), ptr(qzeros), gs, bits, int(sparse14), int(form), ptr(q), ptr(M), ptr(ws), ptr(status), stream_ptr())
     return (q, M) if sparse14 else q
 
 

@@ -125,6 +125,14 @@ int forge_hessian_gather_damp(const float *H, int nb, int64_t C, const int32_t *
  * ws: forge_chol_workspace_bytes(nb, C) bytes.
  * Replaces GPTQ._h_factor, forge/gptq.py:156-177. */
 int64_t forge_chol_workspace_bytes(int nb, int64_t C);
+/* Inversion-free variant: factor only.  With J Hp J = L L^T (A = J Hp J on entry), V = J L J is upper with
+ * Hp = V V^T and Vt = V diag(V)^-1 is the inverse of the reference's unit factor U.  On return the strict upper
+ * triangle of A[b] holds -Vt, the diagonal 1 (the lower triangle is scratch), udiag[b,c] = 1 / V[c,c] (equal to
+ * the diagonal of the reference's un-normalised factor), info as below.  A[b] is then the `U` operand of
+ * forge_gptq_solve_batched with form = 1: x_t = w_t + sum_{s<t} (w_s - deq_s) Vt[s,t] is the reference's
+ * recurrence x_t = w_t - sum_{s<t} err_s U[s,t] with err = (w - deq) Vt substituted.  Half the flops of
+ * forge_chol_inv_upper_batched.  ws: forge_chol_workspace_bytes(nb, C). */
+int forge_chol_factor_batched(float *A, int nb, int64_t C, float *udiag, int32_t *info, void *ws, void *stream);
 int forge_chol_inv_upper_batched(float *A, int nb, int64_t C, float *U, float *udiag, int32_t *info,
                                  int zero_lower, void *ws, void *stream);
 
@@ -177,12 +185,15 @@ int forge_gptq_solve_cr(float *Wt, const float *U, const float *uinv, const floa
  * (group of a column = original index / gs, as forge/gptq.py:251-252 expands them), perm [nu,C] per
  * Hessian slot (NULL = identity; nu = number of slots), udiag [nu,C] from the factorisation (sparse14).  Outputs codes qweight [nb,R,C] uint8 in ORIGINAL
  * column order (forge/gptq.py:139) and, for sparse14, M [nb, ceil(C/32), R] in PERMUTED order like the
- * reference.  ws: forge_solve_workspace_bytes(nb,R,C).  Replaces the glue of GPTQ.quantize/_solver,
+ * reference.  ws: forge_solve_workspace_bytes(nb,R,C).  form = 0: U is the unit upper factor of the inverse
+ * (forge_chol_inv_upper_batched) and the column errors x - deq are propagated, as in the reference;
+ * form = 1: U is the output of forge_chol_factor_batched and w - deq is propagated (same recurrence without
+ * the triangular inverse; needs R % 4 == 0 and C % 4 == 0).  Replaces the glue of GPTQ.quantize/_solver,
  * forge/gptq.py:129-139,231-276, together with the two solvers above. */
 int forge_gptq_solve_batched(const void *W, int w_dtype, int nb, int64_t R, int64_t C, const float *U,
                              const float *udiag, const int32_t *u_map, const int32_t *perm, int nu,
                              const float *scales, const float *qzeros, int gs, int bits, int sparse14,
-                             uint8_t *qweight, uint32_t *M, void *ws, int32_t *status, void *stream);
+                             int form, uint8_t *qweight, uint32_t *M, void *ws, int32_t *status, void *stream);
 
 /* ---- A12: de-quantise codes ------------------------------------------------
  * out[r,c] = dtype( (q[r,c] - qzeros[r,c/gs]) * scales[r,c/gs] )   (fp32 arithmetic)

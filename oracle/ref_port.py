@@ -26,9 +26,18 @@ import numpy as np
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-if _HERE not in sys.path:
-    sys.path.insert(0, _HERE)
-import build as _build  # noqa: E402  (oracle/build.py)
+
+
+def _load_build():
+    """oracle/build.py by path (a plain `import build` could pick up another build.py on sys.path)."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("forge_oracle_build", os.path.join(_HERE, "build.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+_build = _load_build()
 
 _lib = None
 

@@ -439,3 +439,58 @@ def test_pack_sparse14_bit_exact(R, C):
     ref = O.pack_sparsegptq14_to_u64x2(q, M, sc)
     got = ops.pack_sparse14(q.to(DEV), M.to(DEV), sc.to(DEV)).cpu()
     assert torch.equal(ref, got)
+
+
+# --------------------------------------------------------------------------- inversion-free solve form
+@pytest.mark.parametrize("sparse", [False, True])
+@pytest.mark.parametrize("C,R", [(256, 128), (512, 260), (200, 64)])
+def test_inversion_free_form_matches_reference_form(C, R, sparse):
+    """form = 1 (solve from the scaled Cholesky factor, propagate w - deq) is the same recurrence as the
+    reference's form = 0 (unit factor of the inverse, propagate x - deq): the codes agree, and both agree
+    with the oracle."""
+    ops = _ops()
+    gs, nb = 32, 2
+    g = torch.Generator().manual_seed(90)
+    Ws = torch.stack([(torch.randn(R, C, generator=g) * 0.02).to(torch.bfloat16) for _ in range(nb)])
+    Hs = torch.stack([random_spd(C, 91 + b) for b in range(nb)])
+    for b in range(nb):
+        Hs[b][range(C), range(C)] += 0.01 * Hs[b].diag().mean()
+    A = torch.flip(Hs, (1, 2)).contiguous()
+    G = (C + gs - 1) // gs
+    Wp = torch.nn.functional.pad(Ws.float(), (0, G * gs - C)).reshape(nb * R * G, gs)
+    s, z = O.build_group_meta_packed(Wp, 4, True)
+    U0, ud0, info0 = ops.chol_inv_upper(A.clone().to(DEV), zero_lower=False)
+    V1, ud1, info1 = ops.chol_factor(A.clone().to(DEV))
+    assert info0.tolist() == [0] * nb and info1.tolist() == [0] * nb
+    assert rel_fro(ud1.cpu(), ud0.cpu()) < 1e-5
+    # -Vt is the negated inverse of the unit factor: (I - triu(V1,1)) @ triu(U0) = I
+    for b in range(nb):
+        Vt = torch.eye(C, dtype=torch.float64) - torch.triu(V1[b].cpu().double(), 1)
+        Uu = torch.triu(U0[b].cpu().double())
+        assert float((Vt @ Uu - torch.eye(C, dtype=torch.float64)).abs().max()) < 1e-3
+    kw = dict(udiag=None, sparse14=False)
+    st = torch.zeros(1, dtype=torch.int32, device=DEV)
+    o0 = ops.gptq_solve_batched(Ws.to(DEV), U0, s.to(DEV), z.to(DEV), gs, 4, udiag=ud0 if sparse else None,
+                                sparse14=sparse, form=0, status=st)
+    o1 = ops.gptq_solve_batched(Ws.to(DEV), V1, s.to(DEV), z.to(DEV), gs, 4, udiag=ud1 if sparse else None,
+                                sparse14=sparse, form=1, status=st)
+    assert int(st.item()) == 0
+    q0, q1 = (o0[0], o1[0]) if sparse else (o0, o1)
+    if sparse:
+        # the keep-1-of-4 choice is an argmax over near-ties, so the two roundings drift apart more; the
+        # layer driver therefore uses form = 1 for dense GPTQ only
+        assert float((q0 == q1).float().mean()) >= 0.99
+        return
+    assert float((q0 == q1).float().mean()) >= 0.998
+    # and against the oracle, matrix by matrix
+    for b in range(nb):
+        Sel = s.view(nb, R, G)[b].repeat_interleave(gs, 1)[:, :C].T.contiguous()
+        Zel = z.view(nb, R, G)[b].repeat_interleave(gs, 1)[:, :C].T.contiguous()
+        Wt = Ws[b].float().T.contiguous()
+        L = torch.linalg.cholesky(Hs[b])
+        T = torch.linalg.cholesky(torch.cholesky_inverse(L), upper=True).contiguous()
+        if sparse:
+            q_ref, _ = O.sparsegptq14_solver(Wt, T, Sel, Zel, 4)
+        else:
+            q_ref = O.gptq_solver(Wt, (T / T.diag()[:, None]).contiguous(), Sel, Zel, 4)
+        assert float((q1[b].cpu() == q_ref.T).float().mean()) >= 0.995
