@@ -331,11 +331,12 @@ constexpr int kTcThreads = 160;
 constexpr int kKS = 8;                              // columns j per k-step
 constexpr int kPieceBytes = kKS * kBlk * 4;         // 4 KB
 constexpr int kTcStageBytes = 4 * kPieceBytes;      // Ehi, Elo, Uhi, Ulo
-constexpr int kTcStages = 4;
+constexpr int kTcStages = 2;
 constexpr int kTcPrefetch = 4;                      // far k-steps held in registers ahead of the ring
-constexpr int kUsubFloats = kSub * kSub;            // 32x32 triangle of the sub-block
+constexpr int kUsubLd = 2 * kSub;                    // row stride of the staged triangle: 32 values + 32 zeros
+constexpr int kUsubFloats = kSub * kUsubLd;
 constexpr size_t kTcSmem = (size_t)kTcStages * kTcStageBytes + 1024 + 2 * kUsubFloats * sizeof(float) +
-                           kBlk * sizeof(float) + 256;
+                           kSub * kBlk * sizeof(float) + kBlk * sizeof(float) + 256;
 
 // Instruction descriptor: D fp32, A/B tf32, both MN-major, M = 128, N given.
 __device__ __forceinline__ uint32_t idesc_tf32(uint32_t n) {
@@ -383,7 +384,8 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *ring = smem_raw + (smem_base - smem_u32(smem_raw));
     float *Usub = reinterpret_cast<float *>(ring + kTcStages * kTcStageBytes);  // [2][32][32]
-    float *uinv_s = Usub + 2 * kUsubFloats;                                      // [128]
+    float *es = Usub + 2 * kUsubFloats;                                          // [32][128] errors of a sub-block
+    float *uinv_s = es + kSub * kBlk;                                            // [128]
     uint64_t *bars = reinterpret_cast<uint64_t *>(uinv_s + kBlk);                // full[4], empty[4], acc
     uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + 9);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
@@ -405,6 +407,7 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    for (int i = tid; i < 2 * kUsubFloats; i += kTcThreads) Usub[i] = 0.0f;  // columns 32..63 stay zero
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -431,9 +434,6 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
         // scalar slot of this thread's own row in an error piece, for K row jj: piece_offset(jj, tid/4) + (tid%4)*4
         const bool uniform_meta = (MODE == 0) && (p.perm == nullptr) && (p.gs % kSub == 0);
         bool ok = true;
-        float e32[kSub];
-#pragma unroll
-        for (int i = 0; i < kSub; ++i) e32[i] = 0.0f;
 
         for (int64_t bs = 0; bs < C; bs += kBlk) {
             const bool u_ok = (bs + 4 * c4) < C;
@@ -507,7 +507,7 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
                     const int v = tid + 128 * i;
                     const int jj = v >> 3, k = (v & 7) * 4;
                     const bool okl = (cs + jj < C) && (cs + k < C);
-                    cp_async16(us + jj * kSub + k, okl ? (U + (cs + jj) * C + cs + k) : U, okl);
+                    cp_async16(us + jj * kUsubLd + k, okl ? (U + (cs + jj) * C + cs + k) : U, okl);
                 }
                 cp_async_commit();
                 // (2) near update: the previous sub-block's errors go to the later columns of the block
@@ -530,7 +530,7 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
                                 uint8_t *stage = ring + s * kTcStageBytes;
 #pragma unroll
                                 for (int jj = 0; jj < kKS; ++jj) {
-                                    const float v = e32[i * kKS + jj];
+                                    const float v = es[(i * kKS + jj) * kBlk + tid];
                                     const float hi = tf32_round(v);
                                     const float lo = tf32_round(__fsub_rn(v, hi));
                                     const uint32_t off = piece_offset(jj, tid >> 2) + ((tid & 3) << 2);
@@ -577,28 +577,29 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
                 cp_async_wait<0>();
                 rows_barrier();
                 if (*abort_flag) break;
-                // (5) sequential solve of the 32 columns
+                // (5) sequential solve of the 32 columns.  The loop is rolled: x and w slide down by one register per
+                // column, so that the column being solved is always x[0] and every index is static.  (Fully unrolled,
+                // the 32 x ~80 instructions run once per pass and the warp stalls on instruction fetch.)
                 uint32_t maskbits = 0u;
                 float s_nx, q0_nx;
                 load_meta<MODE>(p, b, u, r, cs, active, s_nx, q0_nx);
                 uint8_t *qp = p.q + ((int64_t)b * C + cs) * R + r;
                 float *ep = E + cs * R + r;
                 float *wp = Wt + cs * R + r;
-#pragma unroll
+#pragma unroll 1
                 for (int t = 0; t < kSub; ++t) {
-                    asm volatile("" ::: "memory");  // keep later columns' loads from being hoisted up here
                     const int64_t c = cs + t;
                     const float sc = s_nx, q0 = q0_nx;
                     if (!uniform_meta && t + 1 < kSub) load_meta<MODE>(p, b, u, r, c + 1, active, s_nx, q0_nx);
                     float err = 0.0f;
                     if (c < C) {
-                        if (SPARSE && (t % 4 == 0)) {
+                        if (SPARSE && (t & 3) == 0) {
                             float best = -1e30f;
                             int bidx = -1;
 #pragma unroll
                             for (int k = 0; k < 4; ++k) {
                                 if (active && (c + k < C)) {
-                                    const float sv = fabsf(__fmul_rn(x[t + k], uinv_s[sb * kSub + t + k]));
+                                    const float sv = fabsf(__fmul_rn(x[k], uinv_s[sb * kSub + t + k]));
                                     if (best < sv) { best = sv; bidx = k; }
                                 }
                             }
@@ -607,9 +608,9 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
                         float deq = 0.0f;
                         uint8_t qb = 0;
                         const bool keep = SPARSE ? (((maskbits >> t) & 1u) != 0u) : true;
-                        if (keep && (active || !SPARSE)) quantize_scalar(x[t], sc, q0, maxq, err, deq, qb);
-                        else err = x[t];
-                        if (p.alt) err = __fsub_rn(w32[t], deq);  // inversion-free form propagates w - deq
+                        if (keep && (active || !SPARSE)) quantize_scalar(x[0], sc, q0, maxq, err, deq, qb);
+                        else err = x[0];
+                        if (p.alt) err = __fsub_rn(w32[0], deq);  // inversion-free form propagates w - deq
                         if (active) {
                             *qp = qb;
                             if (p.write_deq) *wp = deq;
@@ -617,19 +618,16 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
                         }
                     }
                     qp += R; ep += R; wp += R;
-                    asm volatile("" : "+l"(qp), "+l"(ep), "+l"(wp));
-                    e32[t] = err;
-                    const float4 *urow = reinterpret_cast<const float4 *>(us + t * kSub);
+                    es[t * kBlk + tid] = err;
+                    // x[k] <- x[k+1] - U[t][t+1+k] * err ; beyond the triangle the staged row reads zero
+                    const float *urow = us + t * kUsubLd + t + 1;
 #pragma unroll
-                    for (int k4 = 0; k4 < kSub / 4; ++k4) {
-                        if (4 * k4 + 3 > t) {
-                            const float4 u4 = urow[k4];
-                            if (4 * k4 + 0 > t) x[4 * k4 + 0] = fmaf(-u4.x, err, x[4 * k4 + 0]);
-                            if (4 * k4 + 1 > t) x[4 * k4 + 1] = fmaf(-u4.y, err, x[4 * k4 + 1]);
-                            if (4 * k4 + 2 > t) x[4 * k4 + 2] = fmaf(-u4.z, err, x[4 * k4 + 2]);
-                            if (4 * k4 + 3 > t) x[4 * k4 + 3] = fmaf(-u4.w, err, x[4 * k4 + 3]);
-                        }
+                    for (int k = 0; k < kSub - 1; ++k) {
+                        x[k] = fmaf(-urow[k], err, x[k + 1]);
+                        w32[k] = w32[k + 1];
                     }
+                    x[kSub - 1] = 0.0f;
+                    w32[kSub - 1] = 0.0f;
                 }
                 if (SPARSE && active && (cs < C)) p.M[((int64_t)b * ((C + 31) / 32) + (cs >> 5)) * R + r] = maskbits;
             }
