@@ -164,7 +164,7 @@ __device__ __forceinline__ float fast_ex2(float x) {
 }
 
 template <int GS, bool BF16, bool ABSMAX>
-__global__ void __launch_bounds__(kMseThreads, 2)
+__global__ void __launch_bounds__(kMseThreads, 4)
 mse_grid_kernel(const void *__restrict__ Wv, int64_t rows, int64_t C, int64_t G, int bits, int symmetric,
                 const float *__restrict__ cand, int P, float norm, float *__restrict__ scales,
                 float *__restrict__ qzeros, int tpg, int gpc) {
@@ -238,10 +238,16 @@ mse_grid_kernel(const void *__restrict__ Wv, int64_t rows, int64_t C, int64_t G,
                 hiq[c] = kMagic + maxq;       // clamp bounds and zero in the "magic" domain (all exact integers)
                 offq[c] = kMagic + q0[c];
             }
-            float a[kMseCPT][32];
+            // The reference reduces the 32 lane sums with a shfl_down tree (offsets 16, 8, 4, 2, 1): node(l) at
+            // offset o is node(l) + node(l + o).  Visiting the lanes in bit-reversed order (0, 16, 8, 24, 4, ...)
+            // makes every tree node the sum of two ADJACENT finished subtrees, so a 6-entry stack (one entry per
+            // pending subtree, as in a binary counter) reproduces the tree exactly with 6 live registers per
+            // candidate instead of 32.
+            float st[kMseCPT][6];
             const float4 *v4 = reinterpret_cast<const float4 *>(&vals_s[gl][0]);
 #pragma unroll
-            for (int l = 0; l < 32; ++l) {
+            for (int idx = 0; idx < 32; ++idx) {
+                const int l = ((idx & 1) << 4) | ((idx & 2) << 2) | (idx & 4) | ((idx & 8) >> 2) | ((idx & 16) >> 4);
                 float v[4];
                 if (VPL == 4) {
                     const float4 t = v4[l];
@@ -249,6 +255,13 @@ mse_grid_kernel(const void *__restrict__ Wv, int64_t rows, int64_t C, int64_t G,
                 } else {
 #pragma unroll
                     for (int i = 0; i < VPL; ++i) v[i] = vals_s[gl][l * VPL + i];
+                }
+                const int pc = __builtin_popcount(idx);   // pending subtrees before this leaf
+                int merges = 0;                            // trailing one bits of idx
+#pragma unroll
+                for (int bbit = 0; bbit < 5; ++bbit) {
+                    if (((idx >> bbit) & 1) == 0) break;
+                    ++merges;
                 }
 #pragma unroll
                 for (int c = 0; c < kMseCPT; ++c) {
@@ -264,40 +277,48 @@ mse_grid_kernel(const void *__restrict__ Wv, int64_t rows, int64_t C, int64_t G,
                         const float val = fast_ex2(__fmul_rn(__fmul_rn(lg, norm), 1.44269502f));  // __expf
                         acc = __fadd_rn(acc, val);
                     }
-                    a[c][l] = acc;
+                    st[c][pc] = acc;
+#pragma unroll
+                    for (int m = 0; m < 5; ++m) {
+                        if (m < merges) st[c][pc - 1 - m] = __fadd_rn(st[c][pc - 1 - m], st[c][pc - m]);
+                    }
                 }
             }
 #pragma unroll
             for (int c = 0; c < kMseCPT; ++c) {
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-                    for (int l = 0; l < o; ++l) a[c][l] = __fadd_rn(a[c][l], a[c][l + o]);
                 const int p = jt + c * tpg;
-                if (p < P) loss_s[gl][p] = a[c][0];
+                if (p < P) loss_s[gl][p] = st[c][0];
             }
         }
         __syncthreads();
-        // ---- first strictly smaller loss in candidate order wins
-        if (tid < gpc && g0 + tid < n_groups) {
-            const float sg = meta_s[tid][0], q0g = meta_s[tid][1];
+        // ---- first strictly smaller loss in candidate order wins == lexicographic minimum of (loss, candidate)
+        if (warp < gpc && g0 + warp < n_groups) {
             float best = FLT_MAX;
-            int bp = -1;
-            for (int p = 0; p < P; ++p) {
-                const float l = loss_s[tid][p];
-                if (l < best) { best = l; bp = p; }
+            int bp = 0x7fffffff;
+            for (int p = lane; p < P; p += 32) {
+                const float l = loss_s[warp][p];
+                if (l < best) { best = l; bp = p; }   // ascending p inside a lane: earlier candidate kept on ties
             }
-            float bs = sg, bq = q0g;
-            if (bp >= 0) {
-                bs = __fmul_rn(sg, cand[bp]);
-                if (!symmetric) {
-                    const float xmin = -__fmul_rn(sg, q0g);
-                    const float rc = __fdiv_rn(1.0f, __fadd_rn(bs, kEps));
-                    bq = fminf(fmaxf(rintf(__fmul_rn(-xmin, rc)), 0.0f), maxq);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int op = __shfl_xor_sync(0xffffffffu, bp, o);
+                if (ob < best || (ob == best && op < bp)) { best = ob; bp = op; }
+            }
+            if (lane == 0) {
+                const float sg = meta_s[warp][0], q0g = meta_s[warp][1];
+                float bs = sg, bq = q0g;
+                if (best < FLT_MAX && bp < P) {
+                    bs = __fmul_rn(sg, cand[bp]);
+                    if (!symmetric) {
+                        const float xmin = -__fmul_rn(sg, q0g);
+                        const float rc = __fdiv_rn(1.0f, __fadd_rn(bs, kEps));
+                        bq = fminf(fmaxf(rintf(__fmul_rn(-xmin, rc)), 0.0f), maxq);
+                    }
                 }
+                scales[g0 + warp] = bs;
+                qzeros[g0 + warp] = bq;
             }
-            scales[g0 + tid] = bs;
-            qzeros[g0 + tid] = bq;
         }
         __syncthreads();
     }
