@@ -135,6 +135,21 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_tc_kernel(const HessParam
             const int nkt = (int)((n + kKT - 1) / kKT);
             const int32_t *tl = P.token_idx ? P.token_idx + off : nullptr;
             bool ok = true;
+            // Token indices of the k-tile about to be issued; the ones of the NEXT k-tile are loaded right after
+            // this tile's copies are issued, so that their latency never sits between two stages.
+            int32_t tok_cur[4], tok_nxt[4];
+            auto load_tokens = [&](int kt, int32_t (&dst)[4]) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int64_t kidx = (int64_t)kt * kKT + warp * 16 + i * 4 + rsub;
+                    int32_t t = -1;
+                    if (kidx < n) t = tl ? tl[kidx] : (int32_t)(off + kidx);
+                    dst[i] = t;
+                }
+            };
+            load_tokens(0, tok_cur);
+            // channel offsets of the (up to) eight 64-channel sub-tiles this thread copies a chunk of
+            const int64_t chA = (int64_t)ti * kTile + chunk * 8, chB = (int64_t)tj * kTile + chunk * 8;
             for (int kt = 0; kt < nkt && ok; ++kt) {
                 const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
                 ok = mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag);
@@ -143,20 +158,20 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_tc_kernel(const HessParam
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int row = warp * 16 + i * 4 + rsub;  // token row inside the k-tile
-                    const int64_t kidx = (int64_t)kt * kKT + row;
-                    const bool rvalid = kidx < n;
-                    int64_t tok = 0;
-                    if (rvalid) tok = tl ? (int64_t)tl[kidx] : off + kidx;
-                    const __nv_bfloat16 *xrow = P.X + tok * P.ldx;
+                    const bool rvalid = tok_cur[i] >= 0;
+                    const __nv_bfloat16 *xrow = P.X + (int64_t)(rvalid ? tok_cur[i] : 0) * P.ldx;
                     const uint32_t drow = (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4));
 #pragma unroll
                     for (int sub = 0; sub < 8; ++sub) {
                         if (diag && sub >= 4) break;
-                        const int64_t ch = (int64_t)(sub < 4 ? ti : tj) * kTile + (sub & 3) * 64 + chunk * 8;
+                        const int64_t ch = (sub < 4 ? chA : chB) + (sub & 3) * 64;
                         const bool v = rvalid && (ch < C);
                         cp_async16_zfill(stage + sub * kSubBytes + drow, v ? (const void *)(xrow + ch) : (const void *)P.X, v);
                     }
                 }
+                if (kt + 1 < nkt) load_tokens(kt + 1, tok_nxt);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) tok_cur[i] = tok_nxt[i];
                 cp_async_commit();
                 ++pend;
                 ++it;
@@ -198,14 +213,37 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_tc_kernel(const HessParam
                     tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(mh * 256 + cc * 32), v);
                     tmem_ld_wait();
                     if (m < C) {
+                        const bool vec_ok = (C % 4 == 0);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            const int64_t nn = n0 + i;
-                            if (nn < C && nn >= m) {
-                                float val = alpha * __uint_as_float(v[i]);
-                                if (np > 0) val = fmaf(beta, Hb[m * C + nn], val);
-                                Hb[m * C + nn] = val;
-                                if (P.mirror && nn > m) Hb[nn * C + m] = val;
+                        for (int g4 = 0; g4 < 8; ++g4) {
+                            const int64_t nn0 = n0 + 4 * g4;
+                            float val[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) val[e] = alpha * __uint_as_float(v[4 * g4 + e]);
+                            if (vec_ok && nn0 >= m && nn0 + 3 < C) {
+                                float4 *dst = reinterpret_cast<float4 *>(Hb + m * C + nn0);
+                                if (np > 0) {
+                                    const float4 old = *dst;
+                                    val[0] = fmaf(beta, old.x, val[0]); val[1] = fmaf(beta, old.y, val[1]);
+                                    val[2] = fmaf(beta, old.z, val[2]); val[3] = fmaf(beta, old.w, val[3]);
+                                }
+                                *dst = make_float4(val[0], val[1], val[2], val[3]);
+                                if (P.mirror) {
+#pragma unroll
+                                    for (int e = 0; e < 4; ++e)
+                                        if (nn0 + e > m) Hb[(nn0 + e) * C + m] = val[e];
+                                }
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const int64_t nn = nn0 + e;
+                                    if (nn < C && nn >= m) {
+                                        float x = val[e];
+                                        if (np > 0) x = fmaf(beta, Hb[m * C + nn], x);
+                                        Hb[m * C + nn] = x;
+                                        if (P.mirror && nn > m) Hb[nn * C + m] = x;
+                                    }
+                                }
                             }
                         }
                     }
