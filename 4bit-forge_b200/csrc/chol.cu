@@ -21,6 +21,9 @@
 // All arithmetic is fp32 FMA on the SIMT pipe: the solver needs fp32-accurate U, and a
 // split-precision tensor-core variant has not been validated against the oracle.
 #include "common.cuh"
+#include "tcgen05.cuh"
+#include <stdlib.h>
+#include <string.h>
 
 using namespace forge;
 
@@ -267,6 +270,179 @@ __global__ void __launch_bounds__(256, 2) chol_syrk_kernel(float *__restrict__ A
     }
 }
 
+// ---- syrk on the tensor cores -----------------------------------------------------------------------
+// Same update,  T[i-tile, j-tile] -= P_i P_j^T  (P = the 64 panel columns just factored), as a TF32 x3 GEMM with
+// the fp32 accumulator in TMEM.  Both operands come from the TRANSPOSED copy of the panel in the upper triangle,
+// Lt[cb + k][rb + i] = L[rb + i][cb + k], whose rows are contiguous along the tile rows: exactly the MN-major
+// [8 K rows][128] pieces the tcgen05 path of the column solver uses (hi/lo split, three MMAs per k-step, see
+// tcgen05.cuh).  K = 64 is eight k-steps; the kernel is bound by the read-modify-write of the trailing matrix
+// in HBM, not by the tensor pipe.  Persistent CTAs walk the lower-triangular tiles of all matrices.
+constexpr int kSyrkThreads = 160;
+constexpr int kSyrkStages = 4;
+constexpr int kSyrkStageBytes = 4 * forge::tc::kPieceBytes;   // Ahi, Alo, Bhi, Blo
+constexpr size_t kSyrkSmem = (size_t)kSyrkStages * kSyrkStageBytes + 1024 + 256;
+
+__global__ void __launch_bounds__(kSyrkThreads, 3) chol_syrk_tc_kernel(float *__restrict__ Aall, int64_t C, int k, int nb,
+                                                                        int nt, int32_t *status) {
+    using namespace forge::tc;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *ring = smem_raw + (smem_base - smem_u32(smem_raw));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(ring + kSyrkStages * kSyrkStageBytes);  // full[4], empty[4], acc
+    uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + 9);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
+    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + kSyrkStages), bar_acc = smem_u32(bars + 8);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (int s = 0; s < kSyrkStages; ++s) {
+            mbar_init(bar_full + 8 * s, 128);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        mbar_init(bar_acc, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 4) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
+                     "r"(128u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    const int64_t cb = (int64_t)k * NB, rb = cb + NB;
+    const int64_t m = C - rb;                       // order of the trailing matrix
+    const int ntri = nt * (nt + 1) / 2;
+    const int total = nb * ntri;
+    uint32_t it = 0, acc_it = 0;
+    constexpr int kSteps = NB / kKS;                // 8
+
+    if (warp < 4) {
+        const int jA = tid >> 5, c4 = tid & 31;
+        const uint32_t sw_off[2] = {piece_offset(jA, c4), piece_offset(jA + 4, c4)};
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+            const int b = tile / ntri;
+            int p = tile % ntri, ti = 0;
+            while (p > ti) { p -= ti + 1; ++ti; }   // lower triangle: row ti holds ti + 1 tiles
+            const int tj = p;
+            float *A = Aall + (int64_t)b * C * C;
+            const int64_t i0 = (int64_t)ti * 128, j0 = (int64_t)tj * 128;
+            const bool diag = (ti == tj);
+            const bool a_ok = (i0 + 4 * c4) < m, b_ok = (j0 + 4 * c4) < m;
+            const float *srcA = A + cb * C + rb + i0 + 4 * c4;
+            const float *srcB = A + cb * C + rb + j0 + 4 * c4;
+            // ---- operands: eight k-steps, loaded four at a time through registers
+#pragma unroll 1
+            for (int half = 0; half < 2 && ok; ++half) {
+                float4 ra[4][2], rbv[4][2];
+#pragma unroll
+                for (int d = 0; d < 4; ++d)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int64_t row = (int64_t)(half * 4 + d) * kKS + jA + 4 * h;
+                        ra[d][h] = a_ok ? *reinterpret_cast<const float4 *>(srcA + row * C) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (!diag) rbv[d][h] = b_ok ? *reinterpret_cast<const float4 *>(srcB + row * C) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                for (int d = 0; d < 4; ++d) {
+                    if (!ok) break;
+                    const uint32_t s = it % kSyrkStages, ph = (it / kSyrkStages) & 1u;
+                    ok = mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag);
+                    if (!ok) break;
+                    uint8_t *stage = ring + s * kSyrkStageBytes;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        float4 hi, lo;
+                        split4(ra[d][h], hi, lo);
+                        *reinterpret_cast<float4 *>(stage + 0 * kPieceBytes + sw_off[h]) = hi;
+                        *reinterpret_cast<float4 *>(stage + 1 * kPieceBytes + sw_off[h]) = lo;
+                        if (!diag) {
+                            split4(rbv[d][h], hi, lo);
+                            *reinterpret_cast<float4 *>(stage + 2 * kPieceBytes + sw_off[h]) = hi;
+                            *reinterpret_cast<float4 *>(stage + 3 * kPieceBytes + sw_off[h]) = lo;
+                        }
+                    }
+                    fence_proxy_async();
+                    mbar_arrive(bar_full + 8 * s);
+                    ++it;
+                }
+            }
+            // ---- epilogue: T -= acc, one row per thread
+            if (ok) ok = mbar_wait(bar_acc, acc_it & 1u, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            ++acc_it;
+            if (!ok) break;
+            tc_fence_after();
+            const int64_t row = i0 + tid;
+            float *Crow = A + (rb + row) * C + rb + j0;
+#pragma unroll 1
+            for (int qd = 0; qd < 4; ++qd) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(qd * 32), v);
+                tmem_ld_wait();
+                if (row < m) {
+#pragma unroll
+                    for (int g4 = 0; g4 < 8; ++g4) {
+                        const int64_t col = j0 + qd * 32 + g4 * 4;
+                        if (col + 3 < m) {
+                            float4 *dst = reinterpret_cast<float4 *>(Crow + qd * 32 + g4 * 4);
+                            float4 o = *dst;
+                            o.x -= __uint_as_float(v[4 * g4 + 0]); o.y -= __uint_as_float(v[4 * g4 + 1]);
+                            o.z -= __uint_as_float(v[4 * g4 + 2]); o.w -= __uint_as_float(v[4 * g4 + 3]);
+                            *dst = o;
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e)
+                                if (col + e < m) Crow[qd * 32 + g4 * 4 + e] -= __uint_as_float(v[4 * g4 + e]);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+        }
+    } else {
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+            int p = tile % ntri, ti = 0;
+            while (p > ti) { p -= ti + 1; ++ti; }
+            const bool diag = (ti == p);
+            for (int ks = 0; ks < kSteps && ok; ++ks) {
+                const uint32_t s = it % kSyrkStages, ph = (it / kSyrkStages) & 1u;
+                ok = mbar_wait(bar_full + 8 * s, ph, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t st = smem_base + s * kSyrkStageBytes;
+                    const uint64_t ahi = make_desc_tf32(st), alo = make_desc_tf32(st + kPieceBytes);
+                    const uint64_t bhi = diag ? ahi : make_desc_tf32(st + 2 * kPieceBytes);
+                    const uint64_t blo = diag ? alo : make_desc_tf32(st + 3 * kPieceBytes);
+                    const uint32_t id = idesc_tf32(128);
+                    umma_tf32(tmem_base, ahi, bhi, id, ks > 0 ? 1u : 0u);
+                    umma_tf32(tmem_base, alo, bhi, id, 1u);
+                    umma_tf32(tmem_base, ahi, blo, id, 1u);
+                    umma_commit(bar_empty + 8 * s);
+                }
+                __syncwarp();
+                ++it;
+            }
+            if (!ok) break;
+            if (lane == 0) umma_commit(bar_acc);
+            __syncwarp();
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && tid == 0 && status) atomicExch(status, FORGE_ERR_TIMEOUT);
+    if (warp == 4) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(128u) : "memory");
+    }
+}
+
 // ---- triangular inverse, block column j: M[below,j] = -(M[below,below] L[below,j]) Dinv_j -------
 __global__ void __launch_bounds__(256, 3) trtri_step_kernel(const float *__restrict__ Aall, float *__restrict__ Uall,
                                                           int64_t C, int j, int nblk,
@@ -371,9 +547,16 @@ __global__ void zero_lower_kernel(float *__restrict__ Uall, int64_t C) {
     if (t < C && k < t) U[t * C + k] = 0.0f;
 }
 
-__global__ void info_clear_kernel(int32_t *info, int nb) {
+__global__ void info_clear_kernel(int32_t *info, int nb, int32_t *status) {
     const int b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b < nb) info[b] = 0;
+    if (b == 0) *status = 0;
+}
+
+// a bounded wait of a tensor-core kernel ran out: report every matrix of the batch as not factorised
+__global__ void status_to_info_kernel(int32_t *info, int nb, const int32_t *status) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < nb && *status != 0 && info[b] == 0) info[b] = 0x40000000;
 }
 
 }  // namespace
@@ -383,19 +566,36 @@ extern "C" int64_t forge_chol_workspace_bytes(int nb, int64_t C) {
     return (int64_t)nb * nblk * 2 * NB * NB * (int64_t)sizeof(float) + 256;
 }
 
+extern "C" int64_t forge_chol_workspace_bytes(int nb, int64_t C);
 static void launch_factor(float *A, int nb, int64_t C, float *U, float *udiag, int32_t *info, float *dinv, int vec,
                           cudaStream_t st) {
+    // the last 256 bytes of the workspace hold the status word of the tensor-core kernels
+    int32_t *status = reinterpret_cast<int32_t *>(reinterpret_cast<char *>(dinv) + forge_chol_workspace_bytes(nb, C) - 256);
     const int nblk = (int)cdiv(C, NB);
-    info_clear_kernel<<<(nb + 127) / 128, 128, 0, st>>>(info, nb); FORGE_NOTE_LAUNCH();
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaFuncSetAttribute(chol_syrk_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSyrkSmem);
+        attr_done = true;
+    }
+    const char *env = getenv("FORGE_SYRK_IMPL");
+    const bool syrk_simt = env && strcmp(env, "simt") == 0;   // cross-checks: plain-FMA trailing update
+    info_clear_kernel<<<(nb + 127) / 128, 128, 0, st>>>(info, nb, status); FORGE_NOTE_LAUNCH();
     for (int k = 0; k < nblk; ++k) {
         chol_diag_kernel<<<nb, 256, 0, st>>>(A, C, k, nblk, dinv, U, udiag, info); FORGE_NOTE_LAUNCH();
         const int64_t m = C - (int64_t)(k + 1) * NB;
         if (m > 0) {
             const unsigned nt = (unsigned)cdiv(m, TM);
             chol_panel_kernel<<<dim3(nt, nb), 256, 0, st>>>(A, C, k, nblk, dinv, vec); FORGE_NOTE_LAUNCH();
-            chol_syrk_kernel<<<dim3(nt, nt, nb), 256, 0, st>>>(A, C, k, vec); FORGE_NOTE_LAUNCH();
+            if (vec && !syrk_simt) {
+                const int total = nb * (int)(nt * (nt + 1) / 2);
+                const int grid = total < 148 * 3 ? total : 148 * 3;
+                chol_syrk_tc_kernel<<<grid, kSyrkThreads, kSyrkSmem, st>>>(A, C, k, nb, (int)nt, status); FORGE_NOTE_LAUNCH();
+            } else {
+                chol_syrk_kernel<<<dim3(nt, nt, nb), 256, 0, st>>>(A, C, k, vec); FORGE_NOTE_LAUNCH();
+            }
         }
     }
+    status_to_info_kernel<<<(nb + 127) / 128, 128, 0, st>>>(info, nb, status); FORGE_NOTE_LAUNCH();
 }
 
 extern "C" int forge_chol_factor_batched(float *A, int nb, int64_t C, float *udiag, int32_t *info, void *ws,

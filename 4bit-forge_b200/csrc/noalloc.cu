@@ -28,7 +28,9 @@ using namespace forge;
 namespace {
 
 constexpr int64_t kMaxC = 4096;
-constexpr int64_t kScratchFloats = (kMaxC / 64) * 2 * 64 * 64;  // one (Dinv, Dinv^T) pair per 64-column block
+// one (Dinv, Dinv^T) pair per 64-column block, plus the 256-byte tail that forge_chol_workspace_bytes reserves
+// for the status word of the tensor-core kernels
+constexpr int64_t kScratchFloats = (kMaxC / 64) * 2 * 64 * 64 + 64;
 
 // In host code this name is only a handle for the runtime, not a device address: the address the
 // kernels can use comes from cudaGetSymbolAddress below.

@@ -26,6 +26,14 @@
 #include <string.h>
 
 using namespace forge;
+using forge::tc::kKS;
+using forge::tc::kPieceBytes;
+using forge::tc::idesc_tf32;
+using forge::tc::make_desc_tf32;
+using forge::tc::piece_offset;
+using forge::tc::umma_tf32;
+using forge::tc::tf32_round;
+using forge::tc::split4;
 
 namespace {
 
@@ -328,8 +336,6 @@ __global__ void __launch_bounds__(128, 3) solve_kernel(const SolveParams p) {
 // issues the MMAs and commits.  Every wait is bounded; a CTA that gives up sets the status word.
 // ================================================================================================
 constexpr int kTcThreads = 160;
-constexpr int kKS = 8;                              // columns j per k-step
-constexpr int kPieceBytes = kKS * kBlk * 4;         // 4 KB
 constexpr int kTcStageBytes = 4 * kPieceBytes;      // Ehi, Elo, Uhi, Ulo
 constexpr int kTcStages = 2;
 constexpr int kTcPrefetch = 4;                      // far k-steps held in registers ahead of the ring
@@ -338,44 +344,7 @@ constexpr int kUsubFloats = kSub * kUsubLd;
 constexpr size_t kTcSmem = (size_t)kTcStages * kTcStageBytes + 1024 + 2 * kUsubFloats * sizeof(float) +
                            kSub * kBlk * sizeof(float) + kBlk * sizeof(float) + 256;
 
-// Instruction descriptor: D fp32, A/B tf32, both MN-major, M = 128, N given.
-__device__ __forceinline__ uint32_t idesc_tf32(uint32_t n) {
-    return (1u << 4) | (2u << 7) | (2u << 10) | (1u << 15) | (1u << 16) | ((n >> 3) << 17) | ((128u >> 4) << 24);
-}
-
-// MN-major operands of 32-bit elements must use the "128-byte swizzle with 32-byte base" layout (type 1):
-// an atom is 4 K rows of 128 bytes (32 elements along MN), inside which the 32-byte chunk index is XORed
-// with the row index.  A piece is [MN block (4)][K group (2)][4 rows][128 B]: next MN block 1 KB further
-// (leading byte offset), next group of 4 K rows 512 B further (stride byte offset).
-__device__ __forceinline__ uint64_t make_desc_tf32(uint32_t saddr) {
-    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(1024 >> 4) << 16) | ((uint64_t)(512 >> 4) << 32) |
-           (1ull << 46) | (1ull << 61);
-}
-// byte offset inside a piece of the 16-byte chunk c4 (0..31 along MN) of K row j (0..7)
-__device__ __forceinline__ uint32_t piece_offset(int j, int c4) {
-    const int rr = j & 3;
-    return (uint32_t)((c4 >> 3) * 1024 + (j >> 2) * 512 + rr * 128 + (((((c4 & 7) >> 1) ^ rr)) << 5) + ((c4 & 1) << 4));
-}
-__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                          uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-        :
-        : "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
-        : "memory");
-}
 __device__ __forceinline__ void rows_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-
-__device__ __forceinline__ float tf32_round(float v) {
-    return __uint_as_float((__float_as_uint(v) + 0x1000u) & 0xFFFFE000u);
-}
-__device__ __forceinline__ void split4(const float4 v, float4 &hi, float4 &lo) {
-    hi.x = tf32_round(v.x); hi.y = tf32_round(v.y); hi.z = tf32_round(v.z); hi.w = tf32_round(v.w);
-    lo.x = tf32_round(__fsub_rn(v.x, hi.x)); lo.y = tf32_round(__fsub_rn(v.y, hi.y));
-    lo.z = tf32_round(__fsub_rn(v.z, hi.z)); lo.w = tf32_round(__fsub_rn(v.w, hi.w));
-}
 
 template <int MODE, bool SPARSE>
 __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolveParams p, int32_t *status) {
