@@ -63,6 +63,11 @@ __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc, boo
     const int sz = pred ? 16 : 0;
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(gsrc), "r"(sz));
 }
+__device__ __forceinline__ void cp_async4(void *smem_dst, const void *gsrc, bool pred) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    const int sz = pred ? 4 : 0;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(d), "l"(gsrc), "r"(sz));
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
@@ -339,7 +344,7 @@ constexpr int kTcThreads = 160;
 constexpr int kTcStageBytes = 4 * kPieceBytes;      // Ehi, Elo, Uhi, Ulo
 constexpr int kTcStages = 2;
 constexpr int kTcPrefetch = 4;                      // far k-steps held in registers ahead of the ring
-constexpr int kUsubLd = 2 * kSub;                    // row stride of the staged triangle: 32 values + 32 zeros
+constexpr int kUsubLd = kSub;                        // staged triangle: row t holds U[t][t+1 ...], zero padded
 constexpr int kUsubFloats = kSub * kUsubLd;
 constexpr size_t kTcSmem = (size_t)kTcStages * kTcStageBytes + 1024 + 2 * kUsubFloats * sizeof(float) +
                            kSub * kBlk * sizeof(float) + kBlk * sizeof(float) + 256;
@@ -376,7 +381,6 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    for (int i = tid; i < 2 * kUsubFloats; i += kTcThreads) Usub[i] = 0.0f;  // columns 32..63 stay zero
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -470,13 +474,15 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
             for (int sb = 0; sb < 4; ++sb) {
                 const int64_t cs = bs + (int64_t)sb * kSub;
                 float *us = Usub + (sb & 1) * kUsubFloats;
-                // (1) the 32x32 triangle U[cs.., cs..] for the in-register part: 256 float4, two per thread
+                // (1) the strict upper triangle of U[cs.., cs..] for the in-register part, row t stored from its
+                // first useful element: us[t][k] = U[cs+t][cs+t+1+k] (zero past the row end), so that the column
+                // loop reads a row with aligned vector loads whatever t is.  4-byte copies: the source is unaligned.
 #pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    const int v = tid + 128 * i;
-                    const int jj = v >> 3, k = (v & 7) * 4;
-                    const bool okl = (cs + jj < C) && (cs + k < C);
-                    cp_async16(us + jj * kUsubLd + k, okl ? (U + (cs + jj) * C + cs + k) : U, okl);
+                for (int i = 0; i < 8; ++i) {
+                    const int v = tid + 128 * i;            // 1024 elements, 8 per thread
+                    const int jj = v >> 5, k = v & 31;
+                    const bool okl = (k < kSub - 1 - jj) && (cs + jj < C) && (cs + jj + 1 + k < C);
+                    cp_async4(us + jj * kUsubLd + k, okl ? (U + (cs + jj) * C + cs + jj + 1 + k) : U, okl);
                 }
                 cp_async_commit();
                 // (2) near update: the previous sub-block's errors go to the later columns of the block
@@ -555,10 +561,22 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
                 uint8_t *qp = p.q + ((int64_t)b * C + cs) * R + r;
                 float *ep = E + cs * R + r;
                 float *wp = Wt + cs * R + r;
+                float inv_s = 0.0f, nq0s = 0.0f;
 #pragma unroll 1
                 for (int t = 0; t < kSub; ++t) {
                     const int64_t c = cs + t;
+                    // the row of U this column propagates along: in flight while the column is quantised
+                    float4 u4[kSub / 4];
+                    {
+                        const float4 *urow = reinterpret_cast<const float4 *>(us + t * kUsubLd);
+#pragma unroll
+                        for (int k4 = 0; k4 < kSub / 4; ++k4) u4[k4] = urow[k4];
+                    }
                     const float sc = s_nx, q0 = q0_nx;
+                    if (!uniform_meta || t == 0) {
+                        inv_s = __fdiv_rn(1.0f, __fadd_rn(sc, kEps));
+                        nq0s = -__fmul_rn(q0, sc);
+                    }
                     if (!uniform_meta && t + 1 < kSub) load_meta<MODE>(p, b, u, r, c + 1, active, s_nx, q0_nx);
                     float err = 0.0f;
                     if (c < C) {
@@ -577,8 +595,16 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
                         float deq = 0.0f;
                         uint8_t qb = 0;
                         const bool keep = SPARSE ? (((maskbits >> t) & 1u) != 0u) : true;
-                        if (keep && (active || !SPARSE)) quantize_scalar(x[0], sc, q0, maxq, err, deq, qb);
-                        else err = x[0];
+                        if (keep && (active || !SPARSE)) {
+                            // quantize_scalar with the reciprocal and -q0*s hoisted (same operations, same rounding)
+                            float q = fminf(fmaxf(fmaf(x[0], inv_s, q0), 0.0f), maxq);
+                            q = __fsub_rn(__fadd_rn(q, 12582912.0f), 12582912.0f);
+                            deq = fmaf(q, sc, nq0s);
+                            err = __fsub_rn(x[0], deq);
+                            qb = (uint8_t)(int)q;
+                        } else {
+                            err = x[0];
+                        }
                         if (p.alt) err = __fsub_rn(w32[0], deq);  // inversion-free form propagates w - deq
                         if (active) {
                             *qp = qb;
@@ -588,14 +614,17 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
                     }
                     qp += R; ep += R; wp += R;
                     es[t * kBlk + tid] = err;
-                    // x[k] <- x[k+1] - U[t][t+1+k] * err ; beyond the triangle the staged row reads zero
-                    const float *urow = us + t * kUsubLd + t + 1;
+                    // x[k] <- x[k+1] - U[t][t+1+k] * err ; past the end of the row the staged value is zero
 #pragma unroll
-                    for (int k = 0; k < kSub - 1; ++k) {
-                        x[k] = fmaf(-urow[k], err, x[k + 1]);
-                        w32[k] = w32[k + 1];
+                    for (int k4 = 0; k4 < kSub / 4; ++k4) {
+                        x[4 * k4 + 0] = fmaf(-u4[k4].x, err, x[4 * k4 + 1]);
+                        x[4 * k4 + 1] = fmaf(-u4[k4].y, err, x[4 * k4 + 2]);
+                        x[4 * k4 + 2] = fmaf(-u4[k4].z, err, x[4 * k4 + 3]);
+                        if (k4 < kSub / 4 - 1) x[4 * k4 + 3] = fmaf(-u4[k4].w, err, x[4 * k4 + 4]);
                     }
                     x[kSub - 1] = 0.0f;
+#pragma unroll
+                    for (int k = 0; k < kSub - 1; ++k) w32[k] = w32[k + 1];
                     w32[kSub - 1] = 0.0f;
                 }
                 if (SPARSE && active && (cs < C)) p.M[((int64_t)b * ((C + 31) / 32) + (cs >> 5)) * R + r] = maskbits;
