@@ -527,11 +527,13 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
                     }
                 }
                 // (3) x = W - acc for the 32 columns of this sub-block
-                float x[kSub], w32[kSub];
+                // es[.][tid] is this thread's own column of the scratch: the near update above has consumed the previous
+                // sub-block's errors, so it now holds this sub-block's original weights until each is replaced by its error
+                float x[kSub];
 #pragma unroll
                 for (int i = 0; i < kSub; ++i) {
-                    w32[i] = (active && (cs + i < C)) ? Wt[(cs + i) * R + r] : 0.0f;
-                    x[i] = w32[i];
+                    x[i] = (active && (cs + i < C)) ? Wt[(cs + i) * R + r] : 0.0f;
+                    es[i * kBlk + tid] = x[i];
                 }
                 if (bs > 0 || sb > 0) {
                     if (ok) ok = mbar_wait(bar_acc, acc_it & 1u, abort_flag);
@@ -572,6 +574,7 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
 #pragma unroll
                         for (int k4 = 0; k4 < kSub / 4; ++k4) u4[k4] = urow[k4];
                     }
+                    const float w_t = es[t * kBlk + tid];   // the column's original weight; replaced by its error below
                     const float sc = s_nx, q0 = q0_nx;
                     if (!uniform_meta || t == 0) {
                         inv_s = __fdiv_rn(1.0f, __fadd_rn(sc, kEps));
@@ -605,7 +608,7 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
                         } else {
                             err = x[0];
                         }
-                        if (p.alt) err = __fsub_rn(w32[0], deq);  // inversion-free form propagates w - deq
+                        if (p.alt) err = __fsub_rn(w_t, deq);  // inversion-free form propagates w - deq
                         if (active) {
                             *qp = qb;
                             if (p.write_deq) *wp = deq;
@@ -623,9 +626,6 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
                         if (k4 < kSub / 4 - 1) x[4 * k4 + 3] = fmaf(-u4[k4].w, err, x[4 * k4 + 4]);
                     }
                     x[kSub - 1] = 0.0f;
-#pragma unroll
-                    for (int k = 0; k < kSub - 1; ++k) w32[k] = w32[k + 1];
-                    w32[kSub - 1] = 0.0f;
                 }
                 if (SPARSE && active && (cs < C)) p.M[((int64_t)b * ((C + 31) / 32) + (cs >> 5)) * R + r] = maskbits;
             }
