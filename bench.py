@@ -373,12 +373,18 @@ def run_ours(args, rank, world, local_rank):
                        else (1400.0, "fallback sustained"))
     n_loc = len(my_ids)
     hess_flops = float((2.0 * counts * (Hd * Hd + I * I)).sum())
+    # the kernel computes only the 256x256 tiles on or above the diagonal: flops it actually executes
+    def _tri(c):
+        nt = (c + 255) // 256
+        return nt * (nt + 1) // 2 * 256 * 256
+    hess_exec_flops = float((2.0 * counts * (_tri(Hd) + _tri(I))).sum())
     elems = n_loc * 3 * I * Hd
     alg_bytes = {
         "forge_hessian_grouped": None,
         "forge_quant_grid": elems * 2 + 8 * elems / 128,
         "forge_gptq_solve_batched": elems * (2 + 1),
         "forge_chol_inv_upper_batched": n_loc * (2 * Hd * Hd + I * I) * 4 * 2,
+        "forge_chol_factor_batched": n_loc * (Hd * Hd + I * I) * 4 * 2,
         "forge_hessian_gather_damp": n_loc * (2 * Hd * Hd + I * I) * 4 * 2,
         "forge_hessian_scan": n_loc * (Hd * Hd + I * I) * 4,
         "forge_pack_int4": elems * 1.5,
@@ -397,9 +403,19 @@ def run_ours(args, rank, world, local_rank):
             roofline = {"kernel": top, "bound": "hbm", "achieved": ach, "peak": hbm_peak, "unit": "GB/s",
                         "frac": ach / hbm_peak, "traffic": None, "peak_source": hbm_src,
                         "note": "fp32-FMA / MUFU issue bound kernel; algorithmic bytes over its device time"}
+        if top == "forge_quant_grid" and recipe["quantization_scale"] == "mse":
+            # the shrink-factor search does 2 MUFU operations (lg2, ex2) per element-candidate: its real ceiling is the
+            # special-function pipe (16 lanes/clk/SM), not HBM
+            sm_hz = (clk or {}).get("sm_mhz") or 1965.0
+            mufu_peak = 16.0 * 148 * sm_hz * 1e6
+            ec = 100.0 * elems
+            roofline["mufu"] = {"element_candidates_per_s": ec / t_s, "mufu_ops_per_s": 2 * ec / t_s,
+                                "peak_mufu_ops_per_s": mufu_peak, "frac": 2 * ec / t_s / mufu_peak}
         t_h = phases.get("forge_hessian_grouped", 0.0) / 1e3
         roofline["hessian_tflops"] = hess_flops / t_h / 1e12 if t_h > 0 else None
         roofline["hessian_frac_of_bf16_peak"] = (hess_flops / t_h / 1e12 / tf_peak) if t_h > 0 else None
+        roofline["hessian_executed_tflops"] = hess_exec_flops / t_h / 1e12 if t_h > 0 else None
+        roofline["hessian_executed_frac_of_bf16_peak"] = (hess_exec_flops / t_h / 1e12 / tf_peak) if t_h > 0 else None
 
     cpu_base = None
     if rank == 0 and not args.no_cpu_baseline:
