@@ -133,68 +133,94 @@ struct CholWs {
     float *dinv;  // [nb][nblk][2][NB][NB]  (0: Dinv, 1: Dinv^T)
 };
 
-// ---- diag: factor + invert the diagonal block of step k (one CTA per matrix) -----------------
-__global__ void __launch_bounds__(256) chol_diag_kernel(float *__restrict__ Aall, int64_t C, int k, int nblk,
-                                                         float *__restrict__ dinv_all, float *__restrict__ Uall,
-                                                         float *__restrict__ udiag, int32_t *__restrict__ info) {
-    __shared__ float D[NB][NB + 1];
-    __shared__ float Di[NB][NB + 1];
+// ---- diag: factor + invert the diagonal block of step k (one CTA of 64 threads per matrix) -----------------
+// Thread i owns row i of the 64x64 block in registers (the full symmetric row, so that no update needs a
+// predicate).  Column j: thread j takes the square root of its pivot, every thread scales its entry of column j
+// and publishes it through shared memory, then subtracts its multiple of column j from the rest of its row
+// (right-looking).  The inverse is then one forward substitution per thread (thread c solves L x = e_c), reading
+// L rows as broadcast float4 from shared memory, with four partial sums to shorten the dependent chain.
+// Everything is statically indexed: no shared-memory round trip for the matrix, two 64-thread barriers per column.
+__global__ void __launch_bounds__(64) chol_diag_kernel(float *__restrict__ Aall, int64_t C, int k, int nblk,
+                                                        float *__restrict__ dinv_all, float *__restrict__ Uall,
+                                                        float *__restrict__ udiag, int32_t *__restrict__ info) {
+    __shared__ __align__(16) float Ls[NB][NB];   // the factor, row-major (upper part zero)
+    __shared__ float col[2][NB];                  // column j of the factor, double buffered
+    __shared__ float invd[NB];
     __shared__ int bad_col;
-    const int b = blockIdx.x, tid = threadIdx.x;
+    const int b = blockIdx.x, i = threadIdx.x;
     float *A = Aall + (int64_t)b * C * C;
     const int64_t cb = (int64_t)k * NB;
     const int nbk = (int)imin64(NB, C - cb);
-    if (tid == 0) bad_col = -1;
-    for (int e = tid; e < NB * NB; e += 256) {
-        const int r = e / NB, c = e % NB;
-        float v = (r == c) ? 1.0f : 0.0f;
-        if (r < nbk && c < nbk && c <= r) v = A[(cb + r) * C + cb + c];
-        if (c > r) v = 0.0f;
-        D[r][c] = v;
+    if (i == 0) bad_col = -1;
+    float a[NB];
+    // the block is symmetric on entry as far as it is used: read the row from the lower triangle and its mirror
+#pragma unroll
+    for (int j = 0; j < NB; ++j) {
+        float v = (i == j) ? 1.0f : 0.0f;         // identity padding of a partial last block
+        if (i < nbk && j < nbk) v = (j <= i) ? A[(cb + i) * C + cb + j] : A[(cb + j) * C + cb + i];
+        a[j] = v;
     }
     __syncthreads();
-    for (int j = 0; j < nbk; ++j) {
-        if (tid == 0) {
-            const float piv = D[j][j];
+#pragma unroll
+    for (int j = 0; j < NB; ++j) {
+        if (i == j) {
+            const float piv = a[j];
             if (!(piv > 0.0f) && bad_col < 0) bad_col = j;
-            D[j][j] = sqrtf(piv);
+            const float d = sqrtf(piv);
+            col[j & 1][j] = d;
+            invd[j] = __fdiv_rn(1.0f, d);
         }
         __syncthreads();
-        const float inv = __fdiv_rn(1.0f, D[j][j]);
-        if (tid > j && tid < nbk) D[tid][j] = __fmul_rn(D[tid][j], inv);
+        const float inv = invd[j];
+        float lij = (i == j) ? col[j & 1][j] : __fmul_rn(a[j], inv);
+        a[j] = lij;
+        if (i != j) col[j & 1][i] = lij;
         __syncthreads();
-        // trailing update of the lower triangle: D[i][l] -= D[i][j]*D[l][j], i >= l > j
-        for (int e = tid; e < NB * NB; e += 256) {
-            const int i = e / NB, l = e % NB;
-            if (l > j && i >= l && i < nbk) D[i][l] = fmaf(-D[i][j], D[l][j], D[i][l]);
+        if (j + 1 < NB) {
+            const float *cj = col[j & 1];
+#pragma unroll
+            for (int l = j + 1; l < NB; ++l) a[l] = fmaf(-lij, cj[l], a[l]);
         }
-        __syncthreads();
     }
-    // inverse of the lower-triangular block, one column per thread (forward substitution)
-    if (tid < NB) {
-        const int c = tid;
-        for (int i = 0; i < NB; ++i) {
-            float s = (i == c) ? 1.0f : 0.0f;
-            if (i < c) { Di[i][c] = 0.0f; continue; }
-            for (int l = c; l < i; ++l) s = fmaf(-D[i][l], Di[l][c], s);
-            Di[i][c] = __fdiv_rn(s, D[i][i]);
-        }
+    // publish the factor (lower part) for the substitution
+#pragma unroll
+    for (int j = 0; j < NB; ++j) Ls[i][j] = (j <= i) ? a[j] : 0.0f;
+    if (i < nbk) {
+#pragma unroll
+        for (int j = 0; j < NB; ++j)
+            if (j <= i && j < nbk) A[(cb + i) * C + cb + j] = a[j];
     }
     __syncthreads();
+    // column c = i of the inverse: forward substitution  x_r = (delta_rc - sum_{l<r} L[r][l] x_l) / L[r][r]
+    float x[NB];
+#pragma unroll
+    for (int r = 0; r < NB; ++r) {
+        float s0 = (r == i) ? 1.0f : 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+        const float4 *Lr = reinterpret_cast<const float4 *>(&Ls[r][0]);
+#pragma unroll
+        for (int l4 = 0; l4 < (r + 3) / 4; ++l4) {
+            const float4 lv = Lr[l4];              // entries at and beyond column r are skipped below
+            if (4 * l4 + 0 < r) s0 = fmaf(-lv.x, x[4 * l4 + 0], s0);
+            if (4 * l4 + 1 < r) s1 = fmaf(-lv.y, x[4 * l4 + 1], s1);
+            if (4 * l4 + 2 < r) s2 = fmaf(-lv.z, x[4 * l4 + 2], s2);
+            if (4 * l4 + 3 < r) s3 = fmaf(-lv.w, x[4 * l4 + 3], s3);
+        }
+        x[r] = __fmul_rn(__fadd_rn(__fadd_rn(s0, s1), __fadd_rn(s2, s3)), invd[r]);
+    }
+    // outputs: L (lower part of A), Dinv and its transpose, the diagonal block of the scaled inverse, udiag, info
     float *dinv = dinv_all + ((int64_t)b * nblk + k) * 2 * NB * NB;
-    float *U = Uall + (int64_t)b * C * C;
-    for (int e = tid; e < NB * NB; e += 256) {
-        const int r = e / NB, c = e % NB;
-        dinv[e] = Di[r][c];
-        dinv[NB * NB + e] = Di[c][r];
-        if (r < nbk && c < nbk) {
-            if (c <= r) A[(cb + r) * C + cb + c] = D[r][c];
-            // diagonal block of the row-scaled inverse  diag(L) L^-1  (unit diagonal)
-            if (Uall) U[(cb + r) * C + cb + c] = (c < r) ? __fmul_rn(D[r][r], Di[r][c]) : ((c == r) ? 1.0f : 0.0f);
+    float *U = Uall ? Uall + (int64_t)b * C * C : nullptr;
+#pragma unroll
+    for (int r = 0; r < NB; ++r) {
+        dinv[r * NB + i] = x[r];                  // Dinv[r][c = i]
+        dinv[NB * NB + i * NB + r] = x[r];        // Dinv^T[c][r]
+        if (U && r < nbk && i < nbk) {
+            // diagonal block of  diag(L) L^-1  (unit diagonal, zero above it)
+            U[(cb + r) * C + cb + i] = (i < r) ? __fmul_rn(Ls[r][r], x[r]) : ((i == r) ? 1.0f : 0.0f);
         }
     }
-    if (tid < nbk) udiag[(int64_t)b * C + (C - 1 - (cb + tid))] = __fdiv_rn(1.0f, D[tid][tid]);
-    if (tid == 0 && bad_col >= 0 && info[b] == 0) info[b] = (int32_t)(cb + bad_col + 1);
+    if (i < nbk) udiag[(int64_t)b * C + (C - 1 - (cb + i))] = invd[i];
+    if (i == 0 && bad_col >= 0 && info[b] == 0) info[b] = (int32_t)(cb + bad_col + 1);
 }
 
 // ---- panel: rows below the diagonal block <- rows * Dinv^T; also stored transposed above ------
@@ -581,7 +607,7 @@ static void launch_factor(float *A, int nb, int64_t C, float *U, float *udiag, i
     const bool syrk_simt = env && strcmp(env, "simt") == 0;   // cross-checks: plain-FMA trailing update
     info_clear_kernel<<<(nb + 127) / 128, 128, 0, st>>>(info, nb, status); FORGE_NOTE_LAUNCH();
     for (int k = 0; k < nblk; ++k) {
-        chol_diag_kernel<<<nb, 256, 0, st>>>(A, C, k, nblk, dinv, U, udiag, info); FORGE_NOTE_LAUNCH();
+        chol_diag_kernel<<<nb, NB, 0, st>>>(A, C, k, nblk, dinv, U, udiag, info); FORGE_NOTE_LAUNCH();
         const int64_t m = C - (int64_t)(k + 1) * NB;
         if (m > 0) {
             const unsigned nt = (unsigned)cdiv(m, TM);
