@@ -350,6 +350,30 @@ __global__ void hessian_simt_kernel(const HessParams P) {
 
 }  // namespace
 
+// Self-test of the bounded wait every tensor-core kernel here relies on: one CTA waits on an mbarrier that nothing
+// ever arrives on, with a budget of `budget_cycles`; the wait gives up, the kernel writes FORGE_ERR_TIMEOUT to the
+// status word and returns normally.  Nothing faults or hangs: this is how a lost producer would surface.
+__global__ void bounded_wait_selftest_kernel(int32_t *status, long long budget_cycles) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const bool ok = mbar_wait(smem_u32(&bar), 0u, &abort_flag, budget_cycles);
+    __syncthreads();
+    if (threadIdx.x == 0) *status = ok ? FORGE_OK : FORGE_ERR_TIMEOUT;
+}
+
+extern "C" int forge_selftest_bounded_wait(int32_t *status, int64_t budget_cycles, void *stream) {
+    FORGE_REQUIRE(status, "null pointer");
+    FORGE_REQUIRE(budget_cycles > 0 && budget_cycles <= 2000000000LL, "budget must be in (0, 2e9] cycles");
+    bounded_wait_selftest_kernel<<<1, 64, 0, (cudaStream_t)stream>>>(status, (long long)budget_cycles); FORGE_NOTE_LAUNCH();
+    return check_launch("forge_selftest_bounded_wait");
+}
+
 extern "C" int forge_hessian_grouped(const void *X_bf16, int64_t ldx, int64_t C, const int32_t *token_idx,
                                      const int64_t *offsets, int nb, float *H, const int64_t *n_prev, int flags,
                                      int32_t *status, void *stream) {

@@ -28,13 +28,14 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok;
 }
 // Bounded wait: false when the budget ran out or another thread of the CTA already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                          long long budget = kWaitBudget) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (clock64() - t0 > kWaitBudget) {
+        if (clock64() - t0 > budget) {
             *abort_flag = 1;
             return false;
         }

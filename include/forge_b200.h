@@ -79,6 +79,11 @@ int forge_hessian_grouped(const void *X_bf16, int64_t ldx, int64_t C, const int3
                           const int64_t *offsets, int nb, float *H, const int64_t *n_prev,
                           int flags, int32_t *status, void *stream);
 
+/* Self-test of the bounded device-side wait used by every tensor-core kernel: a one-CTA kernel waits on a barrier
+ * nothing arrives on for at most budget_cycles (<= 2e9), gives up, writes FORGE_ERR_TIMEOUT to *status (device int32)
+ * and returns normally.  No counterpart in the reference (it has no device-side waits). */
+int forge_selftest_bounded_wait(int32_t *status, int64_t budget_cycles, void *stream);
+
 /* n_prev[b] += offsets[b+1]-offsets[b]  (GPTQ.update's num_samples.add_, forge/gptq.py:80) */
 int forge_counts_add(int64_t *n_prev, const int64_t *offsets, int nb, void *stream);
 
