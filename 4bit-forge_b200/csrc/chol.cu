@@ -296,20 +296,44 @@ __global__ void __launch_bounds__(256, 2) chol_syrk_kernel(float *__restrict__ A
     }
 }
 
-// ---- syrk on the tensor cores -----------------------------------------------------------------------
-// Same update,  T[i-tile, j-tile] -= P_i P_j^T  (P = the 64 panel columns just factored), as a TF32 x3 GEMM with
-// the fp32 accumulator in TMEM.  Both operands come from the TRANSPOSED copy of the panel in the upper triangle,
-// Lt[cb + k][rb + i] = L[rb + i][cb + k], whose rows are contiguous along the tile rows: exactly the MN-major
-// [8 K rows][128] pieces the tcgen05 path of the column solver uses (hi/lo split, three MMAs per k-step, see
-// tcgen05.cuh).  K = 64 is eight k-steps; the kernel is bound by the read-modify-write of the trailing matrix
-// in HBM, not by the tensor pipe.  Persistent CTAs walk the lower-triangular tiles of all matrices.
+// ---- trailing update on the tensor cores ---------------------------------------------------------
+// T[i-tile, j-tile] -= P_i P_j^T  where P = the K panel columns [kb, kb + K) already factored, T = the block of the
+// matrix whose rows start at r0 (to the end) and whose columns are [r0, r0 + ncols): the lower-triangular tiles of
+// that block.  A TF32 x3 GEMM with the fp32 accumulator in TMEM.  Both operands come from the TRANSPOSED copy of
+// the panel in the upper triangle, Lt[kb + k][r0 + i] = L[r0 + i][kb + k], whose rows are contiguous along the tile
+// rows: exactly the MN-major [8 K rows][128] pieces the tcgen05 path of the column solver uses (hi/lo split, three
+// MMAs per k-step, see tcgen05.cuh).  The factorisation is blocked on two levels: inside an outer block of
+// kOuter columns every 64-column panel updates only the rest of that outer block (K = 64, ncols <= kOuter - 64),
+// and the outer block as a whole updates the matrix behind it once (K = kOuter), so the read-modify-write of the
+// trailing matrix in HBM happens once per kOuter columns instead of once per 64.  Persistent CTAs walk the tiles
+// of all matrices.
+constexpr int kOuter = 256;
+
+// tile p of one matrix -> (ti, tj): rows of tiles ti = 0.. hold min(ti + 1, ntj) tiles each
+__device__ __forceinline__ void syrk_tile(int p, int ntj, int &ti, int &tj) {
+    const int tri = ntj * (ntj + 1) / 2;
+    if (p < tri) {
+        ti = 0;
+        while (p > ti) { p -= ti + 1; ++ti; }
+        tj = p;
+    } else {
+        p -= tri;
+        ti = ntj + p / ntj;
+        tj = p % ntj;
+    }
+}
+__host__ __device__ __forceinline__ int syrk_tiles(int nti, int ntj) {
+    return ntj * (ntj + 1) / 2 + (nti - ntj) * ntj;
+}
+
 constexpr int kSyrkThreads = 160;
 constexpr int kSyrkStages = 4;
 constexpr int kSyrkStageBytes = 4 * forge::tc::kPieceBytes;   // Ahi, Alo, Bhi, Blo
 constexpr size_t kSyrkSmem = (size_t)kSyrkStages * kSyrkStageBytes + 1024 + 256;
 
-__global__ void __launch_bounds__(kSyrkThreads, 3) chol_syrk_tc_kernel(float *__restrict__ Aall, int64_t C, int k, int nb,
-                                                                        int nt, int32_t *status) {
+__global__ void __launch_bounds__(kSyrkThreads, 3) chol_syrk_tc_kernel(float *__restrict__ Aall, int64_t C, int64_t kb, int K,
+                                                                        int64_t r0, int64_t ncols, int nb,
+                                                                        int32_t *status) {
     using namespace forge::tc;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -339,12 +363,14 @@ __global__ void __launch_bounds__(kSyrkThreads, 3) chol_syrk_tc_kernel(float *__
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
 
-    const int64_t cb = (int64_t)k * NB, rb = cb + NB;
-    const int64_t m = C - rb;                       // order of the trailing matrix
-    const int ntri = nt * (nt + 1) / 2;
+    const int64_t cb = kb, rb = r0;
+    const int64_t m = C - rb;                       // rows of the block being updated
+    const int64_t ncol = ncols < m ? ncols : m;     // its columns
+    const int nti = (int)((m + 127) / 128), ntj = (int)((ncol + 127) / 128);
+    const int ntri = syrk_tiles(nti, ntj);
     const int total = nb * ntri;
     uint32_t it = 0, acc_it = 0;
-    constexpr int kSteps = NB / kKS;                // 8
+    const int kSteps = K / kKS;                     // 8 K rows per step
 
     if (warp < 4) {
         const int jA = tid >> 5, c4 = tid & 31;
@@ -352,18 +378,17 @@ __global__ void __launch_bounds__(kSyrkThreads, 3) chol_syrk_tc_kernel(float *__
         bool ok = true;
         for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
             const int b = tile / ntri;
-            int p = tile % ntri, ti = 0;
-            while (p > ti) { p -= ti + 1; ++ti; }   // lower triangle: row ti holds ti + 1 tiles
-            const int tj = p;
+            int ti, tj;
+            syrk_tile(tile % ntri, ntj, ti, tj);
             float *A = Aall + (int64_t)b * C * C;
             const int64_t i0 = (int64_t)ti * 128, j0 = (int64_t)tj * 128;
             const bool diag = (ti == tj);
             const bool a_ok = (i0 + 4 * c4) < m, b_ok = (j0 + 4 * c4) < m;
             const float *srcA = A + cb * C + rb + i0 + 4 * c4;
             const float *srcB = A + cb * C + rb + j0 + 4 * c4;
-            // ---- operands: eight k-steps, loaded four at a time through registers
+            // ---- operands: K / 8 k-steps, loaded four at a time through registers
 #pragma unroll 1
-            for (int half = 0; half < 2 && ok; ++half) {
+            for (int half = 0; half < K / 32 && ok; ++half) {
                 float4 ra[4][2], rbv[4][2];
 #pragma unroll
                 for (int d = 0; d < 4; ++d)
@@ -407,6 +432,7 @@ __global__ void __launch_bounds__(kSyrkThreads, 3) chol_syrk_tc_kernel(float *__
             float *Crow = A + (rb + row) * C + rb + j0;
 #pragma unroll 1
             for (int qd = 0; qd < 4; ++qd) {
+                if (j0 + qd * 32 >= ncol) break;            // columns outside the block (same for the whole CTA)
                 uint32_t v[32];
                 tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(qd * 32), v);
                 tmem_ld_wait();
@@ -414,16 +440,19 @@ __global__ void __launch_bounds__(kSyrkThreads, 3) chol_syrk_tc_kernel(float *__
 #pragma unroll
                     for (int g4 = 0; g4 < 8; ++g4) {
                         const int64_t col = j0 + qd * 32 + g4 * 4;
-                        if (col + 3 < m) {
+                        if (col + 3 < ncol) {
                             float4 *dst = reinterpret_cast<float4 *>(Crow + qd * 32 + g4 * 4);
-                            float4 o = *dst;
-                            o.x -= __uint_as_float(v[4 * g4 + 0]); o.y -= __uint_as_float(v[4 * g4 + 1]);
-                            o.z -= __uint_as_float(v[4 * g4 + 2]); o.w -= __uint_as_float(v[4 * g4 + 3]);
-                            *dst = o;
+                            // fire-and-forget reduction in L2 instead of load / subtract / store: the epilogue
+                            // has no load round trip, and since every element gets exactly one addition per launch
+                            // the result does not depend on any ordering
+                            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst),
+                                         "f"(-__uint_as_float(v[4 * g4 + 0])), "f"(-__uint_as_float(v[4 * g4 + 1])),
+                                         "f"(-__uint_as_float(v[4 * g4 + 2])), "f"(-__uint_as_float(v[4 * g4 + 3]))
+                                         : "memory");
                         } else {
 #pragma unroll
                             for (int e = 0; e < 4; ++e)
-                                if (col + e < m) Crow[qd * 32 + g4 * 4 + e] -= __uint_as_float(v[4 * g4 + e]);
+                                if (col + e < ncol) Crow[qd * 32 + g4 * 4 + e] -= __uint_as_float(v[4 * g4 + e]);
                         }
                     }
                 }
@@ -433,9 +462,9 @@ __global__ void __launch_bounds__(kSyrkThreads, 3) chol_syrk_tc_kernel(float *__
     } else {
         bool ok = true;
         for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
-            int p = tile % ntri, ti = 0;
-            while (p > ti) { p -= ti + 1; ++ti; }
-            const bool diag = (ti == p);
+            int ti, tj;
+            syrk_tile(tile % ntri, ntj, ti, tj);
+            const bool diag = (ti == tj);
             for (int ks = 0; ks < kSteps && ok; ++ks) {
                 const uint32_t s = it % kSyrkStages, ph = (it / kSyrkStages) & 1u;
                 ok = mbar_wait(bar_full + 8 * s, ph, abort_flag);
@@ -605,20 +634,38 @@ static void launch_factor(float *A, int nb, int64_t C, float *U, float *udiag, i
     }
     const char *env = getenv("FORGE_SYRK_IMPL");
     const bool syrk_simt = env && strcmp(env, "simt") == 0;   // cross-checks: plain-FMA trailing update
+    const char *env2 = getenv("FORGE_CHOL_OUTER");
+    const int64_t outer = env2 ? atoi(env2) : kOuter;
     info_clear_kernel<<<(nb + 127) / 128, 128, 0, st>>>(info, nb, status); FORGE_NOTE_LAUNCH();
-    for (int k = 0; k < nblk; ++k) {
-        chol_diag_kernel<<<nb, NB, 0, st>>>(A, C, k, nblk, dinv, U, udiag, info); FORGE_NOTE_LAUNCH();
-        const int64_t m = C - (int64_t)(k + 1) * NB;
-        if (m > 0) {
-            const unsigned nt = (unsigned)cdiv(m, TM);
-            chol_panel_kernel<<<dim3(nt, nb), 256, 0, st>>>(A, C, k, nblk, dinv, vec); FORGE_NOTE_LAUNCH();
-            if (vec && !syrk_simt) {
-                const int total = nb * (int)(nt * (nt + 1) / 2);
-                const int grid = total < 148 * 3 ? total : 148 * 3;
-                chol_syrk_tc_kernel<<<grid, kSyrkThreads, kSyrkSmem, st>>>(A, C, k, nb, (int)nt, status); FORGE_NOTE_LAUNCH();
-            } else {
+    if (!vec || syrk_simt) {
+        // plain right-looking form: every panel updates the whole matrix behind it
+        for (int k = 0; k < nblk; ++k) {
+            chol_diag_kernel<<<nb, NB, 0, st>>>(A, C, k, nblk, dinv, U, udiag, info); FORGE_NOTE_LAUNCH();
+            const int64_t m = C - (int64_t)(k + 1) * NB;
+            if (m > 0) {
+                const unsigned nt = (unsigned)cdiv(m, TM);
+                chol_panel_kernel<<<dim3(nt, nb), 256, 0, st>>>(A, C, k, nblk, dinv, vec); FORGE_NOTE_LAUNCH();
                 chol_syrk_kernel<<<dim3(nt, nt, nb), 256, 0, st>>>(A, C, k, vec); FORGE_NOTE_LAUNCH();
             }
+        }
+    } else {
+        auto update = [&](int64_t kb, int K, int64_t r0, int64_t ncols) {
+            const int64_t m = C - r0, nc = ncols < m ? ncols : m;
+            const int total = nb * syrk_tiles((int)cdiv(m, 128), (int)cdiv(nc, 128));
+            const int grid = total < 148 * 3 ? total : 148 * 3;
+            chol_syrk_tc_kernel<<<grid, kSyrkThreads, kSyrkSmem, st>>>(A, C, kb, K, r0, ncols, nb, status);
+            FORGE_NOTE_LAUNCH();
+        };
+        for (int64_t ob = 0; ob < C; ob += outer) {
+            const int64_t oe = imin64(C, ob + outer);
+            for (int k = (int)(ob / NB); (int64_t)k * NB < oe; ++k) {
+                chol_diag_kernel<<<nb, NB, 0, st>>>(A, C, k, nblk, dinv, U, udiag, info); FORGE_NOTE_LAUNCH();
+                const int64_t rb = (int64_t)(k + 1) * NB, m = C - rb;
+                if (m <= 0) continue;
+                chol_panel_kernel<<<dim3((unsigned)cdiv(m, TM), nb), 256, 0, st>>>(A, C, k, nblk, dinv, vec); FORGE_NOTE_LAUNCH();
+                if (rb < oe) update((int64_t)k * NB, NB, rb, oe - rb);     // the rest of this outer block
+            }
+            if (oe < C) update(ob, (int)(oe - ob), oe, C - oe);           // everything behind the outer block
         }
     }
     status_to_info_kernel<<<(nb + 127) / 128, 128, 0, st>>>(info, nb, status); FORGE_NOTE_LAUNCH();
