@@ -10,6 +10,8 @@
 // element-candidate), not by HBM.
 #include "common.cuh"
 #include <float.h>
+#include <stdlib.h>
+#include <string.h>
 
 using namespace forge;
 
@@ -324,11 +326,240 @@ mse_grid_kernel(const void *__restrict__ Wv, int64_t rows, int64_t C, int64_t G,
     }
 }
 
+// ---- the same search with exact pruning -------------------------------------------------------------------
+// The loss of a candidate is a sum of positive terms, so a candidate whose PARTIAL sum already exceeds the loss of
+// some fully evaluated candidate can never be the first strictly smaller one and is abandoned.  Nothing about the
+// result changes: the candidates that finish are summed in exactly the order described above, and an abandoned one
+// is strictly worse than a finished one (the comparison carries a 1e-4 relative margin, three orders of magnitude
+// above the rounding difference between two summation orders of 128 positive fp32 terms).  What changes is the
+// work: with min-max scales the best shrink factor is close to 1 for most groups, and most of the 100 candidates
+// are dropped after two elements (the extremes of the group) or after their first 16.
+//
+// Mapping: a CTA pass takes 32 consecutive groups; lane = group, so the 32 lanes of a warp evaluate the SAME
+// candidate on 32 groups and leave the loop at about the same time.  Warps draw candidates from a shared counter in
+// ascending order (shrink factor 1.0 first: the likely winners finish early and tighten the bound).  The bound
+// of a group starts from the loss of candidate 0 (evaluated cooperatively by the eight warps, in any order, it is
+// only a bound) and is lowered with atomicMin by every candidate that finishes; a stale read is merely
+// conservative.
+constexpr int kPrThreads = 256;
+constexpr int kPrMaxP = 128;
+constexpr int kPrPitch = 33;          // row pitch (in groups) of the staged values and of the loss table
+constexpr float kPrMargin = 1.0001f;
+
+template <bool BF16, bool ABSMAX>
+__global__ void __launch_bounds__(kPrThreads, 4)
+mse_prune_kernel(const void *__restrict__ Wv, int64_t rows, int64_t C, int64_t G, int bits, int symmetric,
+                 const float *__restrict__ cand, int P, float norm, float *__restrict__ scales,
+                 float *__restrict__ qzeros) {
+    constexpr int GS = 128;
+    __shared__ __align__(16) float4 vals_s[32 * kPrPitch];   // [chunk l][group] = elements l, l+32, l+64, l+96
+    __shared__ float loss_s[kPrMaxP * kPrPitch];             // [candidate][group]
+    __shared__ float part_s[8][2][32];
+    __shared__ float meta_s[4][32];                          // scale, zero, smallest and largest value
+    __shared__ int bound_s[32];                              // positive floats order like their bit patterns
+    __shared__ int next_s;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float maxq = (float)((1 << bits) - 1);
+    const int64_t n_groups = rows * G;
+    const float kMagic = 12582912.0f;  // 1.5 * 2^23: adding it rounds to the nearest integer, ties to even
+    const unsigned full = 0xffffffffu;
+
+    for (int64_t g0 = (int64_t)blockIdx.x * 32; g0 < n_groups; g0 += (int64_t)gridDim.x * 32) {
+        // ---- stage 32 groups
+        for (int idx = tid; idx < 32 * GS; idx += kPrThreads) {
+            const int gl = idx / GS, e = idx % GS;
+            const int64_t g = g0 + gl;
+            float x = 0.0f;
+            if (g < n_groups) {
+                const int64_t r = g / G, c = (g % G) * GS + e;
+                if (c < C) {
+                    x = BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(Wv)[r * C + c])
+                             : reinterpret_cast<const float *>(Wv)[r * C + c];
+                }
+            }
+            reinterpret_cast<float *>(vals_s)[((e & 31) * kPrPitch + gl) * 4 + (e >> 5)] = x;
+        }
+        if (tid == 0) next_s = 0;
+        __syncthreads();
+        const bool valid = (g0 + lane) < n_groups;
+        // ---- extremes of each group (order-free), and from them the min-max scale / zero
+        {
+            float mn = 1e30f, mx = -1e30f;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float4 t = vals_s[(4 * warp + k) * kPrPitch + lane];
+                mx = fmaxf(fmaxf(fmaxf(mx, t.x), fmaxf(t.y, t.z)), t.w);
+                mn = fminf(fminf(fminf(mn, t.x), fminf(t.y, t.z)), t.w);
+            }
+            part_s[warp][0][lane] = mn;
+            part_s[warp][1][lane] = mx;
+            __syncthreads();
+            if (warp == 0) {
+                mn = part_s[0][0][lane];
+                mx = part_s[0][1][lane];
+#pragma unroll
+                for (int w = 1; w < 8; ++w) {
+                    mn = fminf(mn, part_s[w][0][lane]);
+                    mx = fmaxf(mx, part_s[w][1][lane]);
+                }
+                float sg, q0g;
+                if (!ABSMAX) {
+                    sg = valid ? scales[g0 + lane] : 1.0f;
+                    q0g = valid ? qzeros[g0 + lane] : 0.0f;
+                } else if (symmetric) {
+                    sg = fmaf(2.0f / maxq, fmaxf(fabsf(mn), fabsf(mx)), kEps);
+                    q0g = 0.5f * (maxq + 1.0f);
+                } else {
+                    sg = __fadd_rn(__fdiv_rn(__fsub_rn(mx, mn), maxq), kEps);
+                    q0g = fminf(fmaxf(rintf(__fdiv_rn(-mn, sg)), 0.0f), maxq);
+                }
+                meta_s[0][lane] = sg;
+                meta_s[1][lane] = q0g;
+                meta_s[2][lane] = mn;
+                meta_s[3][lane] = mx;
+            }
+        }
+        __syncthreads();
+        const float vmin = meta_s[2][lane], vmax = meta_s[3][lane];
+        const float sg = meta_s[0][lane], q0g = meta_s[1][lane];
+        const float xmin = symmetric ? 0.0f : -__fmul_rn(sg, q0g);
+        const float hiq = kMagic + maxq;
+        auto element_loss = [&](float v, float sc, float rcp, float q0, float offq) {
+            // q = clamp(rint(v*rcp + q0), 0, maxq), carried as q + magic
+            float t = __fadd_rn(fmaf(v, rcp, q0), kMagic);
+            t = fminf(fmaxf(t, kMagic), hiq);
+            const float diff = fmaf(__fsub_rn(t, offq), sc, -v);
+            const float e = fmaxf(fabsf(diff), 1e-20f);
+            const float lg = __fmul_rn(fast_lg2(e), 0.693147182f);                  // __logf
+            return fast_ex2(__fmul_rn(__fmul_rn(lg, norm), 1.44269502f));           // __expf
+        };
+        // ---- starting bound: candidate 0, sixteen elements per warp
+        {
+            const float sc = __fmul_rn(sg, cand[0]);
+            const float rcp = __fdiv_rn(1.0f, __fadd_rn(sc, kEps));
+            const float q0 = symmetric ? q0g : fminf(fmaxf(rintf(__fmul_rn(-xmin, rcp)), 0.0f), maxq);
+            const float offq = kMagic + q0;
+            float acc = 0.0f;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float4 t = vals_s[(4 * warp + k) * kPrPitch + lane];
+                acc += element_loss(t.x, sc, rcp, q0, offq) + element_loss(t.y, sc, rcp, q0, offq) +
+                       element_loss(t.z, sc, rcp, q0, offq) + element_loss(t.w, sc, rcp, q0, offq);
+            }
+            part_s[warp][0][lane] = acc;
+            __syncthreads();
+            if (warp == 0) {
+                float b = part_s[0][0][lane];
+#pragma unroll
+                for (int w = 1; w < 8; ++w) b += part_s[w][0][lane];
+                bound_s[lane] = __float_as_int(b * kPrMargin);
+            }
+            __syncthreads();
+        }
+        // ---- candidates, drawn in ascending order
+        while (true) {
+            int p = 0;
+            if (lane == 0) p = atomicAdd(&next_s, 1);
+            p = __shfl_sync(full, p, 0);
+            if (p >= P) break;
+            const float sc = __fmul_rn(sg, cand[p]);
+            const float rcp = __fdiv_rn(1.0f, __fadd_rn(sc, kEps));
+            const float q0 = symmetric ? q0g : fminf(fmaxf(rintf(__fmul_rn(-xmin, rcp)), 0.0f), maxq);
+            const float offq = kMagic + q0;
+            // bit-reversed visit order + 6-entry stack = the reference's shfl_down tree (see mse_grid_kernel)
+            float st[6];
+            // the smallest and the largest value are two of the 128 terms (any two, if all values are equal), and
+            // under a shrunk scale they are the clipped ones: most candidates are dropped right here
+            const float two = element_loss(vmin, sc, rcp, q0, offq) + element_loss(vmax, sc, rcp, q0, offq);
+            bool alive = valid && !(two > __int_as_float(*reinterpret_cast<volatile int *>(&bound_s[lane])));
+            if (!__any_sync(full, alive)) {
+                loss_s[p * kPrPitch + lane] = FLT_MAX;
+                continue;
+            }
+#pragma unroll
+            for (int idx = 0; idx < 32; ++idx) {
+                const int l = ((idx & 1) << 4) | ((idx & 2) << 2) | (idx & 4) | ((idx & 8) >> 2) | ((idx & 16) >> 4);
+                const float4 t = vals_s[l * kPrPitch + lane];
+                float acc = element_loss(t.x, sc, rcp, q0, offq);
+                acc = __fadd_rn(acc, element_loss(t.y, sc, rcp, q0, offq));
+                acc = __fadd_rn(acc, element_loss(t.z, sc, rcp, q0, offq));
+                acc = __fadd_rn(acc, element_loss(t.w, sc, rcp, q0, offq));
+                const int pc = __builtin_popcount(idx);
+                st[pc] = acc;
+#pragma unroll
+                for (int m = 0; m < 5; ++m) {
+                    if (((idx >> m) & 1) == 0) break;
+                    st[pc - 1 - m] = __fadd_rn(st[pc - 1 - m], st[pc - m]);
+                }
+                if ((idx & 3) == 3 && idx != 31) {
+                    float partial = st[0];
+#pragma unroll
+                    for (int k = 1; k < 6; ++k)
+                        if (k < __builtin_popcount(idx + 1)) partial += st[k];
+                    const float bnd = __int_as_float(*reinterpret_cast<volatile int *>(&bound_s[lane]));
+                    alive = alive && !(partial > bnd);
+                    if (!__any_sync(full, alive)) break;
+                }
+            }
+            loss_s[p * kPrPitch + lane] = alive ? st[0] : FLT_MAX;
+            if (alive) atomicMin(&bound_s[lane], __float_as_int(st[0] * kPrMargin));
+        }
+        __syncthreads();
+        // ---- first strictly smaller loss in candidate order wins == lexicographic minimum of (loss, candidate)
+#pragma unroll 1
+        for (int k = 0; k < 4; ++k) {
+            const int gl = 4 * warp + k;
+            if (g0 + gl >= n_groups) break;
+            float best = FLT_MAX;
+            int bp = 0x7fffffff;
+            for (int p = lane; p < P; p += 32) {
+                const float l = loss_s[p * kPrPitch + gl];
+                if (l < best) { best = l; bp = p; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(full, best, o);
+                const int op = __shfl_xor_sync(full, bp, o);
+                if (ob < best || (ob == best && op < bp)) { best = ob; bp = op; }
+            }
+            if (lane == 0) {
+                const float sgl = meta_s[0][gl], q0l = meta_s[1][gl];
+                float bs = sgl, bq = q0l;
+                if (best < FLT_MAX && bp < P) {
+                    bs = __fmul_rn(sgl, cand[bp]);
+                    if (!symmetric) {
+                        const float xm = -__fmul_rn(sgl, q0l);
+                        const float rc = __fdiv_rn(1.0f, __fadd_rn(bs, kEps));
+                        bq = fminf(fmaxf(rintf(__fmul_rn(-xm, rc)), 0.0f), maxq);
+                    }
+                }
+                scales[g0 + gl] = bs;
+                qzeros[g0 + gl] = bq;
+            }
+        }
+        __syncthreads();
+    }
+}
+
 template <bool ABSMAX>
 int launch_grid(const void *W, int w_dtype, int64_t rows, int64_t C, int gs, int bits, int symmetric,
                 const float *cand, int n_cand, float norm, float *scales, float *qzeros, cudaStream_t st) {
     const int64_t G = cdiv(C, gs);
     const int64_t n_groups = rows * G;
+    const char *impl = getenv("FORGE_GRID_IMPL");
+    const bool exhaustive = impl && strcmp(impl, "exhaustive") == 0;   // cross-checks: evaluate every candidate fully
+    if (n_cand > 0 && n_cand <= kPrMaxP && gs == 128 && !exhaustive) {
+        const int blocks = (int)imin64(cdiv(n_groups, 32), 148 * 4 * 2);
+        if (w_dtype == FORGE_DTYPE_BF16) {
+            mse_prune_kernel<true, ABSMAX><<<blocks, kPrThreads, 0, st>>>(W, rows, C, G, bits, symmetric, cand, n_cand,
+                                                                         norm, scales, qzeros);
+        } else {
+            mse_prune_kernel<false, ABSMAX><<<blocks, kPrThreads, 0, st>>>(W, rows, C, G, bits, symmetric, cand, n_cand,
+                                                                          norm, scales, qzeros);
+        }
+        FORGE_NOTE_LAUNCH();
+        return check_launch("forge_quant_grid(mse, pruned)");
+    }
     if (n_cand > 0 && n_cand <= kMseThreads && (gs == 32 || gs == 64 || gs == 128)) {
         const int tpg = (n_cand + kMseCPT - 1) / kMseCPT;                 // threads per group
         int gpc = kMseThreads / tpg;                                       // groups per CTA pass

@@ -494,3 +494,35 @@ def test_inversion_free_form_matches_reference_form(C, R, sparse):
         else:
             q_ref = O.gptq_solver(Wt, (T / T.diag()[:, None]).contiguous(), Sel, Zel, 4)
         assert float((q1[b].cpu() == q_ref.T).float().mean()) >= 0.995
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,C,dtype,sym,P", [
+    (96, 2048, torch.bfloat16, False, 100),
+    (37, 768, torch.float32, False, 100),
+    (64, 1024, torch.bfloat16, True, 100),
+    (5, 200, torch.float32, False, 7),       # ragged last group, fewer than 32 groups
+    (33, 128, torch.bfloat16, False, 128),
+])
+def test_pruned_scale_search_equals_exhaustive(rows, C, dtype, sym, P, monkeypatch):
+    """Abandoning a candidate whose partial loss exceeds a finished candidate's loss must not change the result:
+    bit-identical scales and zeros, on Gaussian rows, rows with outliers (best shrink far from 1) and zero rows."""
+    from forge import ops
+    g = torch.Generator(device="cuda").manual_seed(rows * 7 + C)
+    W = torch.randn(rows, C, generator=g, device="cuda") * 0.02
+    out = torch.rand(rows, C, generator=g, device="cuda") < 0.01
+    W = torch.where(out & (torch.arange(rows, device="cuda")[:, None] % 3 == 1), W * 25.0, W)
+    W[rows // 2] = 0.0
+    W = W.to(dtype)
+    cand = torch.linspace(1.0, 0.2, P, dtype=torch.float32, device="cuda")
+    monkeypatch.setenv("FORGE_GRID_IMPL", "exhaustive")
+    s_ref, z_ref = ops.quant_grid(W, 128, 4, sym, cand, 2.4)
+    monkeypatch.delenv("FORGE_GRID_IMPL")
+    s, z = ops.quant_grid(W, 128, 4, sym, cand, 2.4)
+    assert torch.equal(s, s_ref) and torch.equal(z, z_ref)
+    # the refinement entry point (scales given) goes through the same kernels
+    s0, z0 = ops.quant_grid(W, 128, 4, sym)
+    s2, z2 = ops.quant_grid_mse(W, 128, 4, sym, cand, 2.4, s0.clone(), z0.clone())
+    assert torch.equal(s2, s_ref) and torch.equal(z2, z_ref)
+    if P >= 100:
+        assert float((s_ref < s0).float().mean()) > 0.2      # the search did move scales
