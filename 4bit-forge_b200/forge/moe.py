@@ -40,19 +40,24 @@ class MoEQuantConfig:
 
 def swiglu_expert_forward(X, token_lists, offsets_host, Wg, Wu):
     """Down-projection calibration input of every expert, packed by expert: bf16(silu(x Wg^T) * (x Wu^T)).
-    Library bf16 GEMMs (fp32 accumulate), exactly what the HF MoE block computes before down_proj."""
+    Library bf16 GEMMs (fp32 accumulate), exactly what the HF MoE block computes before down_proj.
+    The routed rows are gathered once for all experts and the activation runs once over the packed buffer,
+    so an expert costs two GEMM launches and nothing else."""
     total = int(offsets_host[-1])
     I = Wg.shape[1]
-    act = torch.empty((max(total, 1), I), dtype=torch.bfloat16, device=X.device)
+    if total == 0:
+        return torch.empty((1, I), dtype=torch.bfloat16, device=X.device)
+    Xg = X.index_select(0, token_lists[:total].long())
+    gate = torch.empty((total, I), dtype=torch.bfloat16, device=X.device)
+    up = torch.empty((total, I), dtype=torch.bfloat16, device=X.device)
     for e in range(Wg.shape[0]):
         a, b = int(offsets_host[e]), int(offsets_host[e + 1])
         if b == a:
             continue
-        xe = X.index_select(0, token_lists[a:b].long())
-        g = xe @ Wg[e].T
-        u = xe @ Wu[e].T
-        act[a:b] = torch.nn.functional.silu(g) * u
-    return act
+        torch.mm(Xg[a:b], Wg[e].T, out=gate[a:b])
+        torch.mm(Xg[a:b], Wu[e].T, out=up[a:b])
+    del Xg
+    return torch.nn.functional.silu(gate, inplace=True).mul_(up)
 
 
 class MoELayerQuantizer:
