@@ -303,8 +303,8 @@ __global__ void __launch_bounds__(256, 2) chol_syrk_kernel(float *__restrict__ A
 // the panel in the upper triangle, Lt[kb + k][r0 + i] = L[r0 + i][kb + k], whose rows are contiguous along the tile
 // rows: exactly the MN-major [8 K rows][128] pieces the tcgen05 path of the column solver uses (hi/lo split, three
 // MMAs per k-step, see tcgen05.cuh).  The factorisation is blocked on two levels: inside an outer block of
-// kOuter columns every 64-column panel updates only the rest of that outer block (K = 64, ncols <= kOuter - 64),
-// and the outer block as a whole updates the matrix behind it once (K = kOuter), so the read-modify-write of the
+// kOuter columns (twice that for large matrices) every 64-column panel updates only the rest of that outer block
+// (K = 64), and the outer block as a whole updates the matrix behind it once (K = the outer block's width), so the read-modify-write of the
 // trailing matrix in HBM happens once per kOuter columns instead of once per 64.  Persistent CTAs walk the tiles
 // of all matrices.
 constexpr int kOuter = 256;
@@ -634,8 +634,7 @@ static void launch_factor(float *A, int nb, int64_t C, float *U, float *udiag, i
     }
     const char *env = getenv("FORGE_SYRK_IMPL");
     const bool syrk_simt = env && strcmp(env, "simt") == 0;   // cross-checks: plain-FMA trailing update
-    const char *env2 = getenv("FORGE_CHOL_OUTER");
-    const int64_t outer = env2 ? atoi(env2) : kOuter;
+    const int64_t outer = (C >= 4096) ? 2 * kOuter : kOuter;   // measured: wider outer blocks pay from C ~ 4096 on
     info_clear_kernel<<<(nb + 127) / 128, 128, 0, st>>>(info, nb, status); FORGE_NOTE_LAUNCH();
     if (!vec || syrk_simt) {
         // plain right-looking form: every panel updates the whole matrix behind it

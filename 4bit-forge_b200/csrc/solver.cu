@@ -21,6 +21,7 @@
 // access is coalesced across the 128 row-threads; the batched entry point builds Wt from W [R,C] with
 // a tiled transpose-gather and scatters the codes back to [R,C] in the original column order.
 #include "common.cuh"
+#include <type_traits>
 #include "tcgen05.cuh"
 #include <stdlib.h>
 #include <string.h>
@@ -564,15 +565,17 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
                 float *ep = E + cs * R + r;
                 float *wp = Wt + cs * R + r;
                 float inv_s = 0.0f, nq0s = 0.0f;
-#pragma unroll 1
-                for (int t = 0; t < kSub; ++t) {
+                // One column.  W = width of the live window: at column t only x[1 .. 31-t] are still unsolved, so the
+                // loop runs in four quarters with W = 32, 24, 16, 8 and each quarter propagates along W-1 entries only.
+                auto column = [&](auto wtag, const int t) {
+                    constexpr int W = decltype(wtag)::value;
                     const int64_t c = cs + t;
                     // the row of U this column propagates along: in flight while the column is quantised
-                    float4 u4[kSub / 4];
+                    float4 u4[W / 4];
                     {
                         const float4 *urow = reinterpret_cast<const float4 *>(us + t * kUsubLd);
 #pragma unroll
-                        for (int k4 = 0; k4 < kSub / 4; ++k4) u4[k4] = urow[k4];
+                        for (int k4 = 0; k4 < W / 4; ++k4) u4[k4] = urow[k4];
                     }
                     const float w_t = es[t * kBlk + tid];   // the column's original weight; replaced by its error below
                     const float sc = s_nx, q0 = q0_nx;
@@ -619,14 +622,22 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
                     es[t * kBlk + tid] = err;
                     // x[k] <- x[k+1] - U[t][t+1+k] * err ; past the end of the row the staged value is zero
 #pragma unroll
-                    for (int k4 = 0; k4 < kSub / 4; ++k4) {
+                    for (int k4 = 0; k4 < W / 4; ++k4) {
                         x[4 * k4 + 0] = fmaf(-u4[k4].x, err, x[4 * k4 + 1]);
                         x[4 * k4 + 1] = fmaf(-u4[k4].y, err, x[4 * k4 + 2]);
                         x[4 * k4 + 2] = fmaf(-u4[k4].z, err, x[4 * k4 + 3]);
-                        if (k4 < kSub / 4 - 1) x[4 * k4 + 3] = fmaf(-u4[k4].w, err, x[4 * k4 + 4]);
+                        if (k4 < W / 4 - 1) x[4 * k4 + 3] = fmaf(-u4[k4].w, err, x[4 * k4 + 4]);
                     }
-                    x[kSub - 1] = 0.0f;
-                }
+                    x[W - 1] = 0.0f;
+                };
+#pragma unroll 1
+                for (int t = 0; t < 8; ++t) column(std::integral_constant<int, 32>{}, t);
+#pragma unroll 1
+                for (int t = 8; t < 16; ++t) column(std::integral_constant<int, 24>{}, t);
+#pragma unroll 1
+                for (int t = 16; t < 24; ++t) column(std::integral_constant<int, 16>{}, t);
+#pragma unroll 1
+                for (int t = 24; t < 32; ++t) column(std::integral_constant<int, 8>{}, t);
                 if (SPARSE && active && (cs < C)) p.M[((int64_t)b * ((C + 31) / 32) + (cs >> 5)) * R + r] = maskbits;
             }
             // the errors of this block must be visible to the far-phase loads of the next one
