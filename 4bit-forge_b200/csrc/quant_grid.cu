@@ -549,7 +549,9 @@ int launch_grid(const void *W, int w_dtype, int64_t rows, int64_t C, int gs, int
     const char *impl = getenv("FORGE_GRID_IMPL");
     const bool exhaustive = impl && strcmp(impl, "exhaustive") == 0;   // cross-checks: evaluate every candidate fully
     if (n_cand > 0 && n_cand <= kPrMaxP && gs == 128 && !exhaustive) {
-        const int blocks = (int)imin64(cdiv(n_groups, 32), 148 * 4 * 2);
+        // two passes per CTA: short-lived CTAs, so that kernels of a higher-priority stream (the factorisation that the
+        // layer driver runs beside the search) find free slots every few tens of microseconds
+        const int blocks = (int)imin64(cdiv(n_groups, 64), 1 << 30);
         if (w_dtype == FORGE_DTYPE_BF16) {
             mse_prune_kernel<true, ABSMAX><<<blocks, kPrThreads, 0, st>>>(W, rows, C, G, bits, symmetric, cand, n_cand,
                                                                          norm, scales, qzeros);

@@ -36,6 +36,7 @@ class MoEQuantConfig:
     mse_norm: float = 2.4
     expert_chunk: int = 0                  # experts factorised/solved per pass (0 = all at once)
     inversion_free: bool = True            # solve from the Cholesky factor itself, without the triangular inverse
+    overlap_streams: bool = True           # scale search on a second stream beside the (latency-bound) factorisation
 
 
 def swiglu_expert_forward(X, token_lists, offsets_host, Wg, Wu):
@@ -67,22 +68,22 @@ class MoELayerQuantizer:
         self.cfg = cfg
         self.inversion_free = False
         self._status = None
+        self._side = None          # second compute stream (scale search), created on first use
+        self._h2d = None           # copy streams of quantize_experts_host
+        self._d2h = None
+        self._host_out = {}
+
+    def _side_stream(self):
+        if self._side is None:
+            self._side = torch.cuda.Stream(priority=-1)
+        return self._side
 
     # ---- one family of matrices sharing per-slot Hessians -------------------------------------
-    def _factor(self, H, n_samples, Ws):
-        """H [nu,C,C] (consumed: overwritten by U).  Ws: list of weight batches [nu,R,C] that share H.
-        Returns (U, udiag, perm32, info, per-batch wzero handling done)."""
+    def _factor(self, H, perm32, pruned, invalid, Ws, wz):
+        """H [nu,C,C] (consumed: overwritten by U).  Ws: list of weight batches [nu,R,C] that share H; wz: their
+        all-zero-column masks.  Returns one (U, udiag, info) per weight batch."""
         cfg = self.cfg
-        nu, C, _ = H.shape
-        diag, pruned, invalid = ops.hessian_scan(H, n_samples)
-        if cfg.quantization_order == "activation":
-            perm32 = torch.argsort(diag, dim=1, descending=True).to(torch.int32).contiguous()
-        else:
-            perm32 = None
-        for W in Ws:
-            ops.weight_apply_pruned(W, pruned)
-        wz = [ops.weight_zero_cols(W) for W in Ws]
-        shared = all(torch.equal(wz[0], w) for w in wz[1:])
+        shared = all(torch.equal(wz[0], w) for w in wz[1:])      # the one host read of this step
         outs = []
         groups = [wz[0]] if shared else wz
         for gi, wzero in enumerate(groups):
@@ -98,9 +99,12 @@ class MoELayerQuantizer:
             outs.append((U, udiag, info))
         if shared:
             outs = outs * len(Ws)
-        return outs, perm32
+        return outs
 
-    def _solve_family(self, H, n_samples, Ws):
+    def _solve_family(self, H, n_samples, Ws, names=(), gates=None, between=None):
+        """Everything after the Hessian for the weight batches Ws that share it.  names[i]: input name to wait for
+        (gates.need) before Ws[i] is touched.  between(): extra work for the main stream while the factorisation
+        runs beside it (the expert forward)."""
         cfg = self.cfg
         sparse = cfg.algorithm == "sparsegptq"
         cand = None
@@ -111,12 +115,60 @@ class MoELayerQuantizer:
         # rounding of that form, so the sparse path keeps the reference's form)
         self.inversion_free = (bool(cfg.inversion_free) and not sparse
                                and all(W.shape[1] % 4 == 0 and W.shape[2] % 4 == 0 for W in Ws))
-        factors, perm32 = self._factor(H, n_samples, Ws)
+        nu, C, _ = H.shape
+        diag, pruned, invalid = ops.hessian_scan(H, n_samples)
+        if cfg.quantization_order == "activation":
+            perm32 = torch.argsort(diag, dim=1, descending=True).to(torch.int32).contiguous()
+        else:
+            perm32 = None
+
+        def grid_of(W):
+            nb, R, Cw = W.shape
+            return ops.quant_grid(W.view(nb * R, Cw), cfg.group_size, cfg.bits, cfg.symmetric, cand, cfg.mse_norm)
+
+        # The scale grids depend on the weights only (after the dead channels are zeroed), the factorisation on the
+        # Hessian and on which weight columns are all zero.  The factorisation is a chain of small latency-bound
+        # launches: it runs on a high-priority second stream, beside the scale search (special-function bound, many
+        # short CTAs) and the expert forward on the main stream, and the solver waits for both.
+        main = torch.cuda.current_stream()
+        fork = cfg.overlap_streams
+        grids = []
+        for i, W in enumerate(Ws):
+            if gates is not None and i < len(names):
+                gates.need(names[i])
+            ops.weight_apply_pruned(W, pruned)
+            if gates is not None and i < len(Ws) - 1:
+                grids.append(grid_of(W))      # overlaps the arrival of the next weight batch
+        if fork:
+            # host order matters: the main stream's work is queued BEFORE the one host read of the factorisation
+            # (are the zero-column masks equal?), so the GPU never waits for the host, and the factorisation's
+            # launches are queued right after that read, at high priority
+            side = self._side_stream()
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                wz = [ops.weight_zero_cols(W) for W in Ws]
+            for W in Ws[len(grids):]:
+                grids.append(grid_of(W))
+            if between is not None:
+                between()
+            with torch.cuda.stream(side):
+                factors = self._factor(H, perm32, pruned, invalid, Ws, wz)
+            for t in [H, pruned, invalid] + ([perm32] if perm32 is not None else []) + list(Ws):
+                t.record_stream(side)
+            main.wait_stream(side)
+            for U, udiag, info in factors:
+                for t in (U, udiag, info):
+                    t.record_stream(main)
+        else:
+            wz = [ops.weight_zero_cols(W) for W in Ws]
+            factors = self._factor(H, perm32, pruned, invalid, Ws, wz)
+            for W in Ws[len(grids):]:
+                grids.append(grid_of(W))
+            if between is not None:
+                between()
         results = []
-        for W, (U, udiag, info) in zip(Ws, factors):
+        for W, (U, udiag, info), (scales, qzeros) in zip(Ws, factors, grids):
             nb, R, C = W.shape
-            scales, qzeros = ops.quant_grid(W.view(nb * R, C), cfg.group_size, cfg.bits, cfg.symmetric, cand,
-                                            cfg.mse_norm)
             out = ops.gptq_solve_batched(W, U, scales, qzeros, cfg.group_size, cfg.bits, perm=perm32,
                                          udiag=udiag if sparse else None, sparse14=sparse, status=self._status,
                                          form=1 if self.inversion_free else 0)
@@ -149,11 +201,15 @@ class MoELayerQuantizer:
     # ---- the layer ----------------------------------------------------------------------------------
     @torch.no_grad()
     def quantize_experts(self, X: torch.Tensor, topk_ids: Optional[torch.Tensor], Wg: torch.Tensor,
-                         Wu: torch.Tensor, Wd: torch.Tensor, e_begin: int = 0, dense_tail: int = 0):
+                         Wu: torch.Tensor, Wd: torch.Tensor, e_begin: int = 0, dense_tail: int = 0, _gates=None):
         """X [T,Hd] bf16; topk_ids [T,k] int32 (global expert ids); Wg/Wu [n,I,Hd], Wd [n,Hd,I] hold the experts
         this rank owns: first the routed experts e_begin.., then `dense_tail` experts that see every token
         (shared experts).  The weight tensors are updated in place only where a dead input channel forces a
-        column to zero.  Returns {"gate": .., "up": .., "down": .., "counts": ..} with per-matrix results."""
+        column to zero.  Returns {"gate": .., "up": .., "down": .., "counts": ..} with per-matrix results.
+
+        `_gates` (internal, see quantize_experts_host): object whose need(name) makes the current stream wait until
+        the named input ("gate", "up", "down") has arrived, and whose done(name, results) is told when a family's
+        results exist."""
         cfg = self.cfg
         n_local = Wg.shape[0]
         n_routed = n_local - dense_tail
@@ -165,10 +221,8 @@ class MoELayerQuantizer:
         if n_routed > 0:
             counts, offsets, lists = ops.route_build_lists(topk_ids, e_begin, n_routed)
             parts_counts.append(counts.to(torch.int64))
-            total_routed = offsets[-1:]
         else:
             lists = torch.empty(0, dtype=torch.int32, device=dev)
-            total_routed = torch.zeros(1, dtype=torch.int64, device=dev)
         if dense_tail > 0:
             parts_counts.append(torch.full((dense_tail,), T, dtype=torch.int64, device=dev))
         counts64 = torch.cat(parts_counts)
@@ -180,25 +234,34 @@ class MoELayerQuantizer:
             ar = torch.arange(T, dtype=torch.int32, device=dev)
             lists = torch.cat([lists[:n_routed_tok]] + [ar] * dense_tail)
         lists = lists.contiguous()
-        # ---- down-projection inputs (packed by expert)
-        act = swiglu_expert_forward(X, lists, offsets_host, Wg, Wu)
 
         chunk = cfg.expert_chunk if cfg.expert_chunk > 0 else n_local
         res = {"gate": [], "up": [], "down": []}
         status = torch.zeros(1, dtype=torch.int32, device=dev)
         self._status = status
+        act = None
         for c0 in range(0, n_local, chunk):
             c1 = min(n_local, c0 + chunk)
             nb = c1 - c0
             offs = offsets[c0:c1 + 1].contiguous()
             n_samples = counts64[c0:c1].contiguous()
+            # the layer-input Hessians need no weights: they run while the weights may still be on their way
             H1 = torch.empty((nb, Hd, Hd), dtype=torch.float32, device=dev)
             ops.hessian_grouped(X, Hd, lists, offs, H1, mirror=True, status=status)
-            g, u = self._solve_family(H1, n_samples, [Wg[c0:c1], Wu[c0:c1]])
+            def forward():
+                # down-projection inputs of all local experts (packed by expert); zeroing dead input channels in the
+                # weights before does not change them (those channels are zero in every routed row)
+                nonlocal act
+                if act is None:
+                    act = swiglu_expert_forward(X, lists, offsets_host, Wg, Wu)
+
+            g, u = self._solve_family(H1, n_samples, [Wg[c0:c1], Wu[c0:c1]], ("gate", "up"), _gates, forward)
             del H1
+            if _gates is not None:
+                _gates.done("gate_up", (g, u))
             H2 = torch.empty((nb, I, I), dtype=torch.float32, device=dev)
             ops.hessian_grouped(act, I, None, offs, H2, mirror=True, status=status)
-            (d,) = self._solve_family(H2, n_samples, [Wd[c0:c1]])
+            (d,) = self._solve_family(H2, n_samples, [Wd[c0:c1]], ("down",), _gates)
             del H2
             res["gate"].append(g)
             res["up"].append(u)
@@ -207,6 +270,119 @@ class MoELayerQuantizer:
         out["counts"] = counts64
         out["status"] = status
         return out
+
+    # ---- the same layer from host memory ---------------------------------------------------------------
+    _HOST_KEYS = {"gptq": ("weight_packed", "weight_scale", "qzeros"), "sparsegptq": ("wpair",)}
+
+    @torch.no_grad()
+    def quantize_experts_host(self, X, topk_ids, Wg_host, Wu_host, Wd_host, e_begin: int = 0, dense_tail: int = 0,
+                              device=None, ship_results: bool = True, fp8_scale_inv=None):
+        """quantize_experts for weights that live in (pinned) host memory, results delivered to pinned host memory.
+
+        X / topk_ids may be host or device tensors.  Copies run on their own streams and overlap the kernels:
+        the layer-input Hessians start as soon as X has arrived, while gate / up are still being uploaded; down is
+        uploaded during the gate / up solve; the packed gate / up results travel back during the down solve.
+        Requires expert_chunk == 0 (one pass).  Returns (out, host) where `host` maps "gate.weight_packed" etc. to
+        pinned host tensors, valid after the call returns (it synchronises the copy streams); with
+        ship_results=False nothing is copied back (the caller gathers on the device) and `host` is empty.
+
+        fp8 checkpoints (DeepSeek-V3): pass the e4m3 weights [n,R,C] and fp8_scale_inv = (sg, su, sd), host fp32
+        block scales [n, R/128, C/128]; half the bytes cross PCIe and the bf16 weights are materialised on the
+        device (forge/utils/io.py:533-563 of the reference does this on the CPU).  R must be a multiple of 128."""
+        cfg = self.cfg
+        if cfg.expert_chunk:
+            raise ValueError("quantize_experts_host runs the layer in one pass: set expert_chunk = 0")
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        main = torch.cuda.current_stream()
+        if self._h2d is None:
+            self._h2d, self._d2h = torch.cuda.Stream(), torch.cuda.Stream()
+        h2d, d2h = self._h2d, self._d2h
+        keys = self._HOST_KEYS["sparsegptq" if cfg.algorithm == "sparsegptq" else "gptq"]
+        host = {}
+        me = self
+
+        def to_device(t, stream_needed):
+            if t.is_cuda:
+                return t, None
+            d = torch.empty(t.shape, dtype=t.dtype, device=dev)      # allocated on the main stream
+            return d, t
+
+        Xd, Xh = to_device(X, True)
+        idd, idh = to_device(topk_ids, True)
+        hosts = (Wg_host, Wu_host, Wd_host)
+        fp8 = fp8_scale_inv is not None
+        Wg, Wu, Wd = (torch.empty(w.shape, dtype=torch.bfloat16, device=dev) for w in hosts)
+        if fp8:
+            if any(w.shape[1] % 128 for w in hosts):
+                raise ValueError("fp8 block scales need R to be a multiple of 128")
+            raw = [torch.empty(w.shape, dtype=torch.uint8, device=dev) for w in hosts]
+            sinv = [torch.empty(t.shape, dtype=torch.float32, device=dev) for t in fp8_scale_inv]
+            src = [w.view(torch.uint8) for w in hosts]
+        else:
+            raw, sinv, src = [Wg, Wu, Wd], [None] * 3, list(hosts)
+        h2d.wait_stream(main)
+        events = {}
+        with torch.cuda.stream(h2d):
+            if Xh is not None:
+                Xd.copy_(Xh, non_blocking=True)
+            if idh is not None:
+                idd.copy_(idh, non_blocking=True)
+            events["x"] = h2d.record_event()
+            for j in (0, 1, 2):
+                raw[j].copy_(src[j], non_blocking=True)
+                if fp8:
+                    sinv[j].copy_(fp8_scale_inv[j], non_blocking=True)
+                events[("gate", "up", "down")[j]] = h2d.record_event()
+        for t in [Xd, idd] + raw + [t for t in sinv if t is not None]:
+            t.record_stream(h2d)
+
+        def materialise(js):
+            if fp8:
+                for j in js:
+                    n, R, C = raw[j].shape
+                    ops.fp8_block_dequant(raw[j].view(n * R, C), sinv[j].view(-1, sinv[j].shape[-1]),
+                                          out=(Wg, Wu, Wd)[j].view(n * R, C))
+
+        def ship(prefix, r):
+            # device -> pinned host on the return stream, after the kernels that produced r
+            if not ship_results:
+                return
+            d2h.wait_stream(main)
+            with torch.cuda.stream(d2h):
+                for k in keys:
+                    v = r.get(k)
+                    if v is None:
+                        continue
+                    if k == "qzeros":
+                        if cfg.symmetric:
+                            continue
+                        v = v.to(torch.uint8)
+                        name = f"{prefix}.weight_zero_point"
+                    else:
+                        name = f"{prefix}.{k}"
+                    buf = me._host_out.get(name)
+                    if buf is None or buf.shape != v.shape or buf.dtype != v.dtype:
+                        buf = torch.empty(v.shape, dtype=v.dtype).pin_memory()
+                        me._host_out[name] = buf
+                    buf.copy_(v, non_blocking=True)
+                    v.record_stream(d2h)
+                    host[name] = buf
+
+        class Gates:
+            def need(self, name):
+                torch.cuda.current_stream().wait_event(events[name])
+                materialise((("gate", "up", "down").index(name),))
+
+            def done(self, name, results):
+                g, u = results
+                ship("gate", g)
+                ship("up", u)
+
+        main.wait_event(events["x"])
+        out = self.quantize_experts(Xd, idd, Wg, Wu, Wd, e_begin=e_begin, dense_tail=dense_tail, _gates=Gates())
+        ship("down", out["down"])
+        d2h.synchronize()
+        return out, host
 
 
 def _cat_results(parts):

@@ -12,12 +12,14 @@ def _dev(t):
     return t.device
 
 
-def fp8_block_dequant(w_fp8: torch.Tensor, scale_inv: torch.Tensor) -> torch.Tensor:
+def fp8_block_dequant(w_fp8: torch.Tensor, scale_inv: torch.Tensor, out=None) -> torch.Tensor:
     """bf16( fp32(w_fp8) * scale_inv[tile] ) — forge/utils/io.py:533-563, :864-874 on the device."""
     O, I = w_fp8.shape
     nO, nI = scale_inv.shape
     w8 = w_fp8.contiguous().view(torch.uint8)
-    out = torch.empty((O, I), dtype=torch.bfloat16, device=_dev(w_fp8))
+    if out is None:
+        out = torch.empty((O, I), dtype=torch.bfloat16, device=_dev(w_fp8))
+    assert out.dtype == torch.bfloat16 and out.shape == (O, I) and out.is_contiguous()
     call("forge_fp8_block_dequant", ptr(w8), ptr(scale_inv.to(torch.float32).contiguous()), ptr(out), O, I, nO, nI,
          stream_ptr())
     return out

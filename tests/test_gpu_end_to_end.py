@@ -179,3 +179,40 @@ def test_moe_layer_against_per_expert_oracle(algorithm, order, scale, sym):
             else:
                 pk = O.pack_int4(res["qweight"][e].cpu(), res["qzeros"][e].cpu(), gs)
                 assert torch.equal(res["weight_packed"][e].cpu(), pk)
+
+
+@pytest.mark.parametrize("algorithm,sym,fp8", [("gptq", False, False), ("gptq", True, True), ("sparsegptq", True, False)])
+def test_host_api_matches_device_api(algorithm, sym, fp8):
+    """quantize_experts_host (pinned host buffers, copies overlapped on their own streams, scale search on a second
+    stream) returns exactly what quantize_experts returns for device-resident inputs."""
+    from forge import synth, moe, ops
+    shape = synth.LayerShape("tiny", 8, 1, 256, 128, 2048, 2)
+    X = synth.student_t_activations(shape.tokens, shape.hidden, seed=9)
+    ids = synth.route(shape, shape.tokens, seed=9)
+    Wg, Wu, Wd = synth.expert_weights(shape, range(9), seed=9)
+    gs = 32 if algorithm == "sparsegptq" else 128
+    cfg = moe.MoEQuantConfig(bits=4, group_size=gs, symmetric=sym, quantization_scale="mse" if not sym else "absmax",
+                             rel_damp=0.01, algorithm=algorithm)
+    host_w, scales = [Wg, Wu, Wd], None
+    if fp8:
+        enc = [[synth.fp8_block_encode(w.to(DEV)) for w in Wm] for Wm in (Wg, Wu, Wd)]
+        host_w = [torch.stack([q for q, _ in e]).cpu() for e in enc]
+        scales = [torch.stack([s for _, s in e]).float().cpu().pin_memory() for e in enc]
+        Wg, Wu, Wd = [torch.stack([ops.fp8_block_dequant(q, s) for q, s in e]).cpu() for e in enc]
+    ref_q = moe.MoELayerQuantizer(moe.MoEQuantConfig(**{**cfg.__dict__, "overlap_streams": False}))
+    ref = ref_q.quantize_experts(X.to(DEV), ids.to(DEV), Wg.to(DEV), Wu.to(DEV), Wd.to(DEV), e_begin=0, dense_tail=1)
+    qz = moe.MoELayerQuantizer(cfg)
+    for _ in range(2):      # second call reuses the pinned result buffers and the streams
+        out, host = qz.quantize_experts_host(X.pin_memory(), ids.pin_memory(), *[w.pin_memory() for w in host_w],
+                                             e_begin=0, dense_tail=1, fp8_scale_inv=scales)
+        assert int(out["status"].item()) == 0
+        for nm in ("gate", "up", "down"):
+            assert torch.equal(out[nm]["qweight"], ref[nm]["qweight"])
+            assert torch.equal(out[nm]["scales"], ref[nm]["scales"])
+            if algorithm == "sparsegptq":
+                assert torch.equal(host[f"{nm}.wpair"], ref[nm]["wpair"].cpu())
+            else:
+                assert torch.equal(host[f"{nm}.weight_packed"], ref[nm]["weight_packed"].cpu())
+                assert torch.equal(host[f"{nm}.weight_scale"], ref[nm]["weight_scale"].cpu())
+                if not sym:
+                    assert torch.equal(host[f"{nm}.weight_zero_point"], ref[nm]["qzeros"].to(torch.uint8).cpu())
