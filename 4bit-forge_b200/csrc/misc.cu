@@ -301,6 +301,36 @@ __global__ void gather_damp_kernel(const float *__restrict__ H, int64_t C, const
     const uint8_t *wzb = wzero ? wzero + (int64_t)b * C : nullptr;
     const bool inv = invalid ? invalid[b] != 0 : false;
     const int64_t pi = pb ? pb[i] : i;
+    // Fast path (the usual case): natural order and no dead channel / zero column anywhere in this matrix: a pure
+    // index reversal of the row with the damping on the diagonal, 16 bytes per access.
+    if (!pb && (C & 3) == 0) {
+        int flagged = inv ? 1 : 0;
+        for (int64_t c = (int64_t)threadIdx.x * 16; c < C; c += (int64_t)blockDim.x * 16) {
+            if (c + 16 <= C && (C & 15) == 0) {
+                if (prb) { const uint4 f = *reinterpret_cast<const uint4 *>(prb + c); flagged |= (f.x | f.y | f.z | f.w) != 0u; }
+                if (wzb) { const uint4 f = *reinterpret_cast<const uint4 *>(wzb + c); flagged |= (f.x | f.y | f.z | f.w) != 0u; }
+            } else {
+                for (int64_t e = c; e < C && e < c + 16; ++e) flagged |= (prb && prb[e]) || (wzb && wzb[e]);
+            }
+        }
+        if (!__syncthreads_or(flagged)) {
+            const float dmp = damp[b];
+            const float4 *src = reinterpret_cast<const float4 *>(Hb + i * C);
+            float *Arow = A + (int64_t)b * C * C + (C - 1 - i) * C;
+            float *Hrow = Hp_out ? Hp_out + (int64_t)b * C * C + i * C : nullptr;
+            for (int64_t c4 = threadIdx.x; c4 < C / 4; c4 += blockDim.x) {
+                float4 v = src[c4];
+                const int64_t j = 4 * c4;
+                if (i >= j && i < j + 4) {
+                    const int k = (int)(i - j);
+                    if (k == 0) v.x += dmp; else if (k == 1) v.y += dmp; else if (k == 2) v.z += dmp; else v.w += dmp;
+                }
+                if (Hrow) *reinterpret_cast<float4 *>(Hrow + j) = v;
+                *reinterpret_cast<float4 *>(Arow + (C - 4 - j)) = make_float4(v.w, v.z, v.y, v.x);
+            }
+            return;
+        }
+    }
     const bool row_dead = inv || (prb && prb[pi]);
     const bool row_wz = wzb && wzb[i];
     if (!row_dead && !row_wz) {

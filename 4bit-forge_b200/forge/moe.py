@@ -167,11 +167,15 @@ class MoELayerQuantizer:
             if between is not None:
                 between()
         results = []
-        for W, (U, udiag, info), (scales, qzeros) in zip(Ws, factors, grids):
+        merged = self._solve_merged(Ws, factors, grids, perm32) if len(Ws) == 2 and not sparse else None
+        for i, (W, (U, udiag, info), (scales, qzeros)) in enumerate(zip(Ws, factors, grids)):
             nb, R, C = W.shape
-            out = ops.gptq_solve_batched(W, U, scales, qzeros, cfg.group_size, cfg.bits, perm=perm32,
-                                         udiag=udiag if sparse else None, sparse14=sparse, status=self._status,
-                                         form=1 if self.inversion_free else 0)
+            if merged is not None:
+                out = merged[i * nb:(i + 1) * nb]
+            else:
+                out = ops.gptq_solve_batched(W, U, scales, qzeros, cfg.group_size, cfg.bits, perm=perm32,
+                                             udiag=udiag if sparse else None, sparse14=sparse, status=self._status,
+                                             form=1 if self.inversion_free else 0)
             q, M = out if sparse else (out, None)
             G = (C + cfg.group_size - 1) // cfg.group_size
             res = {"qweight": q, "scales": scales.view(nb, R, G), "qzeros": qzeros.view(nb, R, G), "info": info,
@@ -182,6 +186,28 @@ class MoELayerQuantizer:
                 res.update(self._pack(q, res["scales"], res["qzeros"], M))
             results.append(res)
         return results
+
+    def _solve_merged(self, Ws, factors, grids, perm32):
+        """Two weight batches that share one factor (gate and up) in ONE solver launch, when that fills the GPU
+        better: the solver runs one CTA per 128 weight rows, three CTAs per SM, all of equal length, so a launch
+        whose last wave is nearly empty wastes most of a wave; together the two batches waste it once, not twice.
+        Returns the codes [2 nb, R, C] or None (not worth it / not applicable)."""
+        cfg = self.cfg
+        (U0, _, _), (U1, _, _) = factors
+        W0, W1 = Ws
+        if U0 is not U1 or W0.shape != W1.shape:
+            return None
+        nb, R, C = W0.shape
+        slots = 3 * torch.cuda.get_device_properties(W0.device).multi_processor_count
+        waves = nb * ((R + 127) // 128) / slots
+        if not (0.0 < waves - int(waves) < 0.35):
+            return None
+        W = torch.cat([W0, W1], 0)
+        scales = torch.cat([grids[0][0], grids[1][0]])
+        qzeros = torch.cat([grids[0][1], grids[1][1]])
+        u_map = torch.arange(nb, dtype=torch.int32, device=W.device).repeat(2)
+        return ops.gptq_solve_batched(W, U0, scales, qzeros, cfg.group_size, cfg.bits, perm=perm32, u_map=u_map,
+                                      status=self._status, form=1 if self.inversion_free else 0)
 
     def _pack(self, q, scales, qzeros, M):
         cfg = self.cfg
