@@ -135,17 +135,17 @@ struct CholWs {
 
 // ---- diag: factor + invert the diagonal block of step k (one CTA of 64 threads per matrix) -----------------
 // Thread i owns row i of the 64x64 block in registers (the full symmetric row, so that no update needs a
-// predicate).  Column j: thread j takes the square root of its pivot, every thread scales its entry of column j
-// and publishes it through shared memory, then subtracts its multiple of column j from the rest of its row
-// (right-looking).  The inverse is then one forward substitution per thread (thread c solves L x = e_c), reading
-// L rows as broadcast float4 from shared memory, with four partial sums to shorten the dependent chain.
-// Everything is statically indexed: no shared-memory round trip for the matrix, two 64-thread barriers per column.
+// predicate).  Both loops are ROLLED with a sliding window, so that every register index is static and the loop
+// bodies stay in the instruction cache (a fully unrolled version spends its time fetching 7000 instructions that
+// each run once): at step j the row's entry for column j is a[0], and the update writes a[m] <- a[m+1] - l_ij *
+// l_(j+1+m),j.  Column j of the factor is published pre-shifted, Lsh[j][m] = L[j+1+m][j], which makes the reads
+// aligned float4 broadcasts for the update and for the inverse alike.  The inverse is one forward substitution per
+// thread (thread c solves L x = e_c, column-oriented with the same sliding window); no barrier is needed there.
 __global__ void __launch_bounds__(64) chol_diag_kernel(float *__restrict__ Aall, int64_t C, int k, int nblk,
                                                         float *__restrict__ dinv_all, float *__restrict__ Uall,
                                                         float *__restrict__ udiag, int32_t *__restrict__ info) {
-    __shared__ __align__(16) float Ls[NB][NB];   // the factor, row-major (upper part zero)
-    __shared__ float col[2][NB];                  // column j of the factor, double buffered
-    __shared__ float invd[NB];
+    __shared__ __align__(16) float Lsh[NB][NB];   // Lsh[j][m] = L[j+1+m][j], zero past the end of the column
+    __shared__ float dg[NB], invd[NB];
     __shared__ int bad_col;
     const int b = blockIdx.x, i = threadIdx.x;
     float *A = Aall + (int64_t)b * C * C;
@@ -159,65 +159,59 @@ __global__ void __launch_bounds__(64) chol_diag_kernel(float *__restrict__ Aall,
         float v = (i == j) ? 1.0f : 0.0f;         // identity padding of a partial last block
         if (i < nbk && j < nbk) v = (j <= i) ? A[(cb + i) * C + cb + j] : A[(cb + j) * C + cb + i];
         a[j] = v;
+        Lsh[j][i] = 0.0f;
     }
     __syncthreads();
-#pragma unroll
+    float *Acol = A + (cb + i) * C + cb;          // L[i][j] goes to Acol[j]
+#pragma unroll 1
     for (int j = 0; j < NB; ++j) {
         if (i == j) {
-            const float piv = a[j];
+            const float piv = a[0];
             if (!(piv > 0.0f) && bad_col < 0) bad_col = j;
             const float d = sqrtf(piv);
-            col[j & 1][j] = d;
+            dg[j] = d;
             invd[j] = __fdiv_rn(1.0f, d);
         }
         __syncthreads();
-        const float inv = invd[j];
-        float lij = (i == j) ? col[j & 1][j] : __fmul_rn(a[j], inv);
-        a[j] = lij;
-        if (i != j) col[j & 1][i] = lij;
+        const float lij = (i == j) ? dg[j] : __fmul_rn(a[0], invd[j]);
+        if (i > j) Lsh[j][i - j - 1] = lij;
+        if (i >= j && i < nbk && j < nbk) Acol[j] = lij;
         __syncthreads();
-        if (j + 1 < NB) {
-            const float *cj = col[j & 1];
+        const float4 *cj = reinterpret_cast<const float4 *>(&Lsh[j][0]);
 #pragma unroll
-            for (int l = j + 1; l < NB; ++l) a[l] = fmaf(-lij, cj[l], a[l]);
+        for (int m4 = 0; m4 < NB / 4; ++m4) {
+            const float4 c4 = cj[m4];
+            a[4 * m4 + 0] = fmaf(-lij, c4.x, a[4 * m4 + 1]);
+            a[4 * m4 + 1] = fmaf(-lij, c4.y, a[4 * m4 + 2]);
+            a[4 * m4 + 2] = fmaf(-lij, c4.z, a[4 * m4 + 3]);
+            if (m4 < NB / 4 - 1) a[4 * m4 + 3] = fmaf(-lij, c4.w, a[4 * m4 + 4]);
         }
+        a[NB - 1] = 0.0f;
     }
-    // publish the factor (lower part) for the substitution
+    // column c = i of the inverse:  x_r = b_r / L[r][r],  b_m <- b_m - L[m][r] x_r  (m > r), window sliding with r
 #pragma unroll
-    for (int j = 0; j < NB; ++j) Ls[i][j] = (j <= i) ? a[j] : 0.0f;
-    if (i < nbk) {
-#pragma unroll
-        for (int j = 0; j < NB; ++j)
-            if (j <= i && j < nbk) A[(cb + i) * C + cb + j] = a[j];
-    }
-    __syncthreads();
-    // column c = i of the inverse: forward substitution  x_r = (delta_rc - sum_{l<r} L[r][l] x_l) / L[r][r]
-    float x[NB];
-#pragma unroll
-    for (int r = 0; r < NB; ++r) {
-        float s0 = (r == i) ? 1.0f : 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
-        const float4 *Lr = reinterpret_cast<const float4 *>(&Ls[r][0]);
-#pragma unroll
-        for (int l4 = 0; l4 < (r + 3) / 4; ++l4) {
-            const float4 lv = Lr[l4];              // entries at and beyond column r are skipped below
-            if (4 * l4 + 0 < r) s0 = fmaf(-lv.x, x[4 * l4 + 0], s0);
-            if (4 * l4 + 1 < r) s1 = fmaf(-lv.y, x[4 * l4 + 1], s1);
-            if (4 * l4 + 2 < r) s2 = fmaf(-lv.z, x[4 * l4 + 2], s2);
-            if (4 * l4 + 3 < r) s3 = fmaf(-lv.w, x[4 * l4 + 3], s3);
-        }
-        x[r] = __fmul_rn(__fadd_rn(__fadd_rn(s0, s1), __fadd_rn(s2, s3)), invd[r]);
-    }
-    // outputs: L (lower part of A), Dinv and its transpose, the diagonal block of the scaled inverse, udiag, info
+    for (int m = 0; m < NB; ++m) a[m] = (m == i) ? 1.0f : 0.0f;
     float *dinv = dinv_all + ((int64_t)b * nblk + k) * 2 * NB * NB;
     float *U = Uall ? Uall + (int64_t)b * C * C : nullptr;
-#pragma unroll
+#pragma unroll 1
     for (int r = 0; r < NB; ++r) {
-        dinv[r * NB + i] = x[r];                  // Dinv[r][c = i]
-        dinv[NB * NB + i * NB + r] = x[r];        // Dinv^T[c][r]
+        const float xr = __fmul_rn(a[0], invd[r]);
+        dinv[r * NB + i] = xr;                    // Dinv[r][c = i]
+        dinv[NB * NB + i * NB + r] = xr;          // Dinv^T[c][r]
         if (U && r < nbk && i < nbk) {
             // diagonal block of  diag(L) L^-1  (unit diagonal, zero above it)
-            U[(cb + r) * C + cb + i] = (i < r) ? __fmul_rn(Ls[r][r], x[r]) : ((i == r) ? 1.0f : 0.0f);
+            U[(cb + r) * C + cb + i] = (i < r) ? __fmul_rn(dg[r], xr) : ((i == r) ? 1.0f : 0.0f);
         }
+        const float4 *cr = reinterpret_cast<const float4 *>(&Lsh[r][0]);
+#pragma unroll
+        for (int m4 = 0; m4 < NB / 4; ++m4) {
+            const float4 c4 = cr[m4];
+            a[4 * m4 + 0] = fmaf(-xr, c4.x, a[4 * m4 + 1]);
+            a[4 * m4 + 1] = fmaf(-xr, c4.y, a[4 * m4 + 2]);
+            a[4 * m4 + 2] = fmaf(-xr, c4.z, a[4 * m4 + 3]);
+            if (m4 < NB / 4 - 1) a[4 * m4 + 3] = fmaf(-xr, c4.w, a[4 * m4 + 4]);
+        }
+        a[NB - 1] = 0.0f;
     }
     if (i < nbk) udiag[(int64_t)b * C + (C - 1 - (cb + i))] = invd[i];
     if (i == 0 && bad_col >= 0 && info[b] == 0) info[b] = (int32_t)(cb + bad_col + 1);

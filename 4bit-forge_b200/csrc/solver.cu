@@ -336,7 +336,8 @@ __global__ void __launch_bounds__(128, 3) solve_kernel(const SolveParams p) {
 // Both operands are "MN-major": the errors are [j][r] with the 128 rows of the strip contiguous, the U
 // panel is [j][bs..bs+128) with the block columns contiguous.  A k-step piece is [8 j][128] fp32 in the
 // swizzle layout that 32-bit MN-major operands require (see make_desc_tf32).  The four row warps are the
-// producers: far k-steps load E and U from global memory through registers (prefetched 4 k-steps ahead),
+// producers: far k-steps bring E and U in with cp.async through a small raw ring (each thread reads back only
+// the chunks it copied itself; holding prefetched k-steps in registers instead spills at 128 registers/thread),
 // near k-steps take the errors straight from the registers that just produced them; the hi/lo pieces are
 // stored with the swizzle, published to the async proxy, and the stage's mbarrier is arrived on.  Warp 4
 // issues the MMAs and commits.  Every wait is bounded; a CTA that gives up sets the status word.
@@ -344,11 +345,13 @@ __global__ void __launch_bounds__(128, 3) solve_kernel(const SolveParams p) {
 constexpr int kTcThreads = 160;
 constexpr int kTcStageBytes = 4 * kPieceBytes;      // Ehi, Elo, Uhi, Ulo
 constexpr int kTcStages = 2;
-constexpr int kTcPrefetch = 4;                      // far k-steps held in registers ahead of the ring
 constexpr int kUsubLd = kSub;                        // staged triangle: row t holds U[t][t+1 ...], zero padded
 constexpr int kUsubFloats = kSub * kUsubLd;
+constexpr int kTcRaw = 2;                            // raw fp32 k-steps in flight (cp.async) in the far phase; three
+                                                     // would cost the third CTA per SM its shared memory
+constexpr int kTcRawBytes = 4 * 128 * 16;            // [E row jA, E row jA+4, U row jA, U row jA+4][128 threads]
 constexpr size_t kTcSmem = (size_t)kTcStages * kTcStageBytes + 1024 + 2 * kUsubFloats * sizeof(float) +
-                           kSub * kBlk * sizeof(float) + kBlk * sizeof(float) + 256;
+                           kSub * kBlk * sizeof(float) + kBlk * sizeof(float) + 256 + (size_t)kTcRaw * kTcRawBytes;
 
 __device__ __forceinline__ void rows_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
@@ -362,6 +365,7 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
     float *es = Usub + 2 * kUsubFloats;                                          // [32][128] errors of a sub-block
     float *uinv_s = es + kSub * kBlk;                                            // [128]
     uint64_t *bars = reinterpret_cast<uint64_t *>(uinv_s + kBlk);                // full[4], empty[4], acc
+    uint8_t *raw = reinterpret_cast<uint8_t *>(bars) + 256;                      // [kTcRaw][8 KB]
     uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + 9);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
     const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + kTcStages), bar_acc = smem_u32(bars + 8);
@@ -413,53 +417,54 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
             const bool u_ok = (bs + 4 * c4) < C;
             // ---------------- far phase: every column before the block ----------------
             if (bs > 0 && ok) {
+                // operands travel global -> raw ring (cp.async, kTcRaw k-steps ahead, no registers held) -> hi/lo split
+                // -> operand stage; a thread reads back only the 16-byte chunks it copied itself (no barrier needed)
                 const int nks = (int)(bs / kKS);
-                float4 re[kTcPrefetch][2], ru[kTcPrefetch][2];
-#pragma unroll
-                for (int d = 0; d < kTcPrefetch; ++d) {
-                    if (d < nks) {
-#pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            const int64_t j = (int64_t)d * kKS + jA + 4 * h;
-                            re[d][h] = e_ok ? *reinterpret_cast<const float4 *>(E + j * R + r0 + 4 * c4) : make_float4(0.f, 0.f, 0.f, 0.f);
-                            ru[d][h] = u_ok ? *reinterpret_cast<const float4 *>(U + j * C + bs + 4 * c4) : make_float4(0.f, 0.f, 0.f, 0.f);
-                        }
+                const uint32_t raw_u32 = smem_u32(raw) + (uint32_t)tid * 16u;
+                const float *srcE = E + (int64_t)jA * R + r0 + 4 * c4;
+                const float *srcU = U + (int64_t)jA * C + bs + 4 * c4;
+                auto issue = [&](int ks) {
+                    if (ks < nks) {
+                        const uint32_t dst = raw_u32 + (uint32_t)(ks % kTcRaw) * kTcRawBytes;
+                        const int64_t j = (int64_t)ks * kKS;
+                        cp_async16_zfill(dst, e_ok ? srcE + j * R : E, e_ok);
+                        cp_async16_zfill(dst + 2048, e_ok ? srcE + (j + 4) * R : E, e_ok);
+                        cp_async16_zfill(dst + 4096, u_ok ? srcU + j * C : U, u_ok);
+                        cp_async16_zfill(dst + 6144, u_ok ? srcU + (j + 4) * C : U, u_ok);
                     }
-                }
-                for (int base = 0; base < nks && ok; base += kTcPrefetch) {
+                    cp_async_commit();
+                };
 #pragma unroll
-                    for (int d = 0; d < kTcPrefetch; ++d) {
-                        const int ks = base + d;
-                        if (ks < nks && ok) {
-                            const uint32_t s = it % kTcStages, ph = (it / kTcStages) & 1u;
-                            ok = mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag);
-                            if (ok) {
-                                uint8_t *stage = ring + s * kTcStageBytes;
+                for (int d = 0; d < kTcRaw; ++d) issue(d);
+#pragma unroll 1
+                for (int ks = 0; ks < nks && ok; ++ks) {
+                    cp_async_wait<kTcRaw - 1>();
+                    const uint8_t *rs = raw + (ks % kTcRaw) * kTcRawBytes + tid * 16;
+                    float4 ve[2], vu[2];
+                    ve[0] = *reinterpret_cast<const float4 *>(rs);
+                    ve[1] = *reinterpret_cast<const float4 *>(rs + 2048);
+                    vu[0] = *reinterpret_cast<const float4 *>(rs + 4096);
+                    vu[1] = *reinterpret_cast<const float4 *>(rs + 6144);
+                    const uint32_t s = it % kTcStages, ph = (it / kTcStages) & 1u;
+                    ok = mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag);
+                    if (!ok) break;
+                    uint8_t *stage = ring + s * kTcStageBytes;
 #pragma unroll
-                                for (int h = 0; h < 2; ++h) {
-                                    float4 hi, lo;
-                                    split4(re[d][h], hi, lo);
-                                    *reinterpret_cast<float4 *>(stage + 0 * kPieceBytes + sw_off[h]) = hi;
-                                    *reinterpret_cast<float4 *>(stage + 1 * kPieceBytes + sw_off[h]) = lo;
-                                    split4(ru[d][h], hi, lo);
-                                    *reinterpret_cast<float4 *>(stage + 2 * kPieceBytes + sw_off[h]) = hi;
-                                    *reinterpret_cast<float4 *>(stage + 3 * kPieceBytes + sw_off[h]) = lo;
-                                }
-                                fence_proxy_async();
-                                mbar_arrive(bar_full + 8 * s);
-                                ++it;
-                                if (ks + kTcPrefetch < nks) {
-#pragma unroll
-                                    for (int h = 0; h < 2; ++h) {
-                                        const int64_t j = (int64_t)(ks + kTcPrefetch) * kKS + jA + 4 * h;
-                                        re[d][h] = e_ok ? *reinterpret_cast<const float4 *>(E + j * R + r0 + 4 * c4) : make_float4(0.f, 0.f, 0.f, 0.f);
-                                        ru[d][h] = u_ok ? *reinterpret_cast<const float4 *>(U + j * C + bs + 4 * c4) : make_float4(0.f, 0.f, 0.f, 0.f);
-                                    }
-                                }
-                            }
-                        }
+                    for (int h = 0; h < 2; ++h) {
+                        float4 hi, lo;
+                        split4(ve[h], hi, lo);
+                        *reinterpret_cast<float4 *>(stage + 0 * kPieceBytes + sw_off[h]) = hi;
+                        *reinterpret_cast<float4 *>(stage + 1 * kPieceBytes + sw_off[h]) = lo;
+                        split4(vu[h], hi, lo);
+                        *reinterpret_cast<float4 *>(stage + 2 * kPieceBytes + sw_off[h]) = hi;
+                        *reinterpret_cast<float4 *>(stage + 3 * kPieceBytes + sw_off[h]) = lo;
                     }
+                    fence_proxy_async();
+                    mbar_arrive(bar_full + 8 * s);
+                    ++it;
+                    issue(ks + kTcRaw);
                 }
+                cp_async_wait<0>();
             }
             if (SPARSE) {
                 const int64_t c = bs + tid;
@@ -571,12 +576,12 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
                     constexpr int W = decltype(wtag)::value;
                     const int64_t c = cs + t;
                     // the row of U this column propagates along: in flight while the column is quantised
+                    // (first half now, second half after the quantisation: holding all of it across the chain spills)
                     float4 u4[W / 4];
-                    {
-                        const float4 *urow = reinterpret_cast<const float4 *>(us + t * kUsubLd);
+                    const float4 *urow = reinterpret_cast<const float4 *>(us + t * kUsubLd);
+                    constexpr int kFirst = (W / 8 > 0) ? W / 8 : 1;
 #pragma unroll
-                        for (int k4 = 0; k4 < W / 4; ++k4) u4[k4] = urow[k4];
-                    }
+                    for (int k4 = 0; k4 < kFirst; ++k4) u4[k4] = urow[k4];
                     const float w_t = es[t * kBlk + tid];   // the column's original weight; replaced by its error below
                     const float sc = s_nx, q0 = q0_nx;
                     if (!uniform_meta || t == 0) {
@@ -621,6 +626,8 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
                     qp += R; ep += R; wp += R;
                     es[t * kBlk + tid] = err;
                     // x[k] <- x[k+1] - U[t][t+1+k] * err ; past the end of the row the staged value is zero
+#pragma unroll
+                    for (int k4 = kFirst; k4 < W / 4; ++k4) u4[k4] = urow[k4];
 #pragma unroll
                     for (int k4 = 0; k4 < W / 4; ++k4) {
                         x[4 * k4 + 0] = fmaf(-u4[k4].x, err, x[4 * k4 + 1]);

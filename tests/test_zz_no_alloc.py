@@ -33,6 +33,7 @@ def test_noalloc_matches_workspace_entry_point_twice_in_a_row():
         U = torch.empty((C, C), dtype=torch.float32, device=dev)
         ud = torch.empty(C, dtype=torch.float32, device=dev)
         info = torch.full((1,), -1, dtype=torch.int32, device=dev)
+        torch.cuda.synchronize()    # earlier tests may have frees pending on other streams: settle them first
         before = torch.cuda.memory_allocated()
         _abi.call("forge_chol_inv_upper_noalloc", _abi.ptr(A_d), C, _abi.ptr(U), _abi.ptr(ud), _abi.ptr(info), 1,
                   _abi.stream_ptr())
