@@ -31,6 +31,45 @@ def shared_expert_owner(topk_ids: torch.Tensor, n_experts: int, world: int) -> i
     return min(range(world), key=lambda r: (loads[r], r))
 
 
+def balance_experts(token_counts, world: int, n_shared: int = 0, n_tokens: int = 0,
+                    fixed_cost_tokens: float = 15000.0) -> List[List[int]]:
+    """Placement by load instead of by index: longest-processing-time-first over the cost
+    `fixed_cost_tokens + routed tokens` of each expert (the factorisation, scale search and solve of an expert
+    cost the same whatever its traffic; the Hessian and the expert forward grow with its tokens: with a skewed
+    router a contiguous split leaves the rank that holds the popular experts far behind the others).
+    Shared experts (ids n_experts .. n_experts + n_shared - 1) see every token.  Deterministic: every rank
+    computes the same placement from the same counts.  Returns the expert ids of each rank, ascending."""
+    counts = [int(c) for c in token_counts]
+    E = len(counts)
+    cost = [(fixed_cost_tokens + c, e) for e, c in enumerate(counts)]
+    cost += [(fixed_cost_tokens + n_tokens, E + j) for j in range(n_shared)]
+    loads = [0.0] * world
+    owned: List[List[int]] = [[] for _ in range(world)]
+    for c, e in sorted(cost, key=lambda t: (-t[0], t[1])):
+        r = min(range(world), key=lambda q: (loads[q], q))
+        loads[r] += c
+        owned[r].append(e)
+    return [sorted(o) for o in owned]
+
+
+def placement_tables(owned: List[List[int]], n_experts: int):
+    """For a placement of the ROUTED experts (ids < n_experts; shared experts are not routed): a table
+    old id -> new id under which every rank's routed experts are one contiguous range, and that range
+    (begin, count) per rank.  Renumbering the routing table through it lets the contiguous-range kernels serve
+    any placement."""
+    table = torch.empty(n_experts, dtype=torch.int64)
+    spans = []
+    nxt = 0
+    for ids in owned:
+        routed = [e for e in ids if e < n_experts]
+        for e in routed:
+            table[e] = nxt
+            nxt += 1
+        spans.append((nxt - len(routed), len(routed)))
+    assert nxt == n_experts, "placement must cover every routed expert exactly once"
+    return table, spans
+
+
 def broadcast_inputs(X: torch.Tensor, topk_ids: torch.Tensor, src: int = 0, chunks: int = 1):
     """Broadcast the calibration input [T,H] and the routing table [T,k] from `src` (in place)."""
     if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:

@@ -46,6 +46,8 @@ def parse():
     ap.add_argument("--tokens", type=int, default=0, help="override the calibration token count (smaller runs)")
     ap.add_argument("--experts", type=int, default=0, help="override the routed expert count (smaller runs)")
     ap.add_argument("--expert-chunk", type=int, default=0)
+    ap.add_argument("--placement", default="lpt", choices=["lpt", "contiguous"],
+                    help="experts to ranks: by load (routed tokens, longest first) or contiguous index ranges")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     return ap.parse_args()
@@ -228,17 +230,36 @@ def run_ours(args, rank, world, local_rank):
         ids = torch.empty((T, shape.top_k), dtype=torch.int32, device=dev)
     if world > 1:
         dist.broadcast(ids, src=0)  # only to place the shared expert; the timed step broadcasts again
-    owner = fdist.shared_expert_owner(ids.cpu(), E, world) if shape.n_shared else -1
-    n_tail = shape.n_shared if rank == owner else 0
-    my_ids = list(range(e0, e1)) + [E + j for j in range(n_tail)]
+    # placement is decided from the routing statistics before the timed region (like the shared expert's owner)
+    ids_host = ids.cpu()
+    remap = None
+    if args.placement == "lpt" and world > 1:
+        counts_all = torch.bincount(ids_host.reshape(-1).long(), minlength=E)
+        # an expert's fixed cost (factor, search, solve) in units of routed tokens: measured ~15k at hidden 2048
+        owned = fdist.balance_experts(counts_all.tolist(), world, shape.n_shared, T,
+                                      fixed_cost_tokens=15000.0 * Hd / 2048.0)
+        table, spans = fdist.placement_tables(owned, E)
+        remap = table.to(dev)
+        my_ids = owned[rank]
+        e0, n_r = spans[rank]
+        e1 = e0 + n_r
+        n_tail = len(my_ids) - n_r
+        n_local_of = [len(o) for o in owned]
+    else:
+        owner = fdist.shared_expert_owner(ids_host, E, world) if shape.n_shared else -1
+        n_tail = shape.n_shared if rank == owner else 0
+        my_ids = list(range(e0, e1)) + [E + j for j in range(n_tail)]
+        n_local_of = []
+        for r in range(world):
+            b, e = fdist.shard_experts(E, world, r)
+            n_local_of.append((e - b) + (shape.n_shared if r == owner else 0))
     Wg, Wu, Wd = synth.expert_weights(shape, my_ids, seed=12, device=dev)
     fp8 = None
     if shape.fp8_weights:
         fp8 = [[synth.fp8_block_encode(w) for w in Wm] for Wm in (Wg, Wu, Wd)]
 
     def shapes_of_rank(r):
-        b, e = fdist.shard_experts(E, world, r)
-        n = (e - b) + (shape.n_shared if r == owner else 0)
+        n = n_local_of[r]
         meta = {}
         for nm, (R, C) in (("gate", (I, Hd)), ("up", (I, Hd)), ("down", (Hd, I))):
             if cfg.algorithm == "sparsegptq":
@@ -270,6 +291,8 @@ def run_ours(args, rank, world, local_rank):
             for Wm, enc in zip((Wgs, Wus, Wds), fp8):
                 for i, (q8, sinv) in enumerate(enc):
                     Wm[i].copy_(ops.fp8_block_dequant(q8, sinv))
+        if remap is not None:
+            idss = remap[idss.long()].to(torch.int32)      # renumber: this rank's experts become one contiguous range
         out = (quantizer or qz).quantize_experts(Xs, idss, Wgs, Wus, Wds, e_begin=e0, dense_tail=n_tail)
         local = local_results(out)
         gathered = fdist.gather_to_rank0(local, shapes_of_rank) if world > 1 else {k: [v] for k, v in local.items()}
@@ -346,7 +369,8 @@ def run_ours(args, rank, world, local_rank):
                 X.copy_(hX, non_blocking=True)
                 ids.copy_(hids, non_blocking=True)
             fdist.broadcast_inputs(X, ids, src=0)
-            out, _ = qz.quantize_experts_host(X, ids, hW[0], hW[1], hW[2], e_begin=e0, dense_tail=n_tail,
+            idl = remap[ids.long()].to(torch.int32) if remap is not None else ids
+            out, _ = qz.quantize_experts_host(X, idl, hW[0], hW[1], hW[2], e_begin=e0, dense_tail=n_tail,
                                               fp8_scale_inv=hS, ship_results=False)
             gathered = fdist.gather_to_rank0(local_results(out), shapes_of_rank)
             if rank == 0:
@@ -472,6 +496,7 @@ def run_ours(args, rank, world, local_rank):
                 "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "bf16 inputs / f32 accumulate and solve", "data": "synthetic",
                 "config": {"workload": workload_name(shape, recipe), "parallelism": f"ep{world}",
+                           "placement": args.placement if world > 1 else "single",
                            "l2": "inputs larger than L2 (X, weights and Hessians >> 126 MB)"},
                 "clocks": clk, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline,
                 "cpu_baseline": cpu_base,

@@ -77,3 +77,25 @@ def _worker(rank, world, port, fail_rank):
 def test_broadcast_and_gather_two_ranks():
     port = _free_port()
     mp.spawn(_worker, args=(2, port, -1), nprocs=2, join=True)
+
+
+def test_balanced_placement_covers_all_and_evens_out_load():
+    from forge import dist as fdist
+    import torch
+    g = torch.Generator().manual_seed(0)
+    E, world, T = 128, 8, 65536
+    counts = (torch.rand(E, generator=g) ** 6 * 60000).long() + 20      # a few hot experts, many cold ones
+    owned = fdist.balance_experts(counts.tolist(), world, n_shared=1, n_tokens=T)
+    flat = sorted(e for o in owned for e in o)
+    assert flat == list(range(E + 1))                                     # every expert once, the shared one included
+    cost = lambda ids: sum(15000.0 + (T if e >= E else int(counts[e])) for e in ids)
+    loads = [cost(o) for o in owned]
+    contiguous = [cost(range(*fdist.shard_experts(E, world, r))) for r in range(world)]
+    assert max(loads) <= 1.05 * (sum(loads) / world) or max(loads) == max(15000.0 + T, 15000.0 + int(counts.max()))
+    assert max(loads) < max(contiguous)
+    table, spans = fdist.placement_tables(owned, E)
+    assert sorted(table.tolist()) == list(range(E))
+    for r, (b, n) in enumerate(spans):
+        routed = [e for e in owned[r] if e < E]
+        assert [int(table[e]) for e in routed] == list(range(b, b + n))     # contiguous, in ascending id order
+    assert fdist.balance_experts(counts.tolist(), world, 1, T) == owned   # deterministic
