@@ -216,3 +216,55 @@ def test_host_api_matches_device_api(algorithm, sym, fp8):
                 assert torch.equal(host[f"{nm}.weight_scale"], ref[nm]["weight_scale"].cpu())
                 if not sym:
                     assert torch.equal(host[f"{nm}.weight_zero_point"], ref[nm]["qzeros"].to(torch.uint8).cpu())
+
+
+class _ToyExpert(torch.nn.Module):
+    def __init__(self, H, I, g):
+        super().__init__()
+        mk = lambda o, i: torch.nn.Parameter((torch.randn(o, i, generator=g) * 0.02).to(torch.bfloat16))
+        self.gate_proj, self.up_proj, self.down_proj = (torch.nn.Linear(H, I, bias=False), torch.nn.Linear(H, I, bias=False),
+                                                        torch.nn.Linear(I, H, bias=False))
+        self.gate_proj.weight, self.up_proj.weight, self.down_proj.weight = mk(I, H), mk(I, H), mk(H, I)
+
+    def forward(self, x):
+        return self.down_proj(torch.nn.functional.silu(self.gate_proj(x)) * self.up_proj(x))
+
+
+def test_block_capture_matches_per_linear_hooks():
+    """forge.capture.quantize_moe_block (one batched pass) against the reference driver's way: one GPTQ handle and
+    one forward hook per expert Linear, quantize() handle by handle (quant.py:344-512)."""
+    from forge import capture, moe
+    from forge.gptq import GPTQ
+    g = torch.Generator().manual_seed(21)
+    H, I, E, T, k = 256, 128, 6, 1536, 2
+    experts = torch.nn.ModuleList([_ToyExpert(H, I, g) for _ in range(E)]).to(DEV)
+    router = (torch.randn(E, H, generator=g) * 0.1).to(DEV)
+    X = (torch.randn(T, H, generator=g) * torch.exp(0.5 * torch.randn(H, generator=g))).to(torch.bfloat16).to(DEV)
+    ids = capture.topk_from_logits(X.float() @ router.T, k)
+    kw = dict(bits=4, group_size=64, symmetric=True, quantization_scale="absmax", quantization_order="default",
+              rel_damp=0.01, algorithm="gptq")
+    # --- the reference driver's structure
+    handles, hooks = {}, []
+    for e, m in enumerate(experts):
+        for nm in ("gate_proj", "up_proj", "down_proj"):
+            # the driver's default mode: every Linear accumulates its own Hessian.  (Its --owner_gptq_handles mode
+            # lets up_proj copy gate_proj's Hessian AFTER gate_proj's quantize() has damped it in place, so up_proj
+            # is damped twice, forge/gptq.py:88-95 with :142-154; the batched path shares the Hessian before damping.)
+            h = GPTQ(getattr(m, nm), owner=None, device=DEV, **kw)
+            handles[f"mlp.experts.{e}.{nm}"] = h
+            hooks.append(getattr(m, nm).register_forward_hook(lambda _, inp, out, h=h: h.update(inp[0])))
+    with torch.no_grad():
+        for e, m in enumerate(experts):
+            rows = (ids == e).any(1).nonzero().flatten()
+            if rows.numel():
+                m(X[rows])
+    for hk in hooks:
+        hk.remove()
+    ref = {n: h.quantize() for n, h in handles.items()}
+    # --- one batched pass
+    got = capture.quantize_moe_block(experts, X, ids, moe.MoEQuantConfig(**kw))
+    for n, (q_ref, s_ref, z_ref) in ref.items():
+        q, s, z = got[n]
+        assert int(got[n + ".info"]) == 0
+        assert torch.equal(s, s_ref) and torch.equal(z, z_ref), n
+        assert float((q == q_ref).float().mean()) >= 0.995, n
