@@ -148,6 +148,44 @@ def cpu_sample(shape, recipe, n_tokens_list, seed=0):
     return t_total
 
 
+def reference_gpu_sample(shape, recipe, n_tokens_list, dev, seed=0):
+    """The reference's algorithm with the reference's OWN CUDA kernels (oracle/_ref, compiled for sm_100a from the
+    reference checkout) and torch for its Python half, on this GPU: one handle per Linear, one update and one
+    quantize() each, as its driver does.  Returns (seconds, launches are not ours) or None when the library was not
+    built.  A same-device baseline beside the CPU one; none of this engine's kernels run here."""
+    import ref_build
+    import ref_port as O
+    from forge import synth
+    ref = ref_build.load_built()
+    if ref is None:
+        return None
+    kw = dict(bits=4, group_size=128, rel_damp=0.01, kernels=ref, **recipe)
+    work = []
+    for i, n in enumerate(n_tokens_list):
+        Wg, Wu, Wd = synth.expert_weights(shape, [i], seed=seed + 1, device=dev)
+        x = synth.student_t_activations(max(n, 1), shape.hidden, seed=seed + 2 + i, device=dev)[:n]
+        work.append((Wg[0], Wu[0], Wd[0], x))
+
+    def one_pass():
+        for Wg, Wu, Wd, x in work:
+            hg, hu = O.OracleGPTQ(Wg, **kw), O.OracleGPTQ(Wu, **kw)
+            hg.update(x)
+            hu.update(x)
+            hd = O.OracleGPTQ(Wd, **kw)
+            hd.update(O.swiglu_down_input(x, Wg, Wu))
+            for h in (hg, hu, hd):
+                h.quantize()
+
+    one_pass()                                  # warm-up (cuSOLVER handles, kernel load)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    one_pass()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / 1e3
+
+
 def run_reference(args, rank, world):
     if rank != 0:
         return
@@ -491,6 +529,15 @@ def run_ours(args, rank, world, local_rank):
                     "sample": f"2 experts at full matrix shape: hottest ({hot} tokens) and coldest ({cold} tokens) "
                               f"of rank 0's slice; experts/s extrapolated from their mean time"}
 
+    ref_gpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        c = sorted(int(v) for v in counts.tolist()[: max(1, e1 - e0)])
+        secs = reference_gpu_sample(shape, recipe, [c[-1], c[0]], dev)
+        if secs is not None:
+            ref_gpu = {"value": 2.0 / secs, "unit": UNIT, "kind": "reference kernels recompiled for sm_100a + torch, "
+                       "per-Linear handles on this GPU", "sample": f"2 experts at full matrix shape: hottest ({c[-1]} "
+                       f"tokens) and coldest ({c[0]} tokens); experts/s extrapolated from their mean time"}
+
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
@@ -499,7 +546,7 @@ def run_ours(args, rank, world, local_rank):
                            "placement": args.placement if world > 1 else "single",
                            "l2": "inputs larger than L2 (X, weights and Hessians >> 126 MB)"},
                 "clocks": clk, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline,
-                "cpu_baseline": cpu_base,
+                "cpu_baseline": cpu_base, "reference_same_gpu": ref_gpu,
                 "phases_ms_rank0": {k: round(v, 3) for k, v in sorted(phases.items(), key=lambda kv: -kv[1])}}
         print(json.dumps(line), flush=True)
 

@@ -6,11 +6,16 @@
  * against it.  Nothing in the shipped library links or calls it; only the test
  * suite, the smoke check and the benchmark's CPU-baseline leg load it.
  *
- * Parity status: the reference repository holds no tests, golden vectors or
- * recorded outputs for these kernels, and they cannot run without a GPU, so
- * this restatement is "parity unpinned": it follows the reference source line
- * by line (citations below, paths inside the reference project) but is not
- * checked against reference outputs.
+ * Parity status: PINNED.  The reference repository holds no tests or golden
+ * vectors for these kernels, so the vectors were made from the reference
+ * itself: its quant_grid.cu, solver.cu, solver_sparsegptq14.cu and
+ * bitpacking_sparsegptq14.cu are compiled for sm_100a where they lie in the
+ * reference checkout (oracle/ref_build.py -> oracle/_ref), run on a B200 by
+ * tests/golden/make_golden_gpu.py, and their inputs and outputs are stored in
+ * tests/golden/ref_kernels_b200.npz.  tests/test_oracle_ref_kernels.py replays
+ * this file on those inputs: scales, zeros, the winning shrink factors, codes,
+ * 1:4 masks and packed words are all bit-identical.  (dense int4 packing is
+ * pinned against the installed compressed_tensors.pack_to_int32 instead.)
  *
  * Build: gcc -O2 -fopenmp -ffp-contract=off -shared -fPIC (see oracle/build.py).
  * -ffp-contract=off matters: every fused multiply-add below is an explicit

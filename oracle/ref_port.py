@@ -9,9 +9,10 @@ activation ordering, damped Cholesky -> upper Cholesky of the inverse) is
 restated with the same torch calls in the same order; tests/golden holds
 outputs of the reference's own code for it (made by tests/golden/make_golden.py
 with the reference importable), so that half is pinned.  The CUDA-only half
-(scale grid, column solver, packers) is restated in oracle/forge_oracle.c; the
-reference holds no tests or recorded outputs for it, so that half is
-"parity unpinned".
+(scale grid, column solver, packers) is restated in oracle/forge_oracle.c and
+pinned against outputs of the reference's own kernels, compiled for sm_100a
+from the reference checkout (oracle/ref_build.py) and run on a B200
+(tests/golden/make_golden_gpu.py -> tests/golden/ref_kernels_b200.npz).
 
 Citations are paths inside the reference project.
 """
@@ -174,7 +175,7 @@ class OracleGPTQ:
 
     def __init__(self, layer, bits=4, group_size=128, symmetric=False, quantization_scale="mse",
                  quantization_order="activation", rel_damp=1e-2, algorithm="gptq", owner=None, device=None,
-                 solver_block=32):
+                 solver_block=32, kernels=None):
         if isinstance(layer, torch.Tensor):
             layer = _W(layer)
         self.layer = layer
@@ -189,6 +190,12 @@ class OracleGPTQ:
         self.prepared = False
         self.issue_non_invertible = False
         self.solver_block = solver_block
+        # the five kernel operators: the C oracle by default; the reference's own CUDA kernels (oracle/_ref) when the
+        # class runs on a GPU as the same-device baseline of the benchmark
+        self.k = kernels
+
+    def _op(self, name):
+        return getattr(self.k, name) if self.k is not None else globals()[name]
 
     @torch.no_grad()
     def update(self, X):
@@ -212,7 +219,7 @@ class OracleGPTQ:
             return
         C = int(self.W.shape[-1])
         if self.H is None or self.num_samples == 0 or torch.isnan(self.H).any().item():
-            self.H = torch.eye(C, dtype=torch.float32)
+            self.H = torch.eye(C, dtype=torch.float32, device=self.W.device)
         self.pruned_ids = torch.diag(self.H) == 0
         self.H[self.pruned_ids, :] = 0
         self.H[:, self.pruned_ids] = 0
@@ -220,7 +227,7 @@ class OracleGPTQ:
         if self.quantization_order == "activation":
             self.perm = torch.argsort(self.H.diag(), descending=True)
         else:
-            self.perm = torch.arange(C)
+            self.perm = torch.arange(C, device=self.W.device)
         self.perm_inv = torch.argsort(self.perm)
         self.W[:, self.pruned_ids] = 0
         self.prepared = True
@@ -247,7 +254,7 @@ class OracleGPTQ:
             H.div_(H.diag()[:, None])
         if info.item() > 0:
             self.issue_non_invertible = True
-            H = torch.eye(C, dtype=torch.float32)
+            H = torch.eye(C, dtype=torch.float32, device=self.W.device)
         return H
 
     @torch.no_grad()
@@ -260,10 +267,11 @@ class OracleGPTQ:
         if pad:
             W = torch.nn.functional.pad(W, (0, pad))
         Wg = W.reshape(R * G, self.group_size).to(torch.float32).contiguous()
-        scales, qzeros = build_group_meta_packed(Wg, self.bits, self.symmetric)
+        scales, qzeros = self._op("build_group_meta_packed")(Wg, self.bits, self.symmetric)
         if self.quantization_scale == "mse":
-            p = torch.linspace(1.0, max_shrink, n_grid, dtype=torch.float32)
-            scales, qzeros = mse_scale_groups_packed(Wg, scales, qzeros, p, float(norm), self.bits, self.symmetric)
+            p = torch.linspace(1.0, max_shrink, n_grid, dtype=torch.float32, device=Wg.device)
+            scales, qzeros = self._op("mse_scale_groups_packed")(Wg, scales, qzeros, p, float(norm), self.bits,
+                                                                 self.symmetric)
         self.G = int(G)
         return scales, qzeros
 
@@ -282,10 +290,13 @@ class OracleGPTQ:
         C, R = W.shape
         s_el, z_el = self._expand(scales, R, C), self._expand(qzeros, R, C)
         if self.algorithm == "sparsegptq":
-            q, M = sparsegptq14_solver(W, A, s_el, z_el, self.bits)
+            q, M = self._op("sparsegptq14_solver")(W, A, s_el, z_el, self.bits)
             self.W_deq_perm = W
             return q[self.perm_inv].transpose(-2, -1).contiguous(), scales, qzeros, M
-        q = gptq_solver(W, A, s_el, z_el, self.bits, block=self.solver_block)
+        if self.k is not None:
+            q = self.k.gptq_solver(W, A, s_el, z_el, self.bits)
+        else:
+            q = gptq_solver(W, A, s_el, z_el, self.bits, block=self.solver_block)
         self.W_deq_perm = W
         return q[self.perm_inv].transpose(-2, -1).contiguous(), scales, qzeros
 

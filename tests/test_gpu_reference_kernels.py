@@ -1,0 +1,105 @@
+"""The engine against the reference's OWN CUDA kernels, both running on the GPU on the same inputs.
+
+oracle/_ref/forge_ref_kernels.so is built from the reference checkout's .cu files by oracle/ref_build.py (test
+infrastructure; it is not part of the product and nothing under the package loads it).  The five functions are the
+solver-path operators of the reference's pybind module (forge/backend/cuda/kernels.cpp:92-150); the engine side
+goes through the same-named wrappers of forge.backend.cuda.kernels, i.e. through the C ABI.
+"""
+import os
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle"))
+import ref_build  # noqa: E402
+
+
+@pytest.fixture(scope="module")
+def ref():
+    mod = ref_build.load_built()
+    if mod is None:
+        pytest.skip("oracle/_ref/forge_ref_kernels.so not built (needs the reference checkout at build time)")
+    return mod
+
+
+def _weights(rows, C, seed, outliers=True):
+    g = torch.Generator().manual_seed(seed)
+    W = torch.randn(rows, C, generator=g) * 0.02
+    if outliers:
+        W = torch.where(torch.rand(rows, C, generator=g) < 0.002, W * 15.0, W)
+    return W.to(DEV)
+
+
+@pytest.mark.parametrize("gs", [32, 64, 128])
+@pytest.mark.parametrize("sym", [False, True])
+def test_minmax_and_mse_grid_bit_exact(ref, gs, sym):
+    from forge.backend.cuda import kernels
+    X = _weights(4096, gs, 100 + gs).contiguous()
+    s_ref, z_ref = ref.build_group_meta_packed(X, 4, sym)
+    s, z = kernels.build_group_meta_packed(X, 4, sym)
+    assert torch.equal(s, s_ref) and torch.equal(z, z_ref)
+    cand = torch.linspace(1.0, 0.2, 100, device=DEV)
+    s2_ref, z2_ref = ref.mse_scale_groups_packed(X, s_ref.clone(), z_ref.clone(), cand, 2.4, 4, sym)
+    s2, z2 = kernels.mse_scale_groups_packed(X, s.clone(), z.clone(), cand, 2.4, 4, sym)
+    assert torch.equal(s2, s2_ref) and torch.equal(z2, z2_ref)      # same approximate lg2 / ex2, same summation order
+
+
+def _factor(C, seed):
+    g = torch.Generator().manual_seed(seed)
+    A = torch.randn(C, 4 * C, generator=g, dtype=torch.float64)
+    H = A @ A.T / (4 * C) + 0.05 * torch.eye(C, dtype=torch.float64)
+    U = torch.linalg.cholesky(torch.linalg.inv(H), upper=True).float()
+    return U
+
+
+def _element_meta(ref, W, gs, sym):
+    R, C = W.shape
+    s, z = ref.build_group_meta_packed(W.reshape(-1, gs).contiguous(), 4, sym)
+    G = C // gs
+    exp = lambda t: t.view(R, G).repeat_interleave(gs, 1).T.contiguous()
+    return exp(s), exp(z), s, z
+
+
+@pytest.mark.parametrize("R,C", [(256, 512), (96, 160)])
+@pytest.mark.parametrize("impl", ["tensor", "simt"])
+def test_gptq_solver_against_reference_kernel(ref, R, C, impl, monkeypatch):
+    from forge.backend.cuda import kernels
+    if impl == "simt":
+        monkeypatch.setenv("FORGE_SOLVER_IMPL", "simt")
+    W = _weights(R, C, 7 + C, outliers=False)
+    U = _factor(C, 3 + C)
+    U = (U / U.diag()[:, None]).contiguous().to(DEV)
+    s_el, z_el, _, _ = _element_meta(ref, W, 32, False)
+    Wt = W.T.contiguous()
+    W_ref, W_eng = Wt.clone(), Wt.clone()
+    q_ref = ref.gptq_solver(W_ref, U, s_el, z_el, 4)
+    q = kernels.gptq_solver(W_eng, U, s_el, z_el, 4)
+    agree = float((q == q_ref).float().mean())
+    # all-FMA build: same arithmetic up to the summation order of the lazy update; tensor-core build: TF32 x3 products
+    assert agree >= (0.9995 if impl == "simt" else 0.995), agree
+    # both overwrite W with the de-quantised weights
+    same = q == q_ref
+    assert torch.equal(W_eng[same], W_ref[same])
+
+
+def test_sparse_solver_and_packer_against_reference_kernels(ref):
+    from forge.backend.cuda import kernels
+    R, C = 192, 256
+    W = _weights(R, C, 77, outliers=False)
+    U = _factor(C, 78).contiguous().to(DEV)                      # un-normalised: the operator divides by the diagonal
+    s_el, z_el, s, _ = _element_meta(ref, W, 32, True)
+    Wt = W.T.contiguous()
+    q_ref, M_ref = ref.sparsegptq14_solver(Wt.clone(), U.clone(), s_el, z_el, 4)
+    q, M = kernels.sparsegptq14_solver(Wt.clone(), U.clone(), s_el, z_el, 4)
+    m_same = float((M.view(torch.int32) == M_ref.view(torch.int32)).float().mean())
+    assert m_same >= 0.99, m_same
+    assert float((q == q_ref).float().mean()) >= 0.99
+    # the packer is integer work: bit-exact on identical inputs
+    s32 = s.view(R, C // 32).T.contiguous()
+    qrc = q_ref.T.contiguous()
+    wp_ref = ref.pack_sparsegptq14_to_u64x2(qrc, M_ref, s32)
+    wp = kernels.pack_sparsegptq14_to_u64x2(qrc, M_ref, s32)
+    assert torch.equal(wp.view(torch.int64), wp_ref.view(torch.int64))
