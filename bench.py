@@ -530,9 +530,13 @@ def run_ours(args, rank, world, local_rank):
                               f"of rank 0's slice; experts/s extrapolated from their mean time"}
 
     ref_gpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and recipe["algorithm"] == "gptq":
         c = sorted(int(v) for v in counts.tolist()[: max(1, e1 - e0)])
-        secs = reference_gpu_sample(shape, recipe, [c[-1], c[0]], dev)
+        try:
+            secs = reference_gpu_sample(shape, recipe, [c[-1], c[0]], dev)
+        except Exception as exc:   # a baseline leg must never take the measurement down with it
+            secs = None
+            print(f"reference_same_gpu leg skipped: {exc}", file=sys.stderr)
         if secs is not None:
             ref_gpu = {"value": 2.0 / secs, "unit": UNIT, "kind": "reference kernels recompiled for sm_100a + torch, "
                        "per-Linear handles on this GPU", "sample": f"2 experts at full matrix shape: hottest ({c[-1]} "
