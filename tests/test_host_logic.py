@@ -39,3 +39,43 @@ def test_activation_model_is_heavy_tailed():
     X = synth.student_t_activations(4096, 64, seed=4).float()
     k = ((X - X.mean(0)) ** 4).mean(0) / (X.var(0) ** 2)
     assert float(k.median()) > 4.0  # well above the Gaussian kurtosis of 3
+
+
+def test_checkpoint_layouts(tmp_path):
+    """Keys, shapes and dtypes of the block tensors match what the reference's writers emit
+    (pack_quantized.py:279-313 for dense W4, quant.py:615-622 for the stacked Wpair tensors)."""
+    import torch
+    from safetensors.torch import load_file
+    from forge import checkpoint
+    n, I, H, gs = 3, 64, 128, 32
+    g = torch.Generator().manual_seed(0)
+
+    def fam(R, C):
+        return {"qweight": torch.randint(0, 16, (n, R, C), generator=g, dtype=torch.uint8),
+                "weight_packed": torch.randint(-2 ** 31, 2 ** 31 - 1, (n, R, C // 8), generator=g, dtype=torch.int32),
+                "weight_scale": torch.rand(n, R, C // gs, generator=g).to(torch.float16),
+                "qzeros": torch.randint(0, 16, (n, R, C // gs), generator=g).float(),
+                "wpair": torch.randint(0, 2 ** 62, (n, (C // 32 + 1) // 2, R, 2), generator=g, dtype=torch.int64)}
+
+    out = {"gate": fam(I, H), "up": fam(I, H), "down": fam(H, I)}
+    t = checkpoint.dense_block_tensors(out, "model.layers.3.", n_routed=2, symmetric=False)
+    assert len(t) == 3 * n * 4
+    k = "model.layers.3.mlp.experts.1.down_proj"
+    assert t[k + ".weight_packed"].shape == (H, I // 8) and t[k + ".weight_packed"].dtype == torch.int32
+    assert t[k + ".weight_shape"].tolist() == [H, I] and t[k + ".weight_shape"].dtype == torch.int64
+    assert t[k + ".weight_scale"].shape == (H, I // gs) and t[k + ".weight_scale"].dtype == torch.float16
+    assert t[k + ".weight_zero_point"].dtype == torch.uint8
+    assert "model.layers.3.mlp.shared_experts.gate_proj.weight_packed" in t          # the one shared expert
+    assert not any("weight_zero_point" in key for key in
+                   checkpoint.dense_block_tensors(out, "p.", n_routed=3, symmetric=True))
+    s = checkpoint.sparse_block_tensors(out, "model.layers.3.")
+    w13 = s["model.layers.3.mlp.experts.gate_up_proj.w13_weight"]
+    assert w13.shape == (n, (H // 32 + 1) // 2, 2 * I, 2)
+    assert torch.equal(w13[:, :, :I], out["gate"]["wpair"]) and torch.equal(w13[:, :, I:], out["up"]["wpair"])
+    assert s["model.layers.3.mlp.experts.down_proj.w2_weight"].shape == (n, (I // 32 + 1) // 2, H, 2)
+    wm = checkpoint.write_block_shard(str(tmp_path / "block_003.safetensors"), {**t, **s})
+    back = load_file(str(tmp_path / "block_003.safetensors"))
+    assert set(wm) == set(back) and all(v == "block_003.safetensors" for v in wm.values())
+    assert torch.equal(back[k + ".weight_packed"], t[k + ".weight_packed"])
+    cfg = checkpoint.quantization_config(4, 128, symmetric=False)
+    assert cfg["format"] == "pack-quantized" and cfg["config_groups"]["group_0"]["weights"]["symmetric"] is False
