@@ -92,7 +92,7 @@ def test_hessian_identities_full_width():
     assert float((H[0, 3000:3064, 5000:5064] - ref).norm() / ref.norm()) < 1e-4
 
 
-@pytest.mark.parametrize("C", [2048, 3072])
+@pytest.mark.parametrize("C", [2048, 3072, 4352])
 def test_factor_identities_full_size(C):
     """U is unit upper triangular and U^-1 U^-T reproduces the damped Hessian up to the diagonal scaling;
     the inversion-free factor is the inverse of it."""
