@@ -347,15 +347,18 @@ constexpr int kTcStageBytes = 4 * kPieceBytes;      // Ehi, Elo, Uhi, Ulo
 constexpr int kTcStages = 2;
 constexpr int kUsubLd = kSub;                        // staged triangle: row t holds U[t][t+1 ...], zero padded
 constexpr int kUsubFloats = kSub * kUsubLd;
-constexpr int kTcRaw = 2;                            // raw fp32 k-steps in flight (cp.async) in the far phase; three
-                                                     // would cost the third CTA per SM its shared memory
+// raw fp32 k-steps in flight (cp.async) in the far phase: 2 where the launch fills the GPU (a third would cost the third
+// CTA per SM its shared memory), 6 where there are at most two CTAs per SM anyway and latency is all that counts
+constexpr int kTcRawFull = 2, kTcRawDeep = 6;
 constexpr int kTcRawBytes = 4 * 128 * 16;            // [E row jA, E row jA+4, U row jA, U row jA+4][128 threads]
-constexpr size_t kTcSmem = (size_t)kTcStages * kTcStageBytes + 1024 + 2 * kUsubFloats * sizeof(float) +
-                           kSub * kBlk * sizeof(float) + kBlk * sizeof(float) + 256 + (size_t)kTcRaw * kTcRawBytes;
+constexpr size_t tc_smem_bytes(int raw) {
+    return (size_t)kTcStages * kTcStageBytes + 1024 + 2 * kUsubFloats * sizeof(float) + kSub * kBlk * sizeof(float) +
+           kBlk * sizeof(float) + 256 + (size_t)raw * kTcRawBytes;
+}
 
 __device__ __forceinline__ void rows_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
-template <int MODE, bool SPARSE>
+template <int MODE, bool SPARSE, int kTcRaw>
 __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolveParams p, int32_t *status) {
     using namespace forge::tc;
     extern __shared__ uint8_t smem_raw[];
@@ -796,13 +799,20 @@ int launch_solve(const SolveParams &p, int nb, int32_t *status, cudaStream_t st)
     if (!attr_done) {
         cudaFuncSetAttribute(solve_kernel<MODE, SPARSE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)kSolveSmem);
-        cudaFuncSetAttribute(solve_tc_kernel<MODE, SPARSE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)kTcSmem);
+        cudaFuncSetAttribute(solve_tc_kernel<MODE, SPARSE, kTcRawFull>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)tc_smem_bytes(kTcRawFull));
+        cudaFuncSetAttribute(solve_tc_kernel<MODE, SPARSE, kTcRawDeep>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)tc_smem_bytes(kTcRawDeep));
         attr_done = true;
     }
     dim3 grid((unsigned)cdiv(p.R, kBlk), (unsigned)nb);
     if (use_tc_solver(p)) {
-        solve_tc_kernel<MODE, SPARSE><<<grid, kTcThreads, kTcSmem, st>>>(p, status); FORGE_NOTE_LAUNCH();
+        if ((int64_t)grid.x * grid.y <= 2 * 148) {
+            solve_tc_kernel<MODE, SPARSE, kTcRawDeep><<<grid, kTcThreads, tc_smem_bytes(kTcRawDeep), st>>>(p, status);
+        } else {
+            solve_tc_kernel<MODE, SPARSE, kTcRawFull><<<grid, kTcThreads, tc_smem_bytes(kTcRawFull), st>>>(p, status);
+        }
+        FORGE_NOTE_LAUNCH();
     } else {
         solve_kernel<MODE, SPARSE><<<grid, kBlk, kSolveSmem, st>>>(p); FORGE_NOTE_LAUNCH();
     }
