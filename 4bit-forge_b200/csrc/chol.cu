@@ -9,17 +9,19 @@
 // is a plain lower Cholesky plus a lower triangular inverse whose rows are scaled by diag(L) as they
 // are produced; one last pass rotates the result by 180 degrees into the upper triangle.
 //
-// Blocked right-looking factorisation with 64-column panels, every step batched over the matrices:
-//   diag  : factor the 64x64 diagonal block in shared memory, invert it (Dinv), emit the matching
-//           diagonal block of the scaled inverse and udiag;
-//   panel : rows below  <-  rows below * Dinv^T   (TRSM as a GEMM); the result is also stored
-//           transposed in the unused upper triangle so that the next step reads both operands with
-//           unit stride;
-//   syrk  : trailing lower triangle -= panel * panel^T   (128x128 tiles, 8x8 per thread, fp32 FMA).
-// The inverse proceeds block column by block column from the right:
-//   M[below, j] = -( M[below, below] * L[below, j] ) * Dinv_j .
-// All arithmetic is fp32 FMA on the SIMT pipe: the solver needs fp32-accurate U, and a
-// split-precision tensor-core variant has not been validated against the oracle.
+// Blocked right-looking factorisation, every step batched over the matrices, blocked on two levels:
+//   diag   : factor the 64x64 diagonal block in registers (one thread per row), invert it (Dinv), emit the
+//            matching diagonal block of the scaled inverse and udiag;
+//   panel  : rows below  <-  rows below * Dinv^T   (TRSM as a GEMM); the result is also stored transposed in
+//            the unused upper triangle so that the update reads both operands with unit stride;
+//   update : inside an outer block of 256 (512 for large matrices) columns, the panel updates only the rest of
+//            that outer block (K = 64); once the outer block is done it updates everything behind it in ONE pass
+//            (K = 256 / 512).  The update is a TF32 x3 GEMM on tcgen05 (fp32 fidelity through a hi/lo split, see
+//            tcgen05.cuh) with a vector red.global.add epilogue; an all-FMA version (chol_syrk_kernel) serves
+//            shapes the vector path does not take and the cross-check FORGE_SYRK_IMPL=simt.
+// forge_chol_factor_batched stops there and hands the solver the factor itself (scaled, negated, rotated:
+// rotate_scale_neg_kernel); forge_chol_inv_upper_batched continues with the inverse, block column by block
+// column from the right,   M[below, j] = -( M[below, below] * L[below, j] ) * Dinv_j   (fp32 FMA).
 #include "common.cuh"
 #include "tcgen05.cuh"
 #include <stdlib.h>

@@ -1,13 +1,18 @@
 // Per-group scale / zero grid: min-max, and the L^p shrink-factor search.
 //
-// One warp per group, lane l holding elements l, l+32, ... exactly as the reference kernels do
-// (forge/backend/cuda/quant_grid.cu:42-183), because the candidate that wins the search depends on the
-// order in which the per-element errors are summed: lane-local sum first, then a shfl_down tree.  What
-// changes is the data path: the weights are read once, in their storage type (bf16, 2 B/element,
-// instead of an fp32 copy), the min-max pass and the search share the registers, the search is
-// unrolled over candidates so that several reduction trees are in flight per warp, and the grid is a
-// multiple of the SM count.  The search is bound by FP32/MUFU issue (two transcendental ops per
-// element-candidate), not by HBM.
+// The reference kernels (forge/backend/cuda/quant_grid.cu:42-183) give one warp to a group, lane l holding
+// elements l, l+32, ..., and the candidate that wins the search depends on the order in which the per-element
+// errors are summed: lane-local sum first, then a shfl_down tree.  Every kernel here reproduces that order (the
+// thread-per-candidate kernels with a 6-entry stack visited in bit-reversed lane order), so scales and zeros are
+// bit-identical to the reference's.  What changes is the data path and the amount of work: the weights are read
+// once, in their storage type (bf16, 2 B/element, instead of an fp32 copy), min-max and search share one staging,
+// and the search abandons a candidate as soon as its partial loss exceeds a finished candidate's
+// (mse_prune_kernel).  Three kernels:
+//   quant_grid_kernel : warp per group; min-max grids and any group size;
+//   mse_grid_kernel   : exhaustive search, one thread per (group, candidate pair); group sizes 32 / 64 and the
+//                       cross-check FORGE_GRID_IMPL=exhaustive;
+//   mse_prune_kernel  : group size 128, up to 128 candidates, exact pruning; the default.
+// The search is bound by the special-function pipe (lg2 + ex2 per element-candidate evaluated), not by HBM.
 #include "common.cuh"
 #include <float.h>
 #include <stdlib.h>

@@ -5,7 +5,10 @@
 // launch per batch of matrices, instead of the reference's C/32 kernel launches plus C/32 skinny
 // GEMMs per matrix (forge/backend/cuda/solver.cu:124-151).
 //
-// For a 128-column block starting at column bs a thread holds its row's 128 values in registers:
+// Two builds of the same algorithm live here.  The default (solve_tc_kernel, further down) puts every product
+// that crosses a 32-column sub-block boundary on the tensor cores; solve_kernel is the all-FMA build for shapes
+// the tensor-core build does not take and for cross-checks (FORGE_SOLVER_IMPL=simt).  In solve_kernel, for a
+// 128-column block starting at column bs a thread holds its row's 128 values in registers:
 //   1. x[k] = W[bs+k] - sum_{j<bs} err_j * U[j, bs+k]      lazy ("left-looking") update from every
 //      earlier column: the errors E[j, r] stream from global memory, the U panel [32 x 128] is staged
 //      in shared memory by cp.async, double buffered;
