@@ -488,8 +488,11 @@ def run_ours(args, rank, world, local_rank):
                 inv = 3.0 if top == "forge_chol_inv_upper_batched" else 1.0    # + triangular inverse (2/3 n^3 more)
                 flops = n_loc * inv * (Hd ** 3 + I ** 3) / 3.0
             ach = flops / t_s / 1e12
+            # DRAM bytes of the solver: ncu capture of a 32-expert cut of this very workload (4.81 GB for the three
+            # launches = 150.4 MB per expert), scaled by the experts of this rank; other shapes: not captured
+            traffic = 150.4e6 * n_loc if (top == "forge_gptq_solve_batched" and args.config == "qwen3_30b_a3b") else None
             roofline = {"kernel": top, "bound": "tensor", "achieved": ach, "peak": tf_peak, "unit": "TFLOP/s",
-                        "frac": ach / tf_peak, "traffic": None, "peak_source": tf_src,
+                        "frac": ach / tf_peak, "traffic": traffic, "peak_source": tf_src,
                         "executed_tf32_tflops": 3.0 * ach, "tf32_peak_assumed": tf_peak / 2.0,
                         "executed_frac_of_tf32_peak": 3.0 * ach / (tf_peak / 2.0),
                         "note": "fp32 algorithm as TF32 x3 on tcgen05; the column loop between the MMAs is a serial "
