@@ -376,6 +376,154 @@ extern "C" int forge_hessian_gather_damp(const float *H, int nb, int64_t C, cons
 }
 
 // --------------------------------------------------------------------------------------------
+// Packed-int4 checkpoint weights (compressed-tensors "pack-quantized", e.g. Kimi-K2) -> dense:
+//   out[o, i] = dtype( fp32(nibble) * sf[o, i / gs] ),  nibble i%8 of packed[o, i/8] at bits [4(i%8), +4),
+//   two's-complement int4 when `symmetric`, unsigned otherwise; sf = scale, or 1/scale when scale_is_inv.
+// Restates _apply_block_scale, forge/utils/io.py:722-808 (bits = 4, scales [O, I/gs]) on the device.
+// One thread per packed word: 4 B in, 8 outputs (16 B of bf16) out.
+// --------------------------------------------------------------------------------------------
+__global__ void int4_packed_dequant_kernel(const int32_t *__restrict__ packed, const float *__restrict__ scales,
+                                           int64_t O, int64_t I, int gs, int symmetric, int scale_is_inv,
+                                           void *__restrict__ out, int out_dtype) {
+    const int64_t IP = I / 8, total = O * IP;
+    const int G = (int)(I / gs);
+    const bool one_scale = (gs % 8) == 0;     // the eight values of a word share a group (the usual case)
+    for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < total;
+         w += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t o = w / IP;
+        const int i0 = (int)(w - o * IP) * 8;
+        const uint32_t word = (uint32_t)packed[w];
+        const float *srow = scales + o * G;
+        float sf0 = srow[i0 / gs];
+        if (scale_is_inv) sf0 = __fdiv_rn(1.0f, sf0);
+        float v[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            int u = (int)((word >> (4 * e)) & 0xFu);
+            if (symmetric && u >= 8) u -= 16;
+            float sf = sf0;
+            if (!one_scale) {
+                sf = srow[(i0 + e) / gs];
+                if (scale_is_inv) sf = __fdiv_rn(1.0f, sf);
+            }
+            v[e] = __fmul_rn((float)u, sf);
+        }
+        if (out_dtype == FORGE_DTYPE_BF16) {
+            __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(out) + o * I + i0;
+            uint4 pk;
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]), h1 = __floats2bfloat162_rn(v[2], v[3]);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]), h3 = __floats2bfloat162_rn(v[6], v[7]);
+            pk.x = *reinterpret_cast<uint32_t *>(&h0); pk.y = *reinterpret_cast<uint32_t *>(&h1);
+            pk.z = *reinterpret_cast<uint32_t *>(&h2); pk.w = *reinterpret_cast<uint32_t *>(&h3);
+            *reinterpret_cast<uint4 *>(dst) = pk;
+        } else {
+            float4 *dst = reinterpret_cast<float4 *>(reinterpret_cast<float *>(out) + o * I + i0);
+            dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+            dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+        }
+    }
+}
+extern "C" int forge_int4_packed_dequant(const int32_t *packed, const float *scales, int64_t O, int64_t I, int gs,
+                                         int symmetric, int scale_is_inv, void *out, int out_dtype, void *stream) {
+    FORGE_REQUIRE(packed && scales && out, "null pointer");
+    FORGE_REQUIRE(O > 0 && I > 0 && gs > 0, "bad sizes");
+    FORGE_REQUIRE(I % 8 == 0 && I % gs == 0, "I must be a multiple of 8 and of the group size");
+    FORGE_REQUIRE(out_dtype == FORGE_DTYPE_F32 || out_dtype == FORGE_DTYPE_BF16, "bad dtype");
+    FORGE_REQUIRE((uintptr_t)out % 16 == 0, "output must be 16-byte aligned");
+    const int blocks = (int)imin64(cdiv(O * (I / 8), 256), 148 * 64);
+    int4_packed_dequant_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(packed, scales, O, I, gs, symmetric,
+                                                                        scale_is_inv, out, out_dtype); FORGE_NOTE_LAUNCH();
+    return check_launch("forge_int4_packed_dequant");
+}
+
+// --------------------------------------------------------------------------------------------
+// MXFP4 checkpoint weights (gpt-oss: 16-byte blocks of 32 E2M1 codes + one E8M0 scale byte) -> dense, transposed:
+//   blocks [rows, NB, 16] u8, scales [rows, NB] u8  ->  out [NB*32, rows]:
+//   code 2k = low nibble of byte k, code 2k+1 = its high nibble; value = +-{0, .5, 1, 1.5, 2, 3, 4, 6}[code & 7];
+//   scale = 2^(e - 127), and 2^-23 for e == 0;  out[nb*32 + c, row] = dtype(value * scale).
+// Restates _dequant_mxfp4_blocks_to_fp / _e8m0_to_scale_fp32, forge/utils/io.py:505-531 (including its final
+// transpose of the last two dimensions).  A CTA converts a [64 rows] x [4 blocks = 128 codes] tile through shared
+// memory: 16-byte block reads (four neighbouring blocks = 64 contiguous bytes), transposed writes of 64 rows each.
+// --------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) mxfp4_dequant_kernel(const uint8_t *__restrict__ blocks,
+                                                            const uint8_t *__restrict__ scales, int64_t rows, int64_t NB,
+                                                            void *__restrict__ out, int out_dtype) {
+    // tile: 64 rows x 4 blocks (128 output columns), tile[code * 4 + block][row]; with a pitch of 72 floats the 32
+    // lanes of a writing warp (8 rows x 4 blocks) hit 32 different banks, and the 8-byte reads below stay aligned
+    __shared__ __align__(8) float tile[128][72];
+    // signed E2M1 values by 4-bit code; sixteen words in sixteen banks, so any mix of lookups is conflict-free
+    __shared__ float lut[16];
+    const int tid = threadIdx.x;
+    if (tid < 16) {
+        const int m = tid & 7;
+        const float mag = (m < 2) ? 0.5f * (float)m : __int_as_float(((126 + (m >> 1)) << 23) | ((m & 1) << 22));
+        lut[tid] = (tid & 8) ? -mag : mag;
+    }
+    __syncthreads();
+    const int64_t nb0 = (int64_t)blockIdx.x * 4, r0 = (int64_t)blockIdx.y * 64;
+    {
+        // read: thread -> (row = tid / 4, block = tid % 4): one 16-byte block and its scale byte
+        const int rr = tid >> 2, bb = tid & 3;
+        const int64_t row = r0 + rr, nb = nb0 + bb;
+        if (row < rows && nb < NB) {
+            const uint4 raw = *reinterpret_cast<const uint4 *>(blocks + (row * NB + nb) * 16);
+            const int e = scales[row * NB + nb];
+            // 2^(e-127) is the fp32 whose exponent field is e (e = 255 gives +inf, as 2^128 does in fp32)
+            const float sc = (e == 0) ? 1.1920928955078125e-07f : __int_as_float(e << 23);
+            const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+                const uint32_t byte = (words[k >> 2] >> (8 * (k & 3))) & 0xFFu;
+                const int lo = (int)(byte & 0xFu), hi = (int)(byte >> 4);
+                const float vlo = lut[lo], vhi = lut[hi];
+                tile[(2 * k) * 4 + bb][rr] = __fmul_rn(vlo, sc);
+                tile[(2 * k + 1) * 4 + bb][rr] = __fmul_rn(vhi, sc);
+            }
+        }
+    }
+    __syncthreads();
+    // write: warp w takes columns w, w + 8, ...; a lane writes rows 2 lane, 2 lane + 1 (128 B of bf16 per warp)
+    const int warp = tid >> 5, lane = tid & 31;
+    const bool pair_ok = (rows & 1) == 0;
+    for (int c = warp; c < 128; c += 8) {
+        const int64_t nb = nb0 + (c & 3);
+        if (nb >= NB) continue;
+        const int64_t col = nb * 32 + (c >> 2);
+        const int64_t row = r0 + 2 * lane;
+        const float2 vv = *reinterpret_cast<const float2 *>(&tile[c][2 * lane]);
+        const float v0 = vv.x, v1 = vv.y;
+        if (out_dtype == FORGE_DTYPE_BF16) {
+            __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(out) + col * rows + row;
+            if (pair_ok && row + 1 < rows) {
+                *reinterpret_cast<__nv_bfloat162 *>(dst) = __floats2bfloat162_rn(v0, v1);
+            } else {
+                if (row < rows) dst[0] = __float2bfloat16_rn(v0);
+                if (row + 1 < rows) dst[1] = __float2bfloat16_rn(v1);
+            }
+        } else {
+            float *dst = reinterpret_cast<float *>(out) + col * rows + row;
+            if (pair_ok && row + 1 < rows) {
+                *reinterpret_cast<float2 *>(dst) = make_float2(v0, v1);
+            } else {
+                if (row < rows) dst[0] = v0;
+                if (row + 1 < rows) dst[1] = v1;
+            }
+        }
+    }
+}
+extern "C" int forge_mxfp4_dequant(const uint8_t *blocks, const uint8_t *scales, int64_t rows, int64_t NB, void *out,
+                                   int out_dtype, void *stream) {
+    FORGE_REQUIRE(blocks && scales && out, "null pointer");
+    FORGE_REQUIRE(rows > 0 && NB > 0 && NB < 65536 * 32, "bad sizes");
+    FORGE_REQUIRE(out_dtype == FORGE_DTYPE_F32 || out_dtype == FORGE_DTYPE_BF16, "bad dtype");
+    FORGE_REQUIRE(cdiv(rows, 64) <= 65535, "too many rows for one launch");
+    FORGE_REQUIRE((uintptr_t)blocks % 16 == 0 && (uintptr_t)out % 8 == 0, "blocks must be 16-byte aligned");
+    dim3 grid((unsigned)cdiv(NB, 4), (unsigned)cdiv(rows, 64));
+    mxfp4_dequant_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(blocks, scales, rows, NB, out, out_dtype); FORGE_NOTE_LAUNCH();
+    return check_launch("forge_mxfp4_dequant");
+}
+
+// --------------------------------------------------------------------------------------------
 // de-quantise codes: out = (q - q0) * s in fp32   (forge/utils/engine.py:93-96)
 // --------------------------------------------------------------------------------------------
 __global__ void dequant_kernel(const uint8_t *__restrict__ q, const float *__restrict__ scales,

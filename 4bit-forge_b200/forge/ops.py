@@ -25,6 +25,36 @@ def fp8_block_dequant(w_fp8: torch.Tensor, scale_inv: torch.Tensor, out=None) ->
     return out
 
 
+def int4_packed_dequant(packed: torch.Tensor, scales: torch.Tensor, shape, symmetric: bool = True,
+                        scale_is_inv: bool = False, dtype=torch.bfloat16) -> torch.Tensor:
+    """Packed int32 [O, I/8] + per-group scales [O, I/gs] -> dense [O, I] — forge/utils/io.py:722-808 on the device."""
+    O, I = int(shape[0]), int(shape[1])
+    sc = scales.to(torch.float32).contiguous()
+    assert (O * I) % sc.numel() == 0
+    gs = (O * I) // sc.numel()
+    out = torch.empty((O, I), dtype=dtype, device=_dev(packed))
+    code = _abi.BF16 if dtype == torch.bfloat16 else _abi.F32
+    assert dtype in (torch.float32, torch.bfloat16)
+    call("forge_int4_packed_dequant", ptr(packed.to(torch.int32).contiguous()), ptr(sc), O, I, gs, int(symmetric),
+         int(scale_is_inv), ptr(out), code, stream_ptr())
+    return out
+
+
+def mxfp4_dequant(blocks_u8: torch.Tensor, scales_u8: torch.Tensor, dtype=torch.bfloat16) -> torch.Tensor:
+    """blocks [..., rows, NB, 16] u8 + scales [..., rows, NB] u8 -> [..., NB*32, rows] — forge/utils/io.py:505-531 on the
+    device (the transpose of the last two dimensions included)."""
+    lead = blocks_u8.shape[:-3]
+    rows, NB = int(blocks_u8.shape[-3]), int(blocks_u8.shape[-2])
+    b = blocks_u8.contiguous().view(-1, rows, NB, 16)
+    s = scales_u8.contiguous().view(-1, rows, NB)
+    out = torch.empty((b.shape[0], NB * 32, rows), dtype=dtype, device=_dev(blocks_u8))
+    code = _abi.BF16 if dtype == torch.bfloat16 else _abi.F32
+    assert dtype in (torch.float32, torch.bfloat16)
+    for k in range(b.shape[0]):
+        call("forge_mxfp4_dequant", ptr(b[k]), ptr(s[k]), rows, NB, ptr(out[k]), code, stream_ptr())
+    return out.view(*lead, NB * 32, rows)
+
+
 def route_build_lists(topk_ids: torch.Tensor, e_begin: int, e_count: int):
     """topk_ids [T,k] int32 -> (counts int32 [e_count], offsets int64 [e_count+1], token_lists int32 [T*k])."""
     T, k = topk_ids.shape

@@ -200,6 +200,19 @@ int forge_gptq_solve_batched(const void *W, int w_dtype, int nb, int64_t R, int6
                              const float *scales, const float *qzeros, int gs, int bits, int sparse14,
                              int form, uint8_t *qweight, uint32_t *M, void *ws, int32_t *status, void *stream);
 
+/* ---- checkpoint weight materialisation on the device (callers of the path) -----
+ * Packed int4 ("pack-quantized", e.g. Kimi-K2): packed int32 [O, I/8] + scales fp32 [O, I/gs] -> dense [O, I]
+ * (bf16 or fp32): out = fp32(nibble) * scale (or * 1/scale when scale_is_inv); nibbles are two's-complement int4 when
+ * symmetric, unsigned otherwise.  Replaces _apply_block_scale, forge/utils/io.py:722-808 (CPU torch there). */
+int forge_int4_packed_dequant(const int32_t *packed, const float *scales, int64_t O, int64_t I, int gs,
+                              int symmetric, int scale_is_inv, void *out, int out_dtype, void *stream);
+
+/* MXFP4 (gpt-oss): blocks u8 [rows, NB, 16] (32 E2M1 codes each, low nibble first) + E8M0 scales u8 [rows, NB]
+ * -> dense, TRANSPOSED like the reference: out [NB*32, rows] (bf16 or fp32); scale = 2^(e-127), 2^-23 for e == 0.
+ * Replaces _dequant_mxfp4_blocks_to_fp / _e8m0_to_scale_fp32, forge/utils/io.py:505-531. */
+int forge_mxfp4_dequant(const uint8_t *blocks, const uint8_t *scales, int64_t rows, int64_t NB, void *out,
+                        int out_dtype, void *stream);
+
 /* ---- A12: de-quantise codes ------------------------------------------------
  * out[r,c] = dtype( (q[r,c] - qzeros[r,c/gs]) * scales[r,c/gs] )   (fp32 arithmetic)
  * Replaces dequantize_forge_full, forge/utils/engine.py:72-97. */

@@ -339,3 +339,37 @@ def swiglu_down_input(x: torch.Tensor, wg: torch.Tensor, wu: torch.Tensor) -> to
     g = (x.to(torch.float32) @ wg.to(torch.float32).T).to(torch.bfloat16)
     u = (x.to(torch.float32) @ wu.to(torch.float32).T).to(torch.bfloat16)
     return (torch.nn.functional.silu(g.to(torch.float32)).to(torch.bfloat16) * u)
+
+
+# --------------------------------------------------------------------------- #
+# checkpoint weight materialisation (forge/utils/io.py)
+# --------------------------------------------------------------------------- #
+_MXFP4_MAG = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0], dtype=np.float32)
+
+
+def int4_packed_dequant(packed: torch.Tensor, scales: torch.Tensor, shape, symmetric=True, scale_is_inv=False):
+    """_apply_block_scale, forge/utils/io.py:722-808 (bits = 4, scales [O, I/gs]) in numpy: fp32 [O, I]."""
+    O, I = int(shape[0]), int(shape[1])
+    w = packed.numpy().astype(np.int64) & 0xFFFFFFFF
+    sf = scales.to(torch.float32).numpy()
+    if scale_is_inv:
+        sf = (np.float32(1.0) / sf).astype(np.float32)
+    gs = (O * I) // sf.size
+    u = np.stack([(w >> (4 * i)) & 0xF for i in range(8)], axis=-1).reshape(O, I).astype(np.int32)
+    if symmetric:
+        u = np.where(u >= 8, u - 16, u)
+    return torch.from_numpy(u.astype(np.float32) * np.repeat(sf.reshape(O, I // gs), gs, axis=1))
+
+
+def mxfp4_dequant(blocks_u8: torch.Tensor, scales_u8: torch.Tensor):
+    """_dequant_mxfp4_blocks_to_fp with _e8m0_to_scale_fp32, forge/utils/io.py:505-531 in numpy: fp32
+    [..., NB*32, rows] (the reference's transpose of the last two dimensions included)."""
+    b = blocks_u8.numpy().astype(np.uint8)
+    codes = np.stack([b & 0x0F, (b >> 4) & 0x0F], axis=-1).reshape(*b.shape[:-1], 32)
+    vals = _MXFP4_MAG[codes & 7]
+    vals = np.where((codes & 8) != 0, -vals, vals)
+    e = scales_u8.numpy().astype(np.int32)
+    with np.errstate(over="ignore"):
+        sc = np.where(e == 0, np.float32(2.0 ** -23), np.power(np.float32(2.0), (e - 127).astype(np.float32))).astype(np.float32)
+    out = (vals * sc[..., None]).astype(np.float32).reshape(*vals.shape[:-2], vals.shape[-2] * 32)
+    return torch.from_numpy(np.ascontiguousarray(np.swapaxes(out, -1, -2)))

@@ -3,6 +3,8 @@
 Tolerances (from the acceptance rules of the path): integer / byte outputs bit-exact; Hessians within 1e-4
 relative Frobenius error of the fp32 torch path; solver codes >= 99.5 % equal to the oracle's.
 """
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -526,3 +528,42 @@ def test_pruned_scale_search_equals_exhaustive(rows, C, dtype, sym, P, monkeypat
     assert torch.equal(s2, s_ref) and torch.equal(z2, z_ref)
     if P >= 100:
         assert float((s_ref < s0).float().mean()) > 0.2      # the search did move scales
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("sym", [True, False])
+@pytest.mark.parametrize("inv", [False, True])
+def test_int4_packed_dequant_against_reference_vectors(sym, inv):
+    """forge_int4_packed_dequant against the reference's _apply_block_scale outputs (golden) and, at a checkpoint-sized
+    shape, against the oracle."""
+    import numpy as np
+    from forge import ops
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", "io_materialise.npz"))
+    packed, scales = torch.from_numpy(z["int4_packed"]), torch.from_numpy(z["int4_scales"])
+    want = torch.from_numpy(z[f"int4_out_sym{int(sym)}_inv{int(inv)}"])
+    got = ops.int4_packed_dequant(packed.cuda(), scales.cuda(), want.shape, sym, inv, dtype=torch.float32)
+    assert torch.equal(got.cpu(), want)
+    got16 = ops.int4_packed_dequant(packed.cuda(), scales.cuda(), want.shape, sym, inv, dtype=torch.bfloat16)
+    assert torch.equal(got16.cpu(), want.to(torch.bfloat16))
+    g = torch.Generator().manual_seed(5)
+    Ob, Ib = 2048, 7168
+    pk = torch.randint(-2 ** 31, 2 ** 31 - 1, (Ob, Ib // 8), generator=g, dtype=torch.int64).to(torch.int32)
+    sc = torch.rand(Ob, Ib // 32, generator=g) * 0.01 + 1e-4
+    big = ops.int4_packed_dequant(pk.cuda(), sc.cuda(), (Ob, Ib), sym, inv, dtype=torch.float32)
+    assert torch.equal(big.cpu(), O.int4_packed_dequant(pk, sc, (Ob, Ib), sym, inv))
+
+
+@pytest.mark.gpu
+def test_mxfp4_dequant_against_reference_vectors():
+    import numpy as np
+    from forge import ops
+    z = np.load(os.path.join(os.path.dirname(__file__), "golden", "io_materialise.npz"))
+    blocks, scales, want = (torch.from_numpy(z[k]) for k in ("mx_blocks", "mx_scales", "mx_out"))
+    got = ops.mxfp4_dequant(blocks.cuda(), scales.cuda(), dtype=torch.float32)
+    assert got.shape == want.shape and torch.equal(got.cpu(), want)
+    assert torch.equal(ops.mxfp4_dequant(blocks.cuda(), scales.cuda()).cpu(), want.to(torch.bfloat16))
+    g = torch.Generator().manual_seed(6)
+    b = torch.randint(0, 256, (2880, 90, 16), generator=g, dtype=torch.int64).to(torch.uint8)   # gpt-oss sized rows
+    s = torch.randint(100, 140, (2880, 90), generator=g, dtype=torch.int64).to(torch.uint8)
+    big = ops.mxfp4_dequant(b.cuda(), s.cuda(), dtype=torch.float32)
+    assert torch.equal(big.cpu(), O.mxfp4_dequant(b, s))
