@@ -81,11 +81,13 @@ def _hessian_ref(X, idx_lists, n_prev=None, H_prev=None):
 
 
 @pytest.mark.parametrize("simt", [True, False])
-@pytest.mark.parametrize("C,counts", [(64, [5]), (256, [64, 1, 0, 130]), (320, [200, 63]), (512, [700, 65, 129])])
+@pytest.mark.parametrize("C,counts", [(64, [5]), (256, [64, 1, 0, 130]), (320, [200, 63]), (512, [700, 65, 129]),
+                                        (512, [1000, 3, 2, 1]), (768, [1024, 5, 0, 7])])   # one popular expert among idle ones
 def test_hessian_grouped_matches_fp32_torch(simt, C, counts):
     ops = _ops()
     g = torch.Generator().manual_seed(3)
     T = 1024
+    assert max(counts) <= T
     X = (torch.randn(T, C, generator=g) * torch.exp(torch.randn(C, generator=g))).to(torch.bfloat16)
     lists = [torch.randperm(T, generator=g)[:n].sort().values for n in counts]
     offsets = torch.tensor([0] + list(np.cumsum(counts)), dtype=torch.int64)
