@@ -74,7 +74,8 @@ int forge_route_build_lists(const int32_t *topk_ids, int64_t T, int k, int e_beg
  * updated (forge_counts_add does that).  C must be a multiple of 8.
  * `status` (device int32, may be NULL) receives FORGE_ERR_TIMEOUT if a bounded
  * wait inside the kernel ran out.
- * Replaces GPTQ.update, forge/gptq.py:62-80 (H.addmm_ at :76-79).  * Preconditions the library cannot check (they live in device memory): offsets is non-decreasing, token_idx
+ * Replaces GPTQ.update, forge/gptq.py:62-80 (H.addmm_ at :76-79).
+ * Preconditions the library cannot check (they live in device memory): offsets is non-decreasing, token_idx
  * (when given) holds at least offsets[nb] entries, each a valid row of X; with token_idx = NULL the rows
  * offsets[b] .. offsets[b+1]-1 of X are used.  A token list shorter than the offsets claim is read out of bounds.
  */
