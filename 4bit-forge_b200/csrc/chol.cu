@@ -623,11 +623,8 @@ static void launch_factor(float *A, int nb, int64_t C, float *U, float *udiag, i
     // the last 256 bytes of the workspace hold the status word of the tensor-core kernels
     int32_t *status = reinterpret_cast<int32_t *>(reinterpret_cast<char *>(dinv) + forge_chol_workspace_bytes(nb, C) - 256);
     const int nblk = (int)cdiv(C, NB);
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaFuncSetAttribute(chol_syrk_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSyrkSmem);
-        attr_done = true;
-    }
+    // per-device attribute: set on the device that is current for this call
+    cudaFuncSetAttribute(chol_syrk_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSyrkSmem);
     const char *env = getenv("FORGE_SYRK_IMPL");
     const bool syrk_simt = env && strcmp(env, "simt") == 0;   // cross-checks: plain-FMA trailing update
     const int64_t outer = (C >= 4096) ? 2 * kOuter : kOuter;   // measured: wider outer blocks pay from C ~ 4096 on

@@ -44,6 +44,8 @@ struct HessParams {
     int64_t ldx, C;
     const int32_t *token_idx;
     const int64_t *offsets;
+    int64_t n_rows;    // rows of X
+    int64_t list_len;  // entries of token_idx (or n_rows when the rows are contiguous)
     int nb;
     float *H;
     const int64_t *n_prev;
@@ -73,6 +75,11 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t adesc, uint6
         :
         : "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(kIdesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
         : "memory");
+}
+// A slot whose offsets claim rows outside the token list (or outside X when the rows are contiguous) is skipped
+// by every role alike; the status word then says FORGE_ERR_INVALID.  Nothing is read through a bad claim.
+__device__ __forceinline__ bool slot_in_bounds(const HessParams &P, int64_t off, int64_t n) {
+    return off >= 0 && n >= 0 && off + n <= P.list_len;
 }
 __device__ __forceinline__ void tile_coords(int p, int nt, int &ti, int &tj) {
     ti = 0;
@@ -130,6 +137,10 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_tc_kernel(const HessParam
             tile_coords(tile % P.ntri, P.nt, ti, tj);
             const int64_t off = P.offsets[b];
             const int64_t n = P.offsets[b + 1] - off;
+            if (!slot_in_bounds(P, off, n)) {
+                if (tid == 0 && P.status) atomicExch(P.status, FORGE_ERR_INVALID);
+                continue;
+            }
             if (n <= 0) continue;
             const bool diag = (ti == tj);
             const int nkt = (int)((n + kKT - 1) / kKT);
@@ -143,7 +154,13 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_tc_kernel(const HessParam
                 for (int i = 0; i < 4; ++i) {
                     const int64_t kidx = (int64_t)kt * kKT + warp * 16 + i * 4 + rsub;
                     int32_t t = -1;
-                    if (kidx < n) t = tl ? tl[kidx] : (int32_t)(off + kidx);
+                    if (kidx < n) {
+                        t = tl ? tl[kidx] : (int32_t)(off + kidx);
+                        if ((int64_t)t < 0 || (int64_t)t >= P.n_rows) {  // not a row of X: contributes zeros
+                            if (P.status) atomicExch(P.status, FORGE_ERR_INVALID);
+                            t = -1;
+                        }
+                    }
                     dst[i] = t;
                 }
             };
@@ -261,7 +278,7 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_tc_kernel(const HessParam
             int ti, tj;
             tile_coords(tile % P.ntri, P.nt, ti, tj);
             const int64_t n = P.offsets[b + 1] - P.offsets[b];
-            if (n <= 0) continue;
+            if (n <= 0 || !slot_in_bounds(P, P.offsets[b], n)) continue;
             const bool diag = (ti == tj);
             const int nkt = (int)((n + kKT - 1) / kKT);
             bool ok = mbar_wait(bar_acc_empty, (tile_iter & 1u) ^ 1u, abort_flag);
@@ -316,6 +333,10 @@ __global__ void hessian_simt_kernel(const HessParams P) {
     if (n0 + 15 < m0) return;
     const int64_t off = P.offsets[b];
     const int64_t n = P.offsets[b + 1] - off;
+    if (!slot_in_bounds(P, off, n)) {
+        if (threadIdx.x == 0 && threadIdx.y == 0 && P.status) atomicExch(P.status, FORGE_ERR_INVALID);
+        return;
+    }
     if (n <= 0) return;
     const int32_t *tl = P.token_idx ? P.token_idx + off : nullptr;
     const int tx = threadIdx.x, ty = threadIdx.y;
@@ -323,8 +344,9 @@ __global__ void hessian_simt_kernel(const HessParams P) {
     for (int64_t k0 = 0; k0 < n; k0 += 16) {
         const int64_t kidx = k0 + ty;
         float va = 0.0f, vb = 0.0f;
-        if (kidx < n) {
-            const int64_t tok = tl ? (int64_t)tl[kidx] : off + kidx;
+        const int64_t tok = (kidx < n) ? (tl ? (int64_t)tl[kidx] : off + kidx) : -1;
+        if (kidx < n && (tok < 0 || tok >= P.n_rows) && P.status) atomicExch(P.status, FORGE_ERR_INVALID);
+        if (tok >= 0 && tok < P.n_rows) {
             if (m0 + tx < C) va = __bfloat162float(P.X[tok * P.ldx + m0 + tx]);
             if (n0 + tx < C) vb = __bfloat162float(P.X[tok * P.ldx + n0 + tx]);
         }
@@ -374,14 +396,17 @@ extern "C" int forge_selftest_bounded_wait(int32_t *status, int64_t budget_cycle
     return check_launch("forge_selftest_bounded_wait");
 }
 
-extern "C" int forge_hessian_grouped(const void *X_bf16, int64_t ldx, int64_t C, const int32_t *token_idx,
-                                     const int64_t *offsets, int nb, float *H, const int64_t *n_prev, int flags,
-                                     int32_t *status, void *stream) {
+extern "C" int forge_hessian_grouped(const void *X_bf16, int64_t n_rows, int64_t ldx, int64_t C,
+                                     const int32_t *token_idx, int64_t list_len, const int64_t *offsets, int nb,
+                                     float *H, const int64_t *n_prev, int flags, int32_t *status, void *stream) {
     FORGE_REQUIRE(X_bf16 && offsets && H, "null pointer");
     FORGE_REQUIRE(nb > 0 && C > 0 && ldx >= C, "bad sizes");
+    FORGE_REQUIRE(n_rows >= 0 && n_rows <= 0x7fffffffLL, "n_rows must fit a 32-bit token index");
+    FORGE_REQUIRE(!token_idx || list_len >= 0, "list_len must be >= 0");
     cudaStream_t st = (cudaStream_t)stream;
     HessParams P{};
     P.X = (const __nv_bfloat16 *)X_bf16; P.ldx = ldx; P.C = C; P.token_idx = token_idx; P.offsets = offsets;
+    P.n_rows = n_rows; P.list_len = token_idx ? list_len : n_rows;
     P.nb = nb; P.H = H; P.n_prev = n_prev; P.mirror = (flags & FORGE_HESS_MIRROR) ? 1 : 0; P.status = status;
     P.nt = (int)cdiv(C, kTile);
     P.ntri = P.nt * (P.nt + 1) / 2;
@@ -392,15 +417,13 @@ extern "C" int forge_hessian_grouped(const void *X_bf16, int64_t ldx, int64_t C,
     }
     FORGE_REQUIRE(C % 8 == 0 && ldx % 8 == 0, "C and ldx must be multiples of 8 (16-byte row chunks)");
     FORGE_REQUIRE((uintptr_t)X_bf16 % 16 == 0, "X must be 16-byte aligned");
-    static bool attr_done = false;
-    if (!attr_done) {
+    {   // per-device attribute: set on the device that is current for this call
         cudaError_t e = cudaFuncSetAttribute(hessian_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)kSmemBytes);
         if (e != cudaSuccess) {
             set_error("forge_hessian_grouped: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
             return FORGE_ERR_LAUNCH;
         }
-        attr_done = true;
     }
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);

@@ -126,25 +126,51 @@ __global__ void route_scan_kernel(const int32_t *__restrict__ ids, int64_t T, in
     if (!FILL && threadIdx.x == 0) counts[e_local] = base_s;
 }
 
-__global__ void route_offsets_kernel(const int32_t *__restrict__ counts, int n, int64_t *__restrict__ offsets) {
+// offsets = exclusive prefix sum of counts; the `tail` dense slots behind the routed ones see every token
+__global__ void route_offsets_kernel(int32_t *__restrict__ counts, int n, int tail, int64_t T,
+                                     int64_t *__restrict__ offsets) {
     if (threadIdx.x == 0 && blockIdx.x == 0) {
         int64_t acc = 0;
         for (int i = 0; i < n; ++i) {
             offsets[i] = acc;
             acc += counts[i];
         }
-        offsets[n] = acc;
+        for (int i = n; i < n + tail; ++i) {
+            counts[i] = (int32_t)T;
+            offsets[i] = acc;
+            acc += T;
+        }
+        offsets[n + tail] = acc;
     }
 }
 
+// token list of a dense slot: 0, 1, ..., T-1
+__global__ void route_dense_fill_kernel(const int64_t *__restrict__ offsets, int n, int64_t T,
+                                        int32_t *__restrict__ lists) {
+    const int64_t base = offsets[n + blockIdx.y];
+    for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < T; t += (int64_t)gridDim.x * blockDim.x)
+        lists[base + t] = (int32_t)t;
+}
+
 extern "C" int forge_route_build_lists(const int32_t *topk_ids, int64_t T, int k, int e_begin, int e_count,
-                                       int32_t *counts, int64_t *offsets, int32_t *token_lists, void *stream) {
-    FORGE_REQUIRE(topk_ids && counts && offsets && token_lists, "null pointer");
-    FORGE_REQUIRE(T >= 0 && k > 0 && e_count > 0 && e_begin >= 0, "bad sizes");
+                                       int dense_tail, int32_t *counts, int64_t *offsets, int32_t *token_lists,
+                                       void *stream) {
+    FORGE_REQUIRE(counts && offsets && token_lists, "null pointer");
+    FORGE_REQUIRE(T >= 0 && k > 0 && e_count >= 0 && dense_tail >= 0 && e_count + dense_tail > 0 && e_begin >= 0,
+                  "bad sizes");
+    FORGE_REQUIRE(e_count == 0 || topk_ids, "null pointer");
     cudaStream_t st = (cudaStream_t)stream;
-    route_scan_kernel<false><<<e_count, 512, 0, st>>>(topk_ids, T, k, e_begin, counts, nullptr, nullptr); FORGE_NOTE_LAUNCH();
-    route_offsets_kernel<<<1, 32, 0, st>>>(counts, e_count, offsets); FORGE_NOTE_LAUNCH();
-    route_scan_kernel<true><<<e_count, 512, 0, st>>>(topk_ids, T, k, e_begin, counts, offsets, token_lists); FORGE_NOTE_LAUNCH();
+    if (e_count > 0) {
+        route_scan_kernel<false><<<e_count, 512, 0, st>>>(topk_ids, T, k, e_begin, counts, nullptr, nullptr); FORGE_NOTE_LAUNCH();
+    }
+    route_offsets_kernel<<<1, 32, 0, st>>>(counts, e_count, dense_tail, T, offsets); FORGE_NOTE_LAUNCH();
+    if (e_count > 0) {
+        route_scan_kernel<true><<<e_count, 512, 0, st>>>(topk_ids, T, k, e_begin, counts, offsets, token_lists); FORGE_NOTE_LAUNCH();
+    }
+    if (dense_tail > 0 && T > 0) {
+        route_dense_fill_kernel<<<dim3((unsigned)imin64(cdiv(T, 256), 592), dense_tail), 256, 0, st>>>(offsets, e_count, T, token_lists);
+        FORGE_NOTE_LAUNCH();
+    }
     return check_launch("forge_route_build_lists");
 }
 
@@ -365,11 +391,9 @@ extern "C" int forge_hessian_gather_damp(const float *H, int nb, int64_t C, cons
     cudaStream_t st = (cudaStream_t)stream;
     damp_kernel<<<nb, 256, 0, st>>>(H, C, perm, pruned, wzero, invalid, rel_damp, damp_out); FORGE_NOTE_LAUNCH();
     const size_t smem = (size_t)C * 4;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaFuncSetAttribute(gather_damp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        attr_done = true;
-    }
+    // the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute: set it on the device that is
+    // current for this call (a process-wide "done" flag would leave a second GPU without it)
+    cudaFuncSetAttribute(gather_damp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     gather_damp_kernel<<<dim3((unsigned)C, nb), 256, smem, st>>>(H, C, perm, pruned, wzero, invalid, damp_out, A,
                                                                 Hp_out); FORGE_NOTE_LAUNCH();
     return check_launch("forge_hessian_gather_damp");

@@ -798,16 +798,12 @@ inline bool use_tc_solver(const SolveParams &p) {
 
 template <int MODE, bool SPARSE>
 int launch_solve(const SolveParams &p, int nb, int32_t *status, cudaStream_t st) {
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaFuncSetAttribute(solve_kernel<MODE, SPARSE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)kSolveSmem);
-        cudaFuncSetAttribute(solve_tc_kernel<MODE, SPARSE, kTcRawFull>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)tc_smem_bytes(kTcRawFull));
-        cudaFuncSetAttribute(solve_tc_kernel<MODE, SPARSE, kTcRawDeep>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)tc_smem_bytes(kTcRawDeep));
-        attr_done = true;
-    }
+    // per-device attributes: set on the device that is current for this call
+    cudaFuncSetAttribute(solve_kernel<MODE, SPARSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSolveSmem);
+    cudaFuncSetAttribute(solve_tc_kernel<MODE, SPARSE, kTcRawFull>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)tc_smem_bytes(kTcRawFull));
+    cudaFuncSetAttribute(solve_tc_kernel<MODE, SPARSE, kTcRawDeep>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)tc_smem_bytes(kTcRawDeep));
     dim3 grid((unsigned)cdiv(p.R, kBlk), (unsigned)nb);
     if (use_tc_solver(p)) {
         if ((int64_t)grid.x * grid.y <= 2 * 148) {

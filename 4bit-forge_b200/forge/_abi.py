@@ -16,7 +16,9 @@ LIB_PATH = os.path.join(_PKG_ROOT, "libforge_b200.so")
 
 F32, BF16 = 0, 1
 HESS_MIRROR, HESS_SIMT = 1, 2
-ERR_TIMEOUT = 3
+FWD_SIMT = 1
+ROUTE_MODES = {"softmax": 0, "sigmoid": 1, "sigmoid_group": 2}
+ERR_INVALID, ERR_TIMEOUT = 1, 3
 
 _c_i64 = ctypes.c_int64
 _c_int = ctypes.c_int
@@ -29,8 +31,13 @@ _PROTOS = {
     "forge_last_error": (ctypes.c_char_p, []),
     "forge_launch_count": (ctypes.c_longlong, []),
     "forge_fp8_block_dequant": (_c_int, [_ptr, _ptr, _ptr, _c_i64, _c_i64, _c_i64, _c_i64, _ptr]),
-    "forge_route_build_lists": (_c_int, [_ptr, _c_i64, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr]),
-    "forge_hessian_grouped": (_c_int, [_ptr, _c_i64, _c_i64, _ptr, _ptr, _c_int, _ptr, _ptr, _c_int, _ptr, _ptr]),
+    "forge_route_topk": (_c_int, [_ptr, _ptr, _c_i64, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr]),
+    "forge_route_build_lists": (_c_int, [_ptr, _c_i64, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr]),
+    "forge_expert_swiglu_grouped": (_c_int, [_ptr, _c_i64, _c_i64, _c_i64, _c_i64, _ptr, _c_i64, _ptr, _c_int, _ptr, _ptr,
+                                             _ptr, _c_i64, _c_int, _ptr, _ptr]),
+    "forge_recon_loss": (_c_int, [_ptr, _c_int, _ptr, _ptr, _ptr, _c_int, _c_int, _c_i64, _c_i64, _ptr, _c_i64, _c_i64,
+                                  _ptr, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr]),
+    "forge_hessian_grouped": (_c_int, [_ptr, _c_i64, _c_i64, _c_i64, _ptr, _c_i64, _ptr, _c_int, _ptr, _ptr, _c_int, _ptr, _ptr]),
     "forge_selftest_bounded_wait": (_c_int, [_ptr, _c_i64, _ptr]),
     "forge_int4_packed_dequant": (_c_int, [_ptr, _ptr, _c_i64, _c_i64, _c_int, _c_int, _c_int, _ptr, _c_int, _ptr]),
     "forge_mxfp4_dequant": (_c_int, [_ptr, _ptr, _c_i64, _c_i64, _ptr, _c_int, _ptr]),

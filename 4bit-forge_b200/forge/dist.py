@@ -71,45 +71,110 @@ def placement_tables(owned: List[List[int]], n_experts: int):
 
 
 def broadcast_inputs(X: torch.Tensor, topk_ids: torch.Tensor, src: int = 0, chunks: int = 1):
-    """Broadcast the calibration input [T,H] and the routing table [T,k] from `src` (in place)."""
+    """Broadcast the calibration input [T,H] and the routing table [T,k] from `src` (in place).
+
+    With chunks > 1 the rows of X travel as `chunks` separate asynchronous broadcasts and the call returns
+    (X, topk_ids, ready) at once: ready = [(row_end, wait)], one entry per chunk in row order, where wait() makes
+    the CURRENT CUDA stream wait for that chunk (it blocks the host only on gloo).  The caller hands `ready` to
+    MoELayerQuantizer.quantize_experts(x_chunks=...), which accumulates the Hessians of chunk i while chunk i+1 is
+    still in flight.  With chunks <= 1 everything is broadcast before returning and ready is None."""
     if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
-        return X, topk_ids
+        return (X, topk_ids) if chunks <= 1 else (X, topk_ids, None)
     dist.broadcast(topk_ids, src=src)
     if chunks <= 1:
         dist.broadcast(X, src=src)
-    else:
-        for part in X.chunk(chunks, dim=0):
-            dist.broadcast(part, src=src)
-    return X, topk_ids
+        return X, topk_ids
+    ready = []
+    T = X.shape[0]
+    bounds = [T * (i + 1) // chunks for i in range(chunks)]
+    t0 = 0
+    for t1 in bounds:
+        if t1 > t0:
+            work = dist.broadcast(X[t0:t1], src=src, async_op=True)
+            ready.append((t1, work.wait))
+        t0 = t1
+    return X, topk_ids, ready
 
 
-def gather_to_rank0(local: Dict[str, torch.Tensor], shapes_of_rank) -> Dict[str, List[torch.Tensor]]:
-    """Gather same-keyed tensors of every rank on rank 0 with point-to-point copies (slices may differ in
-    size, which a plain gather collective does not allow).  `shapes_of_rank(r)` -> {key: (shape, dtype)}.
-    Returns {key: [tensor of rank 0, rank 1, ...]} on rank 0 and {} elsewhere."""
+def agree_ok(ok: bool, what: str = "step") -> None:
+    """Every rank reports whether its part of the step succeeded; if any rank failed, ALL ranks raise.  Call it
+    (from a try / except around the local work) before a collective that would otherwise wait for a rank that has
+    already given up.  A rank that died without reaching this call ends the all-reduce with the process group's
+    timeout error, which is finite, instead of hanging the others."""
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        if not ok:
+            raise RuntimeError(f"forge.dist: the local {what} failed")
+        return
+    dev = torch.device("cuda", torch.cuda.current_device()) if dist.get_backend() == "nccl" else torch.device("cpu")
+    flag = torch.tensor([0 if ok else 1], dtype=torch.int32, device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.SUM)
+    bad = int(flag.item())
+    if bad:
+        raise RuntimeError(f"forge.dist: {bad} rank(s) failed their {what}"
+                           + ("" if ok else " (this rank among them)") + "; nothing was gathered")
+
+
+class GatherPlan:
+    """One exchange per step for the packed results: every rank serialises its tensors into ONE byte buffer (padded
+    to the largest rank's size) and a single gather collective delivers all of them to rank 0.  Slices differ in
+    size between ranks (experts are placed by load), which is why the buffers are padded; layouts are computed
+    once from `shapes_of_rank(r) -> {key: (shape, dtype)}`, and the send / receive buffers are allocated once and
+    reused by every step."""
+
+    ALIGN = 256
+
+    def __init__(self, shapes_of_rank, device, world=None, rank=None):
+        live = dist.is_available() and dist.is_initialized()
+        self.world = world if world is not None else (dist.get_world_size() if live else 1)
+        self.rank = rank if rank is not None else (dist.get_rank() if live else 0)
+        self.device = torch.device(device)
+        self.layouts = []
+        for r in range(self.world):
+            meta = shapes_of_rank(r)
+            lay, off = {}, 0
+            for k in sorted(meta):
+                shape, dtype = meta[k]
+                nbytes = int(torch.Size(shape).numel()) * torch.empty((), dtype=dtype).element_size()
+                lay[k] = (off, nbytes, tuple(shape), dtype)
+                off += (nbytes + self.ALIGN - 1) // self.ALIGN * self.ALIGN
+            self.layouts.append((lay, off))
+        self.max_bytes = max(max(off for _, off in self.layouts), self.ALIGN)
+        self.send = torch.empty(self.max_bytes, dtype=torch.uint8, device=self.device)
+        self.recv = None
+        if self.rank == 0 and self.world > 1:
+            self.recv = [torch.empty(self.max_bytes, dtype=torch.uint8, device=self.device) for _ in range(self.world)]
+
+    def _views(self, buf, r):
+        lay, _ = self.layouts[r]
+        return {k: buf[off:off + nbytes].view(dtype).view(shape) for k, (off, nbytes, shape, dtype) in lay.items()}
+
+    def pack(self, local: Dict[str, torch.Tensor]) -> None:
+        lay, _ = self.layouts[self.rank]
+        assert sorted(local) == sorted(lay), "result keys differ from the plan"
+        for k, (off, nbytes, shape, dtype) in lay.items():
+            t = local[k]
+            assert tuple(t.shape) == shape and t.dtype == dtype, (k, tuple(t.shape), shape, t.dtype, dtype)
+            if nbytes:
+                self.send[off:off + nbytes].view(dtype).view(shape).copy_(t)
+
+    def run(self, local: Dict[str, torch.Tensor]) -> Dict[str, List[torch.Tensor]]:
+        """Returns {key: [tensor of rank 0, rank 1, ...]} on rank 0 (views into the plan's buffers, valid until the
+        next run) and {} elsewhere."""
+        if self.world == 1:
+            return {k: [v] for k, v in local.items()}
+        self.pack(local)
+        dist.gather(self.send, gather_list=self.recv if self.rank == 0 else None, dst=0)
+        if self.rank != 0:
+            return {}
+        per_rank = [self._views(self.recv[r], r) for r in range(self.world)]
+        return {k: [per_rank[r][k] for r in range(self.world)] for k in per_rank[0]}
+
+
+def gather_to_rank0(local: Dict[str, torch.Tensor], shapes_of_rank, plan: "GatherPlan" = None):
+    """Gather same-keyed tensors of every rank on rank 0 in one collective (see GatherPlan; pass a plan built once
+    outside the step to reuse its buffers).  Returns {key: [tensor of rank 0, rank 1, ...]} on rank 0, {} elsewhere."""
     if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
         return {k: [v] for k, v in local.items()}
-    world, rank = dist.get_world_size(), dist.get_rank()
-    keys = sorted(local)
-    if rank == 0:
-        out = {k: [local[k]] for k in keys}
-        reqs = []
-        for r in range(1, world):
-            meta = shapes_of_rank(r)
-            for k in keys:
-                shape, dtype = meta[k]
-                buf = torch.empty(shape, dtype=dtype, device=local[k].device)
-                out[k].append(buf)
-                if buf.numel():
-                    reqs.append(dist.irecv(_as_bytes(buf), src=r))
-        for q in reqs:
-            q.wait()
-        return out
-    reqs = [dist.isend(_as_bytes(local[k].contiguous()), dst=0) for k in keys if local[k].numel()]
-    for q in reqs:
-        q.wait()
-    return {}
-
-
-def _as_bytes(t: torch.Tensor) -> torch.Tensor:
-    return t.view(torch.uint8) if t.dtype not in (torch.uint8,) else t
+    if plan is None:
+        plan = GatherPlan(shapes_of_rank, next(iter(local.values())).device)
+    return plan.run(local)

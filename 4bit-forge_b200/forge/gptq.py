@@ -6,7 +6,11 @@ is where the work happens:
 
 * `update` runs the tcgen05 Hessian kernel on bf16 activations (fp32 accumulation) and never syncs the
   host; the reference upcasts to fp32, calls addmm_ and reads `num_samples.item()` every call.
-* `_prep` / `_h_factor` use the scan + gather/damp kernels and the batched Cholesky (batch of one).
+* `_prep` / `_h_factor` use the scan + gather/damp kernels and the batched Cholesky (batch of one) and do not
+  read anything back either: the NaN / empty / not-positive-definite fall-backs of the reference
+  (forge/gptq.py:96-98, :172-175) happen inside the kernels.  `quantize()` ends with ONE host read, of the
+  status word of the bounded waits and bounds checks; `issue_non_invertible` reads the factorisation's info
+  flag when (and only when) a caller looks at it.
 * `quantize` feeds the fused column solver with per-group scales and the permutation directly instead
   of expanding two [C,R] fp32 tensors (forge/gptq.py:251-252); `_solver` keeps the reference's
   expanded-operand form for callers that use it.
@@ -58,10 +62,23 @@ class GPTQ(object):
         self.pruned_ids = None
         self.prepared = False
         self.perm_inv = None
-        self.issue_non_invertible = False
+        self._info = None
+        self._issue_override = None
         self._status = None
         self._invalid = None
         self.id = uuid.uuid4()
+
+    # the reference sets this attribute in _h_factor after reading info.item() (forge/gptq.py:172-175); here the
+    # flag stays on the device until somebody asks
+    @property
+    def issue_non_invertible(self):
+        if self._issue_override is not None:
+            return self._issue_override
+        return self._info is not None and int(self._info.item()) > 0
+
+    @issue_non_invertible.setter
+    def issue_non_invertible(self, value):
+        self._issue_override = bool(value)
 
     def _is_owner(self):
         return self.id == self.owner.id
@@ -76,6 +93,8 @@ class GPTQ(object):
         self.pruned_ids = None
         self.perm_inv = None
         self._status = None
+        self._info = None
+        self._issue_override = None
         torch.cuda.empty_cache()
 
     # ------------------------------------------------------------------ Hessian (forge/gptq.py:62-80)
@@ -127,8 +146,6 @@ class GPTQ(object):
             return
         o = self.owner
         C = int(o.W.shape[-1])
-        if o._status is not None and int(o._status.item()) != 0:
-            raise RuntimeError("forge_hessian_grouped: a bounded device-side wait ran out (FORGE_ERR_TIMEOUT)")
         if o.H is None:
             o.H = torch.eye(C, device=o.device, dtype=torch.float32)
             n_samples = torch.zeros(1, dtype=torch.int64, device=o.device)
@@ -159,10 +176,18 @@ class GPTQ(object):
         R, C = self.W.shape
         perm32 = self.perm.to(torch.int32).view(1, C).contiguous()
         sparse = self.algorithm == "sparsegptq"
-        U = self._U_norm if not self.issue_non_invertible else A
+        # when the factorisation failed the kernel has already written U = I, udiag = 1 (the reference's fall-back)
+        U = self._U_norm
+        st = self.owner._status
+        if st is None:
+            st = torch.zeros(1, dtype=torch.int32, device=self.W.device)
         out = ops.gptq_solve_batched(self.W.view(1, R, C), U.view(1, C, C), scales, qzeros, int(self.group_size),
                                      int(self.bits), perm=perm32,
-                                     udiag=self._udiag.view(1, C) if sparse else None, sparse14=sparse)
+                                     udiag=self._udiag.view(1, C) if sparse else None, sparse14=sparse, status=st)
+        code = int(st.item())       # the one host read of quantize()
+        if code != 0:
+            raise RuntimeError("forge.gptq: " + ("a bounded device-side wait ran out (FORGE_ERR_TIMEOUT)" if code == 3
+                                                else f"a kernel reported status {code}") + "; the codes are not valid")
         if sparse:
             q, M = out
             return q.view(R, C), scales, qzeros, M.view((C + 31) // 32, R).view(torch.uint32)
@@ -181,10 +206,12 @@ class GPTQ(object):
         U = U.view(C, C)
         self._udiag = udiag.view(C)
         self._U_norm = U
-        if int(info.item()) > 0:
-            self.issue_non_invertible = True
-        if self.algorithm == "sparsegptq" and not self.issue_non_invertible:
-            return U * self._udiag[:, None]  # the reference returns the un-normalised factor here (:165-170)
+        self._info = info
+        self._issue_override = None
+        if self.algorithm == "sparsegptq":
+            # the reference returns the un-normalised factor here (:165-170); after a failed factorisation the kernel
+            # left U = I and udiag = 1, so this is the identity then, like the reference's fall-back
+            return U * self._udiag[:, None]
         return U
 
     # ------------------------------------------------------------------ grid (forge/gptq.py:181-227)

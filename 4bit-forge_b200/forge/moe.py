@@ -8,8 +8,10 @@ over the experts a rank owns:
   --owner_gptq_handles mode) -> expert forward for the down-projection input -> its Hessian ->
   scan / permutation / damping -> batched Cholesky -> scale grid -> fused column solver -> packing.
 
-Everything stays on the device; the host reads back the per-expert token offsets once (to slice the
-expert forward) and one flag (whether gate and up have the same all-zero columns).
+Everything stays on the device and nothing is read back while the step is being queued: routing lists, the
+expert forward and the factorisation take their sizes from device-side offsets.  The host reads ONE small tensor
+when all launches are queued (the status word of the bounded waits and bounds checks, and whether gate and up
+turned out to have different all-zero columns, in which case the layer is redone with separate factors).
 """
 from __future__ import annotations
 
@@ -37,38 +39,25 @@ class MoEQuantConfig:
     expert_chunk: int = 0                  # experts factorised/solved per pass (0 = all at once)
     inversion_free: bool = True            # solve from the Cholesky factor itself, without the triangular inverse
     overlap_streams: bool = True           # scale search on a second stream beside the (latency-bound) factorisation
+    merge_gate_up: Optional[bool] = None   # gate and up in one solver launch (None: when the last wave would be thin)
+    keep_codes: bool = True                # keep the unpacked uint8 codes in the result (tests, write-back)
 
 
-def swiglu_expert_forward(X, token_lists, offsets_host, Wg, Wu):
-    """Down-projection calibration input of every expert, packed by expert: bf16(silu(x Wg^T) * (x Wu^T)).
-    Library bf16 GEMMs (fp32 accumulate), exactly what the HF MoE block computes before down_proj.
-    The routed rows are gathered once for all experts and the activation runs once over the packed buffer,
-    so an expert costs two GEMM launches and nothing else."""
-    total = int(offsets_host[-1])
-    I = Wg.shape[1]
-    if total == 0:
-        return torch.empty((1, I), dtype=torch.bfloat16, device=X.device)
-    Xg = X.index_select(0, token_lists[:total].long())
-    gate = torch.empty((total, I), dtype=torch.bfloat16, device=X.device)
-    up = torch.empty((total, I), dtype=torch.bfloat16, device=X.device)
-    for e in range(Wg.shape[0]):
-        a, b = int(offsets_host[e]), int(offsets_host[e + 1])
-        if b == a:
-            continue
-        torch.mm(Xg[a:b], Wg[e].T, out=gate[a:b])
-        torch.mm(Xg[a:b], Wu[e].T, out=up[a:b])
-    del Xg
-    return torch.nn.functional.silu(gate, inplace=True).mul_(up)
+def swiglu_expert_forward(X, token_lists, offsets, Wg, Wu, out_rows, status=None):
+    """Down-projection calibration input of every expert, packed by expert: bf16(silu(x Wg^T) * (x Wu^T)) with
+    the bf16 roundings of the HF MoE block forward — one grouped tcgen05 launch (forge_expert_swiglu_grouped);
+    `offsets` stays on the device, `out_rows` is the capacity of the packed output."""
+    return ops.expert_swiglu_grouped(X, token_lists, offsets, Wg, Wu, out_rows, status=status)
 
 
 class MoELayerQuantizer:
-    """Quantise the experts [e_begin, e_begin + n_local) of one MoE layer on the current CUDA device."""
+    """Quantise the experts [e_begin, e_begin + n_local) of one MoE layer on the device that holds X."""
 
     def __init__(self, cfg: MoEQuantConfig):
         self.cfg = cfg
-        self.inversion_free = False
         self._status = None
-        self._side = None          # second compute stream (scale search), created on first use
+        self._mismatch = None      # device flag: gate and up of some expert have different all-zero columns
+        self._side = None          # second compute stream (factorisation), created on first use
         self._h2d = None           # copy streams of quantize_experts_host
         self._d2h = None
         self._host_out = {}
@@ -78,30 +67,48 @@ class MoELayerQuantizer:
             self._side = torch.cuda.Stream(priority=-1)
         return self._side
 
-    # ---- one family of matrices sharing per-slot Hessians -------------------------------------
-    def _factor(self, H, perm32, pruned, invalid, Ws, wz):
-        """H [nu,C,C] (consumed: overwritten by U).  Ws: list of weight batches [nu,R,C] that share H; wz: their
-        all-zero-column masks.  Returns one (U, udiag, info) per weight batch."""
+    def _form(self, Ws) -> int:
+        """1 = inversion-free solve (dense GPTQ, 16-byte rows in the solver's work layout), 0 = the reference's.
+        The 1:4 mask choice of SparseGPT is a near-tie argmax and reacts to the different rounding of form 1, so
+        the sparse path keeps the reference's form."""
         cfg = self.cfg
-        shared = all(torch.equal(wz[0], w) for w in wz[1:])      # the one host read of this step
+        ok = (bool(cfg.inversion_free) and cfg.algorithm != "sparsegptq"
+              and all(W.shape[1] % 4 == 0 and W.shape[2] % 4 == 0 for W in Ws))
+        return 1 if ok else 0
+
+    # ---- one family of matrices sharing per-slot Hessians -------------------------------------
+    def _factor(self, H, perm32, pruned, invalid, Ws, wz, form, separate):
+        """H [nu,C,C] (consumed: overwritten by U).  Ws: list of weight batches [nu,R,C] that share H; wz: their
+        all-zero-column masks.  Returns one (U, udiag, info) per weight batch.
+
+        The factor depends on which weight columns are all zero (forge/gptq.py:145-149).  Gate and up normally
+        agree on that (dead input channels are zeroed in both), so ONE factor serves both and a device-side flag
+        records whether some expert disagreed; quantize_experts reads the flag once, when everything is queued,
+        and redoes the layer with `separate` factors in that rare case."""
+        cfg = self.cfg
         outs = []
-        groups = [wz[0]] if shared else wz
+        if not separate and len(wz) > 1:
+            differ = torch.zeros((), dtype=torch.bool, device=H.device)
+            for w in wz[1:]:
+                differ = differ | (wz[0] != w).any()
+            self._mismatch = differ if self._mismatch is None else (self._mismatch | differ)
+        groups = wz if separate else [wz[0]]
         for gi, wzero in enumerate(groups):
             last = gi == len(groups) - 1
             A, _, _ = ops.hessian_gather_damp(H, perm32, pruned, wzero, invalid, cfg.rel_damp)
-            if self.inversion_free:
-                # factor only: the solver works from the scaled reverse-Cholesky factor (form = 1)
+            if form == 1:
+                # factor only: the solver works from the scaled reverse-Cholesky factor
                 U, udiag, info = ops.chol_factor(A)
             else:
                 # the last group may overwrite H with U; earlier groups need H intact
                 U, udiag, info = ops.chol_inv_upper(A, U=H if last else None, zero_lower=False)
                 del A
             outs.append((U, udiag, info))
-        if shared:
+        if not separate:
             outs = outs * len(Ws)
         return outs
 
-    def _solve_family(self, H, n_samples, Ws, names=(), gates=None, between=None):
+    def _solve_family(self, H, n_samples, Ws, names=(), gates=None, between=None, separate=False):
         """Everything after the Hessian for the weight batches Ws that share it.  names[i]: input name to wait for
         (gates.need) before Ws[i] is touched.  between(): extra work for the main stream while the factorisation
         runs beside it (the expert forward)."""
@@ -110,11 +117,7 @@ class MoELayerQuantizer:
         cand = None
         if cfg.quantization_scale == "mse":
             cand = torch.linspace(1.0, cfg.mse_max_shrink, cfg.mse_grid, dtype=torch.float32, device=H.device)
-        # the inversion-free form needs 16-byte rows in the solver's work layout
-        # (dense GPTQ only: the 1:4 mask choice of SparseGPT is a near-tie argmax and reacts to the different
-        # rounding of that form, so the sparse path keeps the reference's form)
-        self.inversion_free = (bool(cfg.inversion_free) and not sparse
-                               and all(W.shape[1] % 4 == 0 and W.shape[2] % 4 == 0 for W in Ws))
+        form = self._form(Ws)
         nu, C, _ = H.shape
         diag, pruned, invalid = ops.hessian_scan(H, n_samples)
         if cfg.quantization_order == "activation":
@@ -140,19 +143,15 @@ class MoELayerQuantizer:
             if gates is not None and i < len(Ws) - 1:
                 grids.append(grid_of(W))      # overlaps the arrival of the next weight batch
         if fork:
-            # host order matters: the main stream's work is queued BEFORE the one host read of the factorisation
-            # (are the zero-column masks equal?), so the GPU never waits for the host, and the factorisation's
-            # launches are queued right after that read, at high priority
             side = self._side_stream()
             side.wait_stream(main)
             with torch.cuda.stream(side):
                 wz = [ops.weight_zero_cols(W) for W in Ws]
+                factors = self._factor(H, perm32, pruned, invalid, Ws, wz, form, separate)
             for W in Ws[len(grids):]:
                 grids.append(grid_of(W))
             if between is not None:
                 between()
-            with torch.cuda.stream(side):
-                factors = self._factor(H, perm32, pruned, invalid, Ws, wz)
             for t in [H, pruned, invalid] + ([perm32] if perm32 is not None else []) + list(Ws):
                 t.record_stream(side)
             main.wait_stream(side)
@@ -161,13 +160,13 @@ class MoELayerQuantizer:
                     t.record_stream(main)
         else:
             wz = [ops.weight_zero_cols(W) for W in Ws]
-            factors = self._factor(H, perm32, pruned, invalid, Ws, wz)
+            factors = self._factor(H, perm32, pruned, invalid, Ws, wz, form, separate)
             for W in Ws[len(grids):]:
                 grids.append(grid_of(W))
             if between is not None:
                 between()
         results = []
-        merged = self._solve_merged(Ws, factors, grids, perm32) if len(Ws) == 2 and not sparse else None
+        merged = self._solve_merged(Ws, factors, grids, perm32, form) if len(Ws) == 2 and not sparse else None
         for i, (W, (U, udiag, info), (scales, qzeros)) in enumerate(zip(Ws, factors, grids)):
             nb, R, C = W.shape
             if merged is not None:
@@ -175,7 +174,7 @@ class MoELayerQuantizer:
             else:
                 out = ops.gptq_solve_batched(W, U, scales, qzeros, cfg.group_size, cfg.bits, perm=perm32,
                                              udiag=udiag if sparse else None, sparse14=sparse, status=self._status,
-                                             form=1 if self.inversion_free else 0)
+                                             form=form)
             q, M = out if sparse else (out, None)
             G = (C + cfg.group_size - 1) // cfg.group_size
             res = {"qweight": q, "scales": scales.view(nb, R, G), "qzeros": qzeros.view(nb, R, G), "info": info,
@@ -184,13 +183,21 @@ class MoELayerQuantizer:
                 res["M"] = M
             if cfg.pack:
                 res.update(self._pack(q, res["scales"], res["qzeros"], M))
+                if not cfg.keep_codes:
+                    res["qweight"] = None
             results.append(res)
         return results
 
-    def _solve_merged(self, Ws, factors, grids, perm32):
-        """Two weight batches that share one factor (gate and up) in ONE solver launch, when that fills the GPU
-        better: the solver runs one CTA per 128 weight rows, three CTAs per SM, all of equal length, so a launch
-        whose last wave is nearly empty wastes most of a wave; together the two batches waste it once, not twice.
+    @staticmethod
+    def merge_pays(nb: int, R: int, sm_count: int) -> bool:
+        """The solver runs one CTA per 128 weight rows, three CTAs per SM, all of equal length; a launch whose last
+        wave is nearly empty wastes most of a wave, and gate and up together waste it once instead of twice."""
+        waves = nb * ((R + 127) // 128) / (3.0 * sm_count)
+        return 0.0 < waves - int(waves) < 0.35
+
+    def _solve_merged(self, Ws, factors, grids, perm32, form):
+        """Two weight batches that share one factor (gate and up) in ONE solver launch.  Same arithmetic per
+        matrix, so the codes are identical to two launches; only the launch shape differs.
         Returns the codes [2 nb, R, C] or None (not worth it / not applicable)."""
         cfg = self.cfg
         (U0, _, _), (U1, _, _) = factors
@@ -198,16 +205,17 @@ class MoELayerQuantizer:
         if U0 is not U1 or W0.shape != W1.shape:
             return None
         nb, R, C = W0.shape
-        slots = 3 * torch.cuda.get_device_properties(W0.device).multi_processor_count
-        waves = nb * ((R + 127) // 128) / slots
-        if not (0.0 < waves - int(waves) < 0.35):
+        want = cfg.merge_gate_up
+        if want is None:
+            want = self.merge_pays(nb, R, torch.cuda.get_device_properties(W0.device).multi_processor_count)
+        if not want:
             return None
         W = torch.cat([W0, W1], 0)
         scales = torch.cat([grids[0][0], grids[1][0]])
         qzeros = torch.cat([grids[0][1], grids[1][1]])
         u_map = torch.arange(nb, dtype=torch.int32, device=W.device).repeat(2)
         return ops.gptq_solve_batched(W, U0, scales, qzeros, cfg.group_size, cfg.bits, perm=perm32, u_map=u_map,
-                                      status=self._status, form=1 if self.inversion_free else 0)
+                                      status=self._status, form=form)
 
     def _pack(self, q, scales, qzeros, M):
         cfg = self.cfg
@@ -227,75 +235,144 @@ class MoELayerQuantizer:
     # ---- the layer ----------------------------------------------------------------------------------
     @torch.no_grad()
     def quantize_experts(self, X: torch.Tensor, topk_ids: Optional[torch.Tensor], Wg: torch.Tensor,
-                         Wu: torch.Tensor, Wd: torch.Tensor, e_begin: int = 0, dense_tail: int = 0, _gates=None):
+                         Wu: torch.Tensor, Wd: torch.Tensor, e_begin: int = 0, dense_tail: int = 0, _gates=None,
+                         check: bool = True, x_chunks=None):
         """X [T,Hd] bf16; topk_ids [T,k] int32 (global expert ids); Wg/Wu [n,I,Hd], Wd [n,Hd,I] hold the experts
         this rank owns: first the routed experts e_begin.., then `dense_tail` experts that see every token
         (shared experts).  The weight tensors are updated in place only where a dead input channel forces a
-        column to zero.  Returns {"gate": .., "up": .., "down": .., "counts": ..} with per-matrix results.
+        column to zero.  Returns {"gate": .., "up": .., "down": .., "counts": .., "status": ..} with per-matrix
+        results.  With check=True (default) the call ends with one host read of the status word and raises
+        RuntimeError if a bounded wait ran out or a bounds check failed; check=False leaves that read to the
+        caller (out["status"], out["mismatch"]).
+
+        x_chunks (expert-parallel runs): [(row_end, wait)] as returned by forge.dist.broadcast_inputs(chunks > 1) —
+        the rows of X arrive chunk by chunk; wait() makes the current stream wait for a chunk.  The layer-input
+        Hessians are then accumulated chunk by chunk in the running-mean form of GPTQ.update (forge/gptq.py:62-80:
+        H <- n_prev/N H + 2/N X_c^T X_c), so the Hessian of chunk i runs while chunk i+1 is still in flight.
 
         `_gates` (internal, see quantize_experts_host): object whose need(name) makes the current stream wait until
-        the named input ("gate", "up", "down") has arrived, and whose done(name, results) is told when a family's
-        results exist."""
+        the named input ("gate", "up", "down") has arrived, and whose done(results, c0, n) is told when the results
+        of the experts [c0, c0 + chunk) of a family exist."""
+        with torch.cuda.device(X.device):
+            out = self._quantize_experts(X, topk_ids, Wg, Wu, Wd, e_begin, dense_tail, _gates, separate=False,
+                                         x_chunks=x_chunks)
+            if check and _gates is None:
+                out = self._finish(out, lambda: self._quantize_experts(X, topk_ids, Wg, Wu, Wd, e_begin, dense_tail,
+                                                                        None, separate=True))
+        return out
+
+    def _finish(self, out, redo):
+        """The one host read of a step: status word + gate/up zero-column disagreement."""
+        flags = torch.stack([out["status"].view(()).to(torch.int32),
+                             out["mismatch"].view(()).to(torch.int32)]).cpu()
+        status, mismatch = int(flags[0]), int(flags[1])
+        if status != 0:
+            what = {1: "a bounds check failed (FORGE_ERR_INVALID)", 3: "a bounded device-side wait ran out "
+                    "(FORGE_ERR_TIMEOUT)"}.get(status, f"status {status}")
+            raise RuntimeError(f"forge.moe: {what}; the results of this step are not valid")
+        if mismatch:
+            out = redo()
+            status = int(out["status"].item())
+            if status != 0:
+                raise RuntimeError(f"forge.moe: status {status} in the separate-factor pass")
+        return out
+
+    def _chunked_input_hessians(self, X, topk_ids, e_begin, n_routed, dense_tail, x_chunks, status):
+        """Layer-input Hessians of all local slots, accumulated over the row chunks of X as they arrive."""
+        T, Hd = X.shape
+        n_local = n_routed + dense_tail
+        H1 = torch.empty((n_local, Hd, Hd), dtype=torch.float32, device=X.device)
+        n_prev = torch.zeros(n_local, dtype=torch.int64, device=X.device)
+        t0 = 0
+        for t1, wait in x_chunks:
+            wait()
+            if t1 > t0:
+                ids_c = topk_ids[t0:t1] if n_routed > 0 else None
+                _, offs_c, lists_c = ops.route_build_lists(ids_c, e_begin, n_routed, dense_tail, n_tokens=t1 - t0)
+                ops.hessian_grouped(X[t0:t1], Hd, lists_c, offs_c, H1, n_prev=n_prev, mirror=True, status=status)
+                ops.counts_add(n_prev, offs_c)
+            t0 = t1
+        return H1
+
+    def _quantize_experts(self, X, topk_ids, Wg, Wu, Wd, e_begin, dense_tail, _gates, separate, x_chunks=None):
         cfg = self.cfg
         n_local = Wg.shape[0]
         n_routed = n_local - dense_tail
         T, Hd = X.shape
         I = Wg.shape[1]
         dev = X.device
-        # ---- routing lists for the local experts
-        parts_counts, parts_lists = [], []
-        if n_routed > 0:
-            counts, offsets, lists = ops.route_build_lists(topk_ids, e_begin, n_routed)
-            parts_counts.append(counts.to(torch.int64))
-        else:
-            lists = torch.empty(0, dtype=torch.int32, device=dev)
-        if dense_tail > 0:
-            parts_counts.append(torch.full((dense_tail,), T, dtype=torch.int64, device=dev))
-        counts64 = torch.cat(parts_counts)
-        offsets = torch.zeros(n_local + 1, dtype=torch.int64, device=dev)
-        offsets[1:] = torch.cumsum(counts64, 0)
-        offsets_host = offsets.cpu()
-        n_routed_tok = int(offsets_host[n_routed])
-        if dense_tail > 0:
-            ar = torch.arange(T, dtype=torch.int32, device=dev)
-            lists = torch.cat([lists[:n_routed_tok]] + [ar] * dense_tail)
-        lists = lists.contiguous()
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        H1_all = None
+        if x_chunks:
+            if cfg.expert_chunk and cfg.expert_chunk < n_local:
+                for _, wait in x_chunks:     # expert chunking and row chunking do not combine: take X whole
+                    wait()
+            else:
+                H1_all = self._chunked_input_hessians(X, topk_ids, e_begin, n_routed, dense_tail, x_chunks, status)
+        # ---- routing lists for the local slots: routed experts, then the dense tail (every token)
+        counts, offsets, lists = ops.route_build_lists(topk_ids if n_routed > 0 else None, e_begin, n_routed,
+                                                       dense_tail, n_tokens=T)
+        counts64 = counts.to(torch.int64)
+        k = topk_ids.shape[1] if (topk_ids is not None and n_routed > 0) else 0
+        act_rows = T * k + dense_tail * T      # capacity of the packed activations; the true size stays on the device
 
         chunk = cfg.expert_chunk if cfg.expert_chunk > 0 else n_local
         res = {"gate": [], "up": [], "down": []}
-        status = torch.zeros(1, dtype=torch.int32, device=dev)
         self._status = status
+        self._mismatch = None
         act = None
         for c0 in range(0, n_local, chunk):
             c1 = min(n_local, c0 + chunk)
             nb = c1 - c0
-            offs = offsets[c0:c1 + 1].contiguous()
-            n_samples = counts64[c0:c1].contiguous()
+            offs = offsets[c0:c1 + 1]
+            n_samples = counts64[c0:c1]
             # the layer-input Hessians need no weights: they run while the weights may still be on their way
-            H1 = torch.empty((nb, Hd, Hd), dtype=torch.float32, device=dev)
-            ops.hessian_grouped(X, Hd, lists, offs, H1, mirror=True, status=status)
+            if H1_all is not None:
+                H1, H1_all = H1_all, None
+            else:
+                H1 = torch.empty((nb, Hd, Hd), dtype=torch.float32, device=dev)
+                ops.hessian_grouped(X, Hd, lists, offs, H1, mirror=True, status=status)
+
             def forward():
                 # down-projection inputs of all local experts (packed by expert); zeroing dead input channels in the
                 # weights before does not change them (those channels are zero in every routed row)
                 nonlocal act
                 if act is None:
-                    act = swiglu_expert_forward(X, lists, offsets_host, Wg, Wu)
+                    act = swiglu_expert_forward(X, lists, offsets, Wg, Wu, act_rows, status=status)
 
-            g, u = self._solve_family(H1, n_samples, [Wg[c0:c1], Wu[c0:c1]], ("gate", "up"), _gates, forward)
+            g, u = self._solve_family(H1, n_samples, [Wg[c0:c1], Wu[c0:c1]], ("gate", "up"), _gates, forward, separate)
             del H1
             if _gates is not None:
-                _gates.done("gate_up", (g, u))
+                _gates.done({"gate": g, "up": u}, c0, n_local)
             H2 = torch.empty((nb, I, I), dtype=torch.float32, device=dev)
             ops.hessian_grouped(act, I, None, offs, H2, mirror=True, status=status)
             (d,) = self._solve_family(H2, n_samples, [Wd[c0:c1]], ("down",), _gates)
             del H2
+            if _gates is not None:
+                _gates.done({"down": d}, c0, n_local)
             res["gate"].append(g)
             res["up"].append(u)
             res["down"].append(d)
-        out = {k: _cat_results(v) for k, v in res.items()}
+        out = {k_: _cat_results(v) for k_, v in res.items()}
         out["counts"] = counts64
         out["status"] = status
+        out["mismatch"] = self._mismatch if self._mismatch is not None else torch.zeros((), dtype=torch.bool, device=dev)
+        out["routing"] = {"lists": lists, "offsets": offsets, "act": act}
         return out
+
+    @torch.no_grad()
+    def reconstruction_loss(self, out, X, Wg, Wu, Wd):
+        """|| X W^T - X What^T ||_F^2 of every matrix of a quantize_experts result, on the device
+        (forge_recon_loss): {"gate": f64 [n], "up": f64 [n], "down": f64 [n]}.  Wg/Wu/Wd are the weights as
+        quantize_experts left them; the down projection is evaluated on the activations the step produced."""
+        gs = self.cfg.group_size
+        r = out["routing"]
+        losses = {}
+        for name, W, Xin, lst in (("gate", Wg, X, r["lists"]), ("up", Wu, X, r["lists"]), ("down", Wd, r["act"], None)):
+            o = out[name]
+            losses[name] = ops.recon_loss(W, o["qweight"], o["scales"].contiguous(), o["qzeros"].contiguous(), gs, Xin,
+                                          lst, r["offsets"], status=out["status"])
+        return losses
 
     # ---- the same layer from host memory ---------------------------------------------------------------
     _HOST_KEYS = {"gptq": ("weight_packed", "weight_scale", "qzeros"), "sparsegptq": ("wpair",)}
@@ -308,17 +385,31 @@ class MoELayerQuantizer:
         X / topk_ids may be host or device tensors.  Copies run on their own streams and overlap the kernels:
         the layer-input Hessians start as soon as X has arrived, while gate / up are still being uploaded; down is
         uploaded during the gate / up solve; the packed gate / up results travel back during the down solve.
-        Requires expert_chunk == 0 (one pass).  Returns (out, host) where `host` maps "gate.weight_packed" etc. to
-        pinned host tensors, valid after the call returns (it synchronises the copy streams); with
-        ship_results=False nothing is copied back (the caller gathers on the device) and `host` is empty.
+        Returns (out, host) where `host` maps "gate.weight_packed" etc. to
+        pinned host tensors.  They are complete when the call returns (it synchronises the copy streams and checks
+        the status word: RuntimeError if a bounded wait ran out or a bounds check failed) and they are the
+        quantizer's own cached buffers: the NEXT call on this quantizer with the same shapes overwrites them, so a
+        caller that keeps a layer's results while the next layer runs (an asynchronous checkpoint writer) must copy
+        them or use a second quantizer.  With ship_results=False nothing is copied back (the caller gathers on the
+        device) and `host` is empty.
 
         fp8 checkpoints (DeepSeek-V3): pass the e4m3 weights [n,R,C] and fp8_scale_inv = (sg, su, sd), host fp32
         block scales [n, R/128, C/128]; half the bytes cross PCIe and the bf16 weights are materialised on the
         device (forge/utils/io.py:533-563 of the reference does this on the CPU).  R must be a multiple of 128."""
         cfg = self.cfg
-        if cfg.expert_chunk:
-            raise ValueError("quantize_experts_host runs the layer in one pass: set expert_chunk = 0")
         dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        if dev.index is None:
+            dev = torch.device("cuda", torch.cuda.current_device())
+        for t in (X, topk_ids):
+            if t.is_cuda and t.device != dev:
+                raise ValueError(f"quantize_experts_host: input on {t.device}, but the layer runs on {dev}")
+        with torch.cuda.device(dev):
+            return self._quantize_experts_host(X, topk_ids, Wg_host, Wu_host, Wd_host, e_begin, dense_tail, dev,
+                                               ship_results, fp8_scale_inv)
+
+    def _quantize_experts_host(self, X, topk_ids, Wg_host, Wu_host, Wd_host, e_begin, dense_tail, dev, ship_results,
+                               fp8_scale_inv):
+        cfg = self.cfg
         main = torch.cuda.current_stream()
         if self._h2d is None:
             self._h2d, self._d2h = torch.cuda.Stream(), torch.cuda.Stream()
@@ -369,8 +460,9 @@ class MoELayerQuantizer:
                     ops.fp8_block_dequant(raw[j].view(n * R, C), sinv[j].view(-1, sinv[j].shape[-1]),
                                           out=(Wg, Wu, Wd)[j].view(n * R, C))
 
-        def ship(prefix, r):
-            # device -> pinned host on the return stream, after the kernels that produced r
+        def ship(prefix, r, c0=0, n_total=None):
+            # device -> pinned host on the return stream, after the kernels that produced r; r holds the experts
+            # [c0, c0 + len) of n_total, the pinned buffers hold all of them
             if not ship_results:
                 return
             d2h.wait_stream(main)
@@ -386,27 +478,41 @@ class MoELayerQuantizer:
                         name = f"{prefix}.weight_zero_point"
                     else:
                         name = f"{prefix}.{k}"
+                    full = (n_total if n_total is not None else v.shape[0],) + tuple(v.shape[1:])
                     buf = me._host_out.get(name)
-                    if buf is None or buf.shape != v.shape or buf.dtype != v.dtype:
-                        buf = torch.empty(v.shape, dtype=v.dtype).pin_memory()
+                    if buf is None or tuple(buf.shape) != full or buf.dtype != v.dtype:
+                        buf = torch.empty(full, dtype=v.dtype).pin_memory()
                         me._host_out[name] = buf
-                    buf.copy_(v, non_blocking=True)
+                    buf[c0:c0 + v.shape[0]].copy_(v, non_blocking=True)
                     v.record_stream(d2h)
                     host[name] = buf
 
+        arrived = set()
+
         class Gates:
             def need(self, name):
+                if name in arrived:
+                    return
+                arrived.add(name)
                 torch.cuda.current_stream().wait_event(events[name])
                 materialise((("gate", "up", "down").index(name),))
 
-            def done(self, name, results):
-                g, u = results
-                ship("gate", g)
-                ship("up", u)
+            def done(self, results, c0, n_total):
+                for nm, r in results.items():
+                    ship(nm, r, c0, n_total)
 
         main.wait_event(events["x"])
-        out = self.quantize_experts(Xd, idd, Wg, Wu, Wd, e_begin=e_begin, dense_tail=dense_tail, _gates=Gates())
-        ship("down", out["down"])
+        out = self._quantize_experts(Xd, idd, Wg, Wu, Wd, e_begin, dense_tail, Gates(), separate=False)
+
+        def redo():
+            # gate and up disagree on their all-zero columns: same layer again with one factor per matrix
+            # (every input is on the device by now; nothing overlaps in this rare pass)
+            o = self._quantize_experts(Xd, idd, Wg, Wu, Wd, e_begin, dense_tail, None, separate=True)
+            for nm in ("gate", "up", "down"):
+                ship(nm, o[nm])
+            return o
+
+        out = self._finish(out, redo)
         d2h.synchronize()
         return out, host
 

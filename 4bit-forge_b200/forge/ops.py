@@ -55,17 +55,64 @@ def mxfp4_dequant(blocks_u8: torch.Tensor, scales_u8: torch.Tensor, dtype=torch.
     return out.view(*lead, NB * 32, rows)
 
 
-def route_build_lists(topk_ids: torch.Tensor, e_begin: int, e_count: int):
-    """topk_ids [T,k] int32 -> (counts int32 [e_count], offsets int64 [e_count+1], token_lists int32 [T*k])."""
-    T, k = topk_ids.shape
-    ids = topk_ids.to(torch.int32).contiguous()
-    dev = _dev(ids)
-    counts = torch.empty(e_count, dtype=torch.int32, device=dev)
-    offsets = torch.empty(e_count + 1, dtype=torch.int64, device=dev)
-    lists = torch.empty(max(T * k, 1), dtype=torch.int32, device=dev)
-    call("forge_route_build_lists", ptr(ids), T, k, e_begin, e_count, ptr(counts), ptr(offsets), ptr(lists),
+def route_topk(logits: torch.Tensor, top_k: int, mode: str = "softmax", n_groups: int = 1, topk_groups: int = 1,
+               bias=None, want_weights: bool = False):
+    """Router logits [T,E] fp32 -> expert ids int32 [T,k] in descending score order (forge_route_topk).
+    mode: "softmax", "sigmoid" or "sigmoid_group" (DeepSeek-V3 group-limited selection)."""
+    T, E = logits.shape
+    lg = logits.to(torch.float32).contiguous()
+    dev = _dev(lg)
+    ids = torch.empty((T, top_k), dtype=torch.int32, device=dev)
+    w = torch.empty((T, top_k), dtype=torch.float32, device=dev) if want_weights else None
+    b = None if bias is None else bias.to(torch.float32).contiguous()
+    call("forge_route_topk", ptr(lg), ptr(b), T, E, int(top_k), _abi.ROUTE_MODES[mode], int(n_groups), int(topk_groups),
+         ptr(ids), ptr(w), stream_ptr())
+    return (ids, w) if want_weights else ids
+
+
+def route_build_lists(topk_ids, e_begin: int, e_count: int, dense_tail: int = 0, n_tokens: int = 0):
+    """topk_ids [T,k] int32 -> (counts int32 [n], offsets int64 [n+1], token_lists int32 [T*k + dense_tail*T]) for the
+    routed experts [e_begin, e_begin+e_count) followed by dense_tail slots that see every token; n = e_count +
+    dense_tail.  With e_count == 0 topk_ids may be None and n_tokens gives T."""
+    if topk_ids is not None:
+        T, k = topk_ids.shape
+        ids = topk_ids.to(torch.int32).contiguous()
+        dev = _dev(ids)
+    else:
+        T, k, ids = int(n_tokens), 1, None
+        dev = torch.device("cuda", torch.cuda.current_device())
+    n = e_count + dense_tail
+    counts = torch.empty(n, dtype=torch.int32, device=dev)
+    offsets = torch.empty(n + 1, dtype=torch.int64, device=dev)
+    lists = torch.empty(max((T * k if e_count else 0) + dense_tail * T, 1), dtype=torch.int32, device=dev)
+    call("forge_route_build_lists", ptr(ids), T, k, e_begin, e_count, dense_tail, ptr(counts), ptr(offsets), ptr(lists),
          stream_ptr())
     return counts, offsets, lists
+
+
+def expert_swiglu_grouped(X, token_idx, offsets, Wg, Wu, out_rows: int, out=None, simt: bool = False, status=None):
+    """Down-projection calibration input of every slot, packed by slot: bf16(silu(x Wg^T) * (x Wu^T)) with the
+    block forward's bf16 roundings (forge_expert_swiglu_grouped).  X bf16 [T, ldx], Wg/Wu bf16 [nb, I, H]."""
+    assert X.dtype == torch.bfloat16 and Wg.dtype == torch.bfloat16 and Wu.dtype == torch.bfloat16
+    nb, I, H = Wg.shape
+    assert offsets.dtype == torch.int64 and offsets.numel() == nb + 1
+    if out is None:
+        out = torch.empty((max(out_rows, 1), I), dtype=torch.bfloat16, device=_dev(X))
+    list_len = 0 if token_idx is None else token_idx.numel()
+    call("forge_expert_swiglu_grouped", ptr(X), X.shape[0], X.stride(0), H, I, ptr(token_idx), list_len, ptr(offsets), nb,
+         ptr(Wg), ptr(Wu), ptr(out), out.shape[0], _abi.FWD_SIMT if simt else 0, ptr(status), stream_ptr())
+    return out
+
+
+def recon_loss(W, q, scales, qzeros, gs: int, X, token_idx, offsets, x_map=None, status=None):
+    """|| X_b W[b]^T - X_b What[b]^T ||_F^2 per matrix (forge_recon_loss) -> float64 [nb].  W [nb,R,C], q [nb,R,C] u8,
+    scales/qzeros [nb,R,G]; X bf16 rows listed per slot like hessian_grouped."""
+    nb, R, C = W.shape
+    loss = torch.empty(nb, dtype=torch.float64, device=_dev(W))
+    list_len = 0 if token_idx is None else token_idx.numel()
+    call("forge_recon_loss", ptr(W), dtype_code(W), ptr(q), ptr(scales), ptr(qzeros), int(gs), nb, R, C, ptr(X), X.shape[0],
+         X.stride(0), ptr(token_idx), list_len, ptr(offsets), ptr(x_map), ptr(loss), ptr(status), stream_ptr())
+    return loss
 
 
 def hessian_grouped(X: torch.Tensor, C: int, token_idx, offsets: torch.Tensor, H: torch.Tensor, n_prev=None,
@@ -78,8 +125,9 @@ def hessian_grouped(X: torch.Tensor, C: int, token_idx, offsets: torch.Tensor, H
     own_status = status is None
     if own_status:
         status = torch.zeros(1, dtype=torch.int32, device=_dev(X))
-    call("forge_hessian_grouped", ptr(X), X.stride(0), C, ptr(token_idx), ptr(offsets), nb, ptr(H), ptr(n_prev), flags,
-         ptr(status), stream_ptr())
+    list_len = 0 if token_idx is None else token_idx.numel()
+    call("forge_hessian_grouped", ptr(X), X.shape[0], X.stride(0), C, ptr(token_idx), list_len, ptr(offsets), nb, ptr(H),
+         ptr(n_prev), flags, ptr(status), stream_ptr())
     return status
 
 

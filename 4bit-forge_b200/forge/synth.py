@@ -58,11 +58,19 @@ def zipf_bias(n_experts, seed, s=1.1, device="cpu"):
     return torch.log(w / w.sum() * n_experts).to(device)
 
 
-def route(shape: LayerShape, T, seed, device="cpu"):
-    """Top-k expert ids [T,k] int32 for the layer's router type."""
+def router_logits(shape: LayerShape, T, seed, device="cpu"):
+    """Router logits [T,E] fp32: N(0,1) plus the Zipf(1.1) per-expert bias."""
     g = torch.Generator(device=device).manual_seed(seed + 17)
     E = shape.n_experts
-    logits = torch.randn(T, E, generator=g, device=device) + zipf_bias(E, seed + 18, device=device)
+    return torch.randn(T, E, generator=g, device=device) + zipf_bias(E, seed + 18, device=device)
+
+
+def route(shape: LayerShape, T, seed, device="cpu", logits=None):
+    """Top-k expert ids [T,k] int32 for the layer's router type, in torch (the statement the device kernel
+    forge_route_topk is checked against)."""
+    E = shape.n_experts
+    if logits is None:
+        logits = router_logits(shape, T, seed, device)
     if shape.router == "softmax":
         scores = torch.softmax(logits, dim=-1)
         ids = scores.topk(shape.top_k, dim=-1).indices

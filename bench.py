@@ -27,6 +27,11 @@ import torch  # noqa: E402
 METRIC = "experts_gptq_per_sec_per_moe_layer"
 UNIT = "experts/s"
 
+# DRAM bytes of forge_gptq_solve_batched per expert (gate + up + down launches), from ncu captures of small cuts of
+# the same matrix shapes (the full layers are too large to capture; traffic is per expert, so it scales with the
+# expert count).  The summaries and their commands are under profiles/.
+SOLVER_TRAFFIC_PER_EXPERT = {"qwen3_30b_a3b": 150.4e6}
+
 # quantisation recipe per benchmark configuration
 RECIPES = {
     "qwen3_30b_a3b": dict(symmetric=False, quantization_scale="mse", quantization_order="default", algorithm="gptq"),
@@ -41,11 +46,13 @@ def parse():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--config", default="qwen3_30b_a3b", choices=sorted(RECIPES))
+    ap.add_argument("--config", default="deepseek_v3", choices=sorted(RECIPES))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=0, help="override the calibration token count (smaller runs)")
     ap.add_argument("--experts", type=int, default=0, help="override the routed expert count (smaller runs)")
-    ap.add_argument("--expert-chunk", type=int, default=0)
+    ap.add_argument("--expert-chunk", type=int, default=0, help="experts per pass (0: chosen from the free memory)")
+    ap.add_argument("--bcast-chunks", type=int, default=2,
+                    help="row chunks of the X broadcast (N > 1): the Hessian of chunk i overlaps the transfer of chunk i+1")
     ap.add_argument("--placement", default="lpt", choices=["lpt", "contiguous"],
                     help="experts to ranks: by load (routed tokens, longest first) or contiguous index ranges")
     ap.add_argument("--no-e2e", action="store_true")
@@ -245,6 +252,18 @@ class PhaseTimer:
         return out
 
 
+def pick_expert_chunk(n_local, Hd, I, free_bytes, sparse):
+    """Experts factorised / solved per pass so that the per-pass working set fits the free memory: two fp32 [Hd,Hd]
+    matrices (Hessian and its factor copy; a third for the triangular inverse of the sparse path) plus the solver's
+    work buffers of the gate and up batches (fp32 transposed weights + codes)."""
+    per_expert = (3 if sparse else 2) * Hd * Hd * 4 + 2 * I * Hd * 5 + (1 << 20)
+    fit = max(1, int(0.55 * free_bytes // per_expert))
+    if fit >= n_local:
+        return 0
+    passes = -(-n_local // fit)
+    return -(-n_local // passes)
+
+
 def run_ours(args, rank, world, local_rank):
     import torch.distributed as dist
     from forge import _abi, synth, moe, ops, dist as fdist
@@ -253,23 +272,22 @@ def run_ours(args, rank, world, local_rank):
     _abi.load_library()
     shape = layer_shape(args)
     recipe = RECIPES[args.config]
-    cfg = moe.MoEQuantConfig(bits=4, group_size=128, rel_damp=0.01, expert_chunk=args.expert_chunk, **recipe)
-    qz = moe.MoELayerQuantizer(cfg)
     E = shape.n_experts
     e0, e1 = fdist.shard_experts(E, world, rank)
+    route_args = (shape.top_k, shape.router, shape.n_groups, shape.topk_groups)
 
-    # ---- inputs resident in HBM: X and routing on rank 0, each rank's own expert weights
+    # ---- inputs resident in HBM: X and the router logits on rank 0, each rank's own expert weights
     T, Hd, I = shape.tokens, shape.hidden, shape.inter
     if rank == 0:
         X = synth.student_t_activations(T, Hd, seed=11, device=dev)
-        ids = synth.route(shape, T, seed=11, device=dev)
+        logits = synth.router_logits(shape, T, seed=11, device=dev)
     else:
         X = torch.empty((T, Hd), dtype=torch.bfloat16, device=dev)
-        ids = torch.empty((T, shape.top_k), dtype=torch.int32, device=dev)
+        logits = torch.empty((T, E), dtype=torch.float32, device=dev)
     if world > 1:
-        dist.broadcast(ids, src=0)  # only to place the shared expert; the timed step broadcasts again
+        dist.broadcast(logits, src=0)  # only to decide the placement; the timed step broadcasts again
     # placement is decided from the routing statistics before the timed region (like the shared expert's owner)
-    ids_host = ids.cpu()
+    ids_host = ops.route_topk(logits, *route_args).cpu()
     remap = None
     if args.placement == "lpt" and world > 1:
         counts_all = torch.bincount(ids_host.reshape(-1).long(), minlength=E)
@@ -291,16 +309,25 @@ def run_ours(args, rank, world, local_rank):
         for r in range(world):
             b, e = fdist.shard_experts(E, world, r)
             n_local_of.append((e - b) + (shape.n_shared if r == owner else 0))
+    n_loc = len(my_ids)
     Wg, Wu, Wd = synth.expert_weights(shape, my_ids, seed=12, device=dev)
     fp8 = None
     if shape.fp8_weights:
-        fp8 = [[synth.fp8_block_encode(w) for w in Wm] for Wm in (Wg, Wu, Wd)]
+        # the checkpoint form: e4m3 weights [n,R,C] + fp32 block scales [n,R/128,C/128]; de-quantised inside the step
+        enc = [[synth.fp8_block_encode(w) for w in Wm] for Wm in (Wg, Wu, Wd)]
+        fp8 = [(torch.stack([q8 for q8, _ in e_]), torch.stack([sv for _, sv in e_]).float().contiguous()) for e_ in enc]
+        del enc
+    sparse = recipe["algorithm"] == "sparsegptq"
+    torch.cuda.empty_cache()
+    chunk = args.expert_chunk or pick_expert_chunk(n_loc, Hd, I, torch.cuda.mem_get_info()[0], sparse)
+    cfg = moe.MoEQuantConfig(bits=4, group_size=128, rel_damp=0.01, expert_chunk=chunk, keep_codes=False, **recipe)
+    qz = moe.MoELayerQuantizer(cfg)
 
     def shapes_of_rank(r):
         n = n_local_of[r]
         meta = {}
         for nm, (R, C) in (("gate", (I, Hd)), ("up", (I, Hd)), ("down", (Hd, I))):
-            if cfg.algorithm == "sparsegptq":
+            if sparse:
                 meta[f"{nm}.wpair"] = ((n, (C // 32 + 1) // 2, R, 2), torch.int64)
             else:
                 meta[f"{nm}.weight_packed"] = ((n, R, C // 8), torch.int32)
@@ -309,11 +336,13 @@ def run_ours(args, rank, world, local_rank):
                     meta[f"{nm}.weight_zero_point"] = ((n, R, C // 128), torch.uint8)
         return meta
 
+    plan = fdist.GatherPlan(shapes_of_rank, dev) if world > 1 else None   # buffers allocated once, outside the step
+
     def local_results(out):
         local = {}
         for nm in ("gate", "up", "down"):
             r = out[nm]
-            if cfg.algorithm == "sparsegptq":
+            if sparse:
                 local[f"{nm}.wpair"] = r["wpair"]
             else:
                 local[f"{nm}.weight_packed"] = r["weight_packed"]
@@ -322,60 +351,104 @@ def run_ours(args, rank, world, local_rank):
                     local[f"{nm}.weight_zero_point"] = r["qzeros"].to(torch.uint8)
         return local
 
-    def step(Xs, idss, Wgs, Wus, Wds, quantizer=None):
-        if world > 1:
-            fdist.broadcast_inputs(Xs, idss, src=0)
-        if fp8 is not None:
-            for Wm, enc in zip((Wgs, Wus, Wds), fp8):
-                for i, (q8, sinv) in enumerate(enc):
-                    Wm[i].copy_(ops.fp8_block_dequant(q8, sinv))
+    def route_local(lg):
+        ids = ops.route_topk(lg, *route_args)
         if remap is not None:
-            idss = remap[idss.long()].to(torch.int32)      # renumber: this rank's experts become one contiguous range
-        out = (quantizer or qz).quantize_experts(Xs, idss, Wgs, Wus, Wds, e_begin=e0, dense_tail=n_tail)
-        local = local_results(out)
-        gathered = fdist.gather_to_rank0(local, shapes_of_rank) if world > 1 else {k: [v] for k, v in local.items()}
+            ids = remap[ids.long()].to(torch.int32)      # renumber: this rank's experts become one contiguous range
+        return ids
+
+    def dequant_weights():
+        if fp8 is not None:
+            for Wm, (q8, sinv) in zip((Wg, Wu, Wd), fp8):
+                n, R, C = q8.shape
+                ops.fp8_block_dequant(q8.view(n * R, C), sinv.view(-1, sinv.shape[-1]), out=Wm.view(n * R, C))
+
+    def step(quantizer=None):
+        """One layer: broadcast -> route -> (fp8 -> bf16) -> Hessians / factor / search / solve / pack -> gather."""
+        x_chunks = None
+        if world > 1:
+            dist.broadcast(logits, src=0)
+            ids = route_local(logits)
+            x_chunks = _bcast_x()
+        else:
+            ids = route_local(logits)
+        dequant_weights()
+        ok, out, err = True, None, None
+        try:
+            out = (quantizer or qz).quantize_experts(X, ids, Wg, Wu, Wd, e_begin=e0, dense_tail=n_tail,
+                                                     x_chunks=x_chunks)
+        except RuntimeError as exc:     # a rank that failed says so before the gather; nobody waits for it
+            ok, err = False, exc
+        if world > 1:
+            fdist.agree_ok(ok, "solve")
+        elif not ok:
+            raise err
+        gathered = plan.run(local_results(out)) if world > 1 else None
         return out, gathered
+
+    def _bcast_x():
+        ready = []
+        t0 = 0
+        for i in range(args.bcast_chunks):
+            t1 = T * (i + 1) // args.bcast_chunks
+            if t1 > t0:
+                ready.append((t1, dist.broadcast(X[t0:t1], src=0, async_op=True).wait))
+            t0 = t1
+        return ready
 
     def barrier():
         if world > 1:
             dist.barrier()
 
-    def max_over_ranks(ms):
+    def max_over_ranks(vals):
         if world > 1:
-            t = torch.tensor([ms], dtype=torch.float64, device=dev)
+            t = torch.tensor(vals, dtype=torch.float64, device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            return float(t.item())
-        return ms
+            return [float(v) for v in t.tolist()]
+        return list(vals)
 
     def timed(fn, steps):
+        """Total device time of `steps` calls (barrier + synchronize on both sides, max over ranks) and the per-step
+        device times (events between the steps, max over ranks per step)."""
         barrier()
         torch.cuda.synchronize()
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        ev0.record()
-        for _ in range(steps):
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        evs[0].record()
+        for i in range(steps):
             fn()
-        ev1.record()
+            evs[i + 1].record()
         torch.cuda.synchronize()
         barrier()
-        return max_over_ranks(ev0.elapsed_time(ev1))
+        total = max_over_ranks([evs[0].elapsed_time(evs[-1])])[0]
+        per_step = max_over_ranks([evs[i].elapsed_time(evs[i + 1]) for i in range(steps)])
+        return total, per_step
 
     # ---- device-resident timing
-    out, _ = step(X, ids, Wg, Wu, Wd)   # always at least one untimed pass: it also checks the status word
-    for _ in range(max(args.warmup - 1, 0)):
-        out, _ = step(X, ids, Wg, Wu, Wd)
+    for _ in range(max(args.warmup, 1)):
+        out, _ = step()     # every step checks the status word (quantize_experts raises on a non-zero status)
     torch.cuda.synchronize()
-    status = int(out["status"].item())
-    if status != 0:
-        raise RuntimeError(f"a tensor-core kernel reported status {status} (bounded wait ran out)")
     clocks = ClockSampler(local_rank)
     if rank == 0:
         clocks.start()
     n0 = _abi.query("forge_launch_count")
-    ms = timed(lambda: step(X, ids, Wg, Wu, Wd), args.steps)
+    ms, per_step = timed(step, args.steps)
     launches = _abi.query("forge_launch_count") - n0
     clk = clocks.stop() if rank == 0 else None
     n_total = E + shape.n_shared
     value = n_total * args.steps / (ms / 1e3)
+
+    # ---- per-entry-point device time of one more step (rank 0's slice) and the roofline of the top kernel
+    # (streams not overlapped in this one step, so that every entry point's events bracket its own kernels only)
+    qz_serial = moe.MoELayerQuantizer(moe.MoEQuantConfig(**{**cfg.__dict__, "overlap_streams": False}))
+    pt = PhaseTimer()
+    pt.install()
+    pt.enabled = True
+    out, _ = step(qz_serial)
+    phases = pt.summary()
+    pt.enabled = False
+    counts = out["counts"].cpu().double()
+    del out
+    barrier()
 
     # ---- end to end: host buffers in, packed results out (pinned memory, copies inside the timed region).
     # The call a user makes: MoELayerQuantizer.quantize_experts_host — weights (fp8 + block scales where the
@@ -384,33 +457,51 @@ def run_ours(args, rank, world, local_rank):
     e2e = None
     if not args.no_e2e:
         hX = X.cpu().pin_memory() if rank == 0 else None
-        hids = ids.cpu().pin_memory() if rank == 0 else None
+        hlog = logits.cpu().pin_memory() if rank == 0 else None
         if fp8 is not None:
-            hW = [torch.stack([q8 for q8, _ in enc]).cpu().pin_memory() for enc in fp8]
-            hS = [torch.stack([sv for _, sv in enc]).float().cpu().pin_memory() for enc in fp8]
+            hW = [q8.cpu().pin_memory() for q8, _ in fp8]
+            hS = [sv.cpu().pin_memory() for _, sv in fp8]
         else:
             hW = [w.cpu().pin_memory() for w in (Wg, Wu, Wd)]
             hS = None
+        # the device-resident copies of the weights are not part of this path: free them
+        del Wg, Wu, Wd
+        fp8 = None
+        torch.cuda.empty_cache()
         bytes_in = sum(w.numel() * w.element_size() for w in hW) + sum(t.numel() * 4 for t in (hS or []))
         if rank == 0:
-            bytes_in += hX.numel() * 2 + hids.numel() * 4
+            bytes_in += hX.numel() * 2 + hlog.numel() * 4
         host_out = {}
         d2h = [0]
 
         def step_e2e():
-            if world == 1:
-                _, host = qz.quantize_experts_host(hX, hids, hW[0], hW[1], hW[2], e_begin=e0, dense_tail=n_tail,
-                                                   fp8_scale_inv=hS)
-                d2h[0] = sum(v.numel() * v.element_size() for v in host.values())
-                return
             if rank == 0:
                 X.copy_(hX, non_blocking=True)
-                ids.copy_(hids, non_blocking=True)
-            fdist.broadcast_inputs(X, ids, src=0)
-            idl = remap[ids.long()].to(torch.int32) if remap is not None else ids
-            out, _ = qz.quantize_experts_host(X, idl, hW[0], hW[1], hW[2], e_begin=e0, dense_tail=n_tail,
-                                              fp8_scale_inv=hS, ship_results=False)
-            gathered = fdist.gather_to_rank0(local_results(out), shapes_of_rank)
+                logits.copy_(hlog, non_blocking=True)
+            x_chunks = None
+            if world > 1:
+                dist.broadcast(logits, src=0)
+                x_chunks = _bcast_x()
+            ids = route_local(logits)
+            ok, res, err = True, None, None
+            try:
+                if world == 1:
+                    res = qz.quantize_experts_host(X, ids, hW[0], hW[1], hW[2], e_begin=e0, dense_tail=n_tail,
+                                                   fp8_scale_inv=hS)
+                else:
+                    for _, wait in x_chunks:
+                        wait()
+                    res = qz.quantize_experts_host(X, ids, hW[0], hW[1], hW[2], e_begin=e0, dense_tail=n_tail,
+                                                   fp8_scale_inv=hS, ship_results=False)
+            except RuntimeError as exc:
+                ok, err = False, exc
+            if world == 1:
+                if not ok:
+                    raise err
+                d2h[0] = sum(v.numel() * v.element_size() for v in res[1].values())
+                return
+            fdist.agree_ok(ok, "solve")
+            gathered = plan.run(local_results(res[0]))
             if rank == 0:
                 tot = 0
                 for k, parts in gathered.items():
@@ -425,25 +516,17 @@ def run_ours(args, rank, world, local_rank):
 
         for _ in range(min(args.warmup, 2)):
             step_e2e()
-        ms_e2e = timed(step_e2e, args.steps)
+        ms_e2e, per_e2e = timed(step_e2e, args.steps)
         h2d_total = bytes_in
         if world > 1:
             t = torch.tensor([float(bytes_in)], dtype=torch.float64, device=dev)
             dist.all_reduce(t)
             h2d_total = int(t.item())
-        e2e = {"value": n_total * args.steps / (ms_e2e / 1e3), "unit": UNIT, "h2d_bytes_per_step": int(h2d_total),
-               "d2h_bytes_per_step": int(d2h[0]), "ms_per_step": ms_e2e / args.steps}
+        med = sorted(per_e2e)[len(per_e2e) // 2]
+        e2e = {"value": n_total / (med / 1e3), "unit": UNIT, "h2d_bytes_per_step": int(h2d_total),
+               "d2h_bytes_per_step": int(d2h[0]), "ms_per_step": med, "statistic": "median of the per-step device times",
+               "ms_per_step_mean": ms_e2e / args.steps, "ms_per_step_min": min(per_e2e), "ms_per_step_max": max(per_e2e)}
 
-    # ---- per-entry-point device time of one more step (rank 0's slice) and the roofline of the top kernel
-    # (streams not overlapped in this one step, so that every entry point's events bracket its own kernels only)
-    qz_serial = moe.MoELayerQuantizer(moe.MoEQuantConfig(**{**cfg.__dict__, "overlap_streams": False}))
-    pt = PhaseTimer()
-    pt.install()
-    pt.enabled = True
-    out, _ = step(X, ids, Wg, Wu, Wd, qz_serial)
-    phases = pt.summary()
-    pt.enabled = False
-    counts = out["counts"].cpu().double()
     peaks = {}
     try:
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -452,8 +535,8 @@ def run_ours(args, rank, world, local_rank):
     hbm_peak, hbm_src = (peaks.get("hbm_gbs"), "measured") if peaks.get("hbm_gbs") else (6650.0, "fallback")
     tf_peak, tf_src = ((peaks.get("bf16_tflops_sustained"), "measured sustained") if peaks.get("bf16_tflops_sustained")
                        else (1400.0, "fallback sustained"))
-    n_loc = len(my_ids)
     hess_flops = float((2.0 * counts * (Hd * Hd + I * I)).sum())
+    fwd_flops = float((2.0 * counts * (2.0 * I * Hd)).sum())
     # the kernel computes only the 256x256 tiles on or above the diagonal: flops it actually executes
     def _tri(c):
         nt = (c + 255) // 256
@@ -461,21 +544,20 @@ def run_ours(args, rank, world, local_rank):
     hess_exec_flops = float((2.0 * counts * (_tri(Hd) + _tri(I))).sum())
     elems = n_loc * 3 * I * Hd
     alg_bytes = {
-        "forge_hessian_grouped": None,
         "forge_quant_grid": elems * 2 + 8 * elems / 128,
-        "forge_gptq_solve_batched": elems * (2 + 1),
         "forge_chol_inv_upper_batched": n_loc * (2 * Hd * Hd + I * I) * 4 * 2,
         "forge_chol_factor_batched": n_loc * (Hd * Hd + I * I) * 4 * 2,
-        "forge_hessian_gather_damp": n_loc * (2 * Hd * Hd + I * I) * 4 * 2,
+        "forge_hessian_gather_damp": n_loc * (Hd * Hd + I * I) * 4 * 2,
         "forge_hessian_scan": n_loc * (Hd * Hd + I * I) * 4,
         "forge_pack_int4": elems * 1.5,
+        "forge_fp8_block_dequant": elems * 3.0,
     }
     top = max(phases, key=phases.get) if phases else None
     roofline = None
     if top is not None:
         t_s = phases[top] / 1e3
-        if top == "forge_hessian_grouped":
-            ach = hess_flops / t_s / 1e12
+        if top in ("forge_hessian_grouped", "forge_expert_swiglu_grouped"):
+            ach = (hess_flops if top == "forge_hessian_grouped" else fwd_flops) / t_s / 1e12
             roofline = {"kernel": top, "bound": "tensor", "achieved": ach, "peak": tf_peak, "unit": "TFLOP/s",
                         "frac": ach / tf_peak, "traffic": None, "peak_source": tf_src}
         elif top in ("forge_gptq_solve_batched", "forge_chol_factor_batched", "forge_chol_inv_upper_batched"):
@@ -488,11 +570,12 @@ def run_ours(args, rank, world, local_rank):
                 inv = 3.0 if top == "forge_chol_inv_upper_batched" else 1.0    # + triangular inverse (2/3 n^3 more)
                 flops = n_loc * inv * (Hd ** 3 + I ** 3) / 3.0
             ach = flops / t_s / 1e12
-            # DRAM bytes of the solver: ncu capture of a 32-expert cut of this very workload (4.81 GB for the three
-            # launches = 150.4 MB per expert), scaled by the experts of this rank; other shapes: not captured
-            traffic = 150.4e6 * n_loc if (top == "forge_gptq_solve_batched" and args.config == "qwen3_30b_a3b") else None
+            # DRAM bytes of the solver per expert, from ncu captures of small cuts of the same shapes (profiles/),
+            # scaled by the experts of this rank; shapes without a capture: null
+            per_expert = SOLVER_TRAFFIC_PER_EXPERT.get(args.config) if top == "forge_gptq_solve_batched" else None
             roofline = {"kernel": top, "bound": "tensor", "achieved": ach, "peak": tf_peak, "unit": "TFLOP/s",
-                        "frac": ach / tf_peak, "traffic": traffic, "peak_source": tf_src,
+                        "frac": ach / tf_peak, "traffic": per_expert * n_loc if per_expert else None,
+                        "peak_source": tf_src,
                         "executed_tf32_tflops": 3.0 * ach, "tf32_peak_assumed": tf_peak / 2.0,
                         "executed_frac_of_tf32_peak": 3.0 * ach / (tf_peak / 2.0),
                         "note": "fp32 algorithm as TF32 x3 on tcgen05; the column loop between the MMAs is a serial "
@@ -522,6 +605,12 @@ def run_ours(args, rank, world, local_rank):
         roofline["hessian_frac_of_bf16_peak"] = (hess_flops / t_h / 1e12 / tf_peak) if t_h > 0 else None
         roofline["hessian_executed_tflops"] = hess_exec_flops / t_h / 1e12 if t_h > 0 else None
         roofline["hessian_executed_frac_of_bf16_peak"] = (hess_exec_flops / t_h / 1e12 / tf_peak) if t_h > 0 else None
+        t_f = phases.get("forge_expert_swiglu_grouped", 0.0) / 1e3
+        roofline["expert_forward_tflops"] = fwd_flops / t_f / 1e12 if t_f > 0 else None
+        # HBM-bound entry points: algorithmic bytes over their device time, against the measured copy bandwidth
+        roofline["hbm_kernels"] = {k: {"GB/s": round(alg_bytes[k] / (phases[k] / 1e3) / 1e9, 1),
+                                       "frac": round(alg_bytes[k] / (phases[k] / 1e3) / 1e9 / hbm_peak, 3)}
+                                   for k in alg_bytes if phases.get(k)}
 
     cpu_base = None
     if rank == 0 and not args.no_cpu_baseline:
@@ -550,10 +639,11 @@ def run_ours(args, rank, world, local_rank):
                 "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "bf16 inputs / f32 accumulate and solve", "data": "synthetic",
                 "config": {"workload": workload_name(shape, recipe), "parallelism": f"ep{world}",
-                           "placement": args.placement if world > 1 else "single",
+                           "placement": args.placement if world > 1 else "single", "expert_chunk": chunk,
                            "l2": "inputs larger than L2 (X, weights and Hessians >> 126 MB)"},
                 "clocks": clk, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline,
                 "cpu_baseline": cpu_base, "reference_same_gpu": ref_gpu,
+                "ms_per_step_median": sorted(per_step)[len(per_step) // 2],
                 "phases_ms_rank0": {k: round(v, 3) for k, v in sorted(phases.items(), key=lambda kv: -kv[1])}}
         print(json.dumps(line), flush=True)
 

@@ -40,6 +40,10 @@ enum {
     FORGE_HESS_MIRROR = 1,   /* also write the lower triangle (full symmetric H) */
     FORGE_HESS_SIMT = 2      /* plain-FMA validation kernel instead of tcgen05 */
 };
+/* flags of forge_expert_swiglu_grouped */
+enum { FORGE_FWD_SIMT = 1 }; /* plain-FMA validation kernel instead of tcgen05 */
+/* selection rule of forge_route_topk */
+enum { FORGE_ROUTE_SOFTMAX = 0, FORGE_ROUTE_SIGMOID = 1, FORGE_ROUTE_SIGMOID_GROUPED = 2 };
 
 int forge_version(void);
 const char *forge_last_error(void);
@@ -54,15 +58,40 @@ long long forge_launch_count(void);
 int forge_fp8_block_dequant(const void *w_fp8, const float *scale_inv, void *out_bf16,
                             int64_t O, int64_t I, int64_t nO, int64_t nI, void *stream);
 
+/* ---- routing: router logits -> top-k expert ids -------------------------------
+ * logits [T,E] fp32 -> topk_ids [T,k] int32 in descending score order (ties: lower expert id) and, when
+ * topk_weights is not NULL, the scores of the chosen experts [T,k] (softmax probabilities / sigmoid scores).
+ * mode FORGE_ROUTE_SOFTMAX / FORGE_ROUTE_SIGMOID: plain top-k.  FORGE_ROUTE_SIGMOID_GROUPED (DeepSeek-V3): the
+ * experts form n_groups equal groups, a group scores the sum of its two best experts, only the topk_groups best
+ * groups stay eligible.  bias [E] (may be NULL) is added to the sigmoid scores for the selection only.  E <= 1024.
+ * The reference leaves this step to the HF MoE block's own forward (quant.py:398-406); the in-repo statement of
+ * the selection it relies on is the fused-experts capture, forge/utils/engine.py:228-238. */
+int forge_route_topk(const float *logits, const float *bias, int64_t T, int E, int k, int mode, int n_groups,
+                     int topk_groups, int32_t *topk_ids, float *topk_weights, void *stream);
+
 /* ---- routing: top-k ids -> per-expert token lists ------------------------
- * topk_ids [T,k] int32 (expert id per slot).  For the experts
- * [e_begin, e_begin+e_count) writes counts[e_count], offsets[e_count+1]
- * (exclusive prefix sum) and token_lists (token indices grouped by expert,
- * ascending inside each expert; capacity T*k).  Stands in for the gather the
- * HF MoE block performs before each expert's forward hook fires
- * (quant.py:398-406; the in-repo statement is forge/utils/engine.py:228-238). */
-int forge_route_build_lists(const int32_t *topk_ids, int64_t T, int k, int e_begin, int e_count,
+ * topk_ids [T,k] int32 (expert id per slot).  For the routed experts [e_begin, e_begin+e_count) followed by
+ * dense_tail slots that see every token (shared experts) writes counts[e_count+dense_tail],
+ * offsets[e_count+dense_tail+1] (exclusive prefix sum) and token_lists (token indices grouped by slot, ascending
+ * inside each slot; capacity T*k + dense_tail*T).  Stands in for the gather the HF MoE block performs before each
+ * expert's forward hook fires (quant.py:398-406; the in-repo statement is forge/utils/engine.py:228-238). */
+int forge_route_build_lists(const int32_t *topk_ids, int64_t T, int k, int e_begin, int e_count, int dense_tail,
                             int32_t *counts, int64_t *offsets, int32_t *token_lists, void *stream);
+
+/* ---- expert forward: the down-projection calibration input of every local expert --------
+ * For slot b and j < n_b = offsets[b+1]-offsets[b], x = row token_idx[offsets[b]+j] of X (row offsets[b]+j when
+ * token_idx is NULL):
+ *   out[offsets[b]+j, :] = bf16( bf16(silu(bf16(x Wg[b]^T))) * bf16(x Wu[b]^T) )      (fp32 accumulation)
+ * X bf16 [n_rows, ldx >= H]; Wg, Wu bf16 [nb, I, H]; out bf16 [out_rows, I], packed by slot.  One grouped
+ * tcgen05 GEMM launch, gather fused into the load, SwiGLU in the epilogue.  H % 8 == 0.  Slots whose claim does
+ * not fit the list, X or out are skipped and list entries that are not rows of X contribute zeros; the status
+ * word then says FORGE_ERR_INVALID (FORGE_ERR_TIMEOUT: a bounded wait ran out).
+ * Replaces the HF expert-module forward the reference hooks at down_proj (quant.py:398-406) and the fused-experts
+ * recomputation of that input, forge/utils/engine.py:228-258. */
+int forge_expert_swiglu_grouped(const void *X_bf16, int64_t n_rows, int64_t ldx, int64_t H, int64_t I,
+                                const int32_t *token_idx, int64_t list_len, const int64_t *offsets, int nb,
+                                const void *Wg_bf16, const void *Wu_bf16, void *out_bf16, int64_t out_rows,
+                                int flags, int32_t *status, void *stream);
 
 /* ---- A2: per-expert Hessian accumulation ---------------------------------
  * For b in [0,nb):  n = offsets[b+1]-offsets[b];  N = n_prev[b] + n;
@@ -73,14 +102,15 @@ int forge_route_build_lists(const int32_t *topk_ids, int64_t T, int k, int e_beg
  * overwritten, not read).  When n == 0 H[b] is left untouched.  n_prev is NOT
  * updated (forge_counts_add does that).  C must be a multiple of 8.
  * `status` (device int32, may be NULL) receives FORGE_ERR_TIMEOUT if a bounded
- * wait inside the kernel ran out.
+ * wait inside the kernel ran out, FORGE_ERR_INVALID if a bounds check failed.
  * Replaces GPTQ.update, forge/gptq.py:62-80 (H.addmm_ at :76-79).
- * Preconditions the library cannot check (they live in device memory): offsets is non-decreasing, token_idx
- * (when given) holds at least offsets[nb] entries, each a valid row of X; with token_idx = NULL the rows
- * offsets[b] .. offsets[b+1]-1 of X are used.  A token list shorter than the offsets claim is read out of bounds.
+ * Bounds: n_rows = rows of X, list_len = entries of token_idx (ignored when token_idx is NULL).  offsets lives in
+ * device memory, so the kernel checks it: a slot whose claim offsets[b] .. offsets[b+1] does not fit in the token
+ * list (in X, when the rows are contiguous) is skipped untouched, and a list entry that is not a row of X
+ * contributes zeros; either way the status word becomes FORGE_ERR_INVALID and no out-of-bounds read happens.
  */
-int forge_hessian_grouped(const void *X_bf16, int64_t ldx, int64_t C, const int32_t *token_idx,
-                          const int64_t *offsets, int nb, float *H, const int64_t *n_prev,
+int forge_hessian_grouped(const void *X_bf16, int64_t n_rows, int64_t ldx, int64_t C, const int32_t *token_idx,
+                          int64_t list_len, const int64_t *offsets, int nb, float *H, const int64_t *n_prev,
                           int flags, int32_t *status, void *stream);
 
 /* Self-test of the bounded device-side wait used by every tensor-core kernel: a one-CTA kernel waits on a barrier
@@ -222,6 +252,18 @@ int forge_mxfp4_dequant(const uint8_t *blocks, const uint8_t *scales, int64_t ro
  * Replaces dequantize_forge_full, forge/utils/engine.py:72-97. */
 int forge_dequantize(const uint8_t *q, const float *scales, const float *qzeros, int64_t rows, int64_t C,
                      int gs, void *out, int out_dtype, void *stream);
+
+/* ---- acceptance quantity: layer reconstruction loss ---------------------------
+ * loss[b] = || X_b W[b]^T - X_b What[b]^T ||_F^2 with What = (q - qzeros) * scales (per group of gs input
+ * columns), X_b the rows of X that slot x_map[b] (x_map NULL = b) lists through token_idx / offsets exactly as in
+ * forge_hessian_grouped.  W [nb,R,C] bf16 or fp32, q [nb,R,C] uint8, scales/qzeros [nb,R,G] fp32, loss [nb] double
+ * (overwritten).  fp32 dot products, squares summed in double.  A check, not a hot kernel.
+ * Replaces the per-layer relative-error evaluation of the driver, quant.py:491-496 (dequantize_forge_full,
+ * forge/utils/engine.py:72-97, followed by a forward). */
+int forge_recon_loss(const void *W, int w_dtype, const uint8_t *q, const float *scales, const float *qzeros, int gs,
+                     int nb, int64_t R, int64_t C, const void *X_bf16, int64_t n_rows, int64_t ldx,
+                     const int32_t *token_idx, int64_t list_len, const int64_t *offsets, const int32_t *x_map,
+                     double *loss, int32_t *status, void *stream);
 
 /* ---- A11: dense int4 "pack-quantized" layout -------------------------------
  * packed[r, j] = sum_{i<8} uint8(int8(q[r,8j+i]) - int8(zero[r,(8j+i)/gs]) + 8) << 4i   (int32 wrap;

@@ -2,7 +2,8 @@
 
     python tests/golden/make_golden_io.py <reference checkout>
 
-Calls forge/utils/io.py::_apply_block_scale (packed int4 + group scales) and ::_dequant_mxfp4_blocks_to_fp (MXFP4) of
+Calls forge/utils/io.py::_apply_block_scale (packed int4 + group scales), ::_dequant_mxfp4_blocks_to_fp (MXFP4) and
+::_apply_block_scale_inv_2d followed by the cast of materialize_block_weights_to_fp (fp8 e4m3 + 128x128 block scales) of
 the reference on small seeded inputs and stores inputs and outputs in tests/golden/io_materialise.npz.  The module
 imports accelerate and huggingface_hub at its top for unrelated functions; where those packages are absent they
 are replaced by empty stand-ins, which the two functions used here never touch.
@@ -48,6 +49,15 @@ sc[0, 0, 0] = 0          # the e == 0 rule
 sc[1, 5, 2] = 254
 out["mx_blocks"], out["mx_scales"] = blocks, sc
 out["mx_out"] = rio._dequant_mxfp4_blocks_to_fp(blocks, sc).contiguous()
+# fp8 e4m3 weights with fp32 block scales: whole tiles, a partial last row tile, and a scale grid whose row tile is
+# not the column tile (the `so` fall-back of the reference's inference rule)
+for tag, (O8, I8, nO, nI) in {"sq": (256, 256, 2, 2), "ragged": (200, 384, 2, 3), "tall": (96, 128, 3, 1)}.items():
+    w8 = (torch.randn(O8, I8, generator=g) * 60.0).to(torch.float8_e4m3fn)
+    sinv = (torch.rand(nO, nI, generator=g) * 2e-3 + 1e-5).to(torch.float32)
+    w = rio._apply_block_scale_inv_2d(w8.to(torch.float32), sinv).to(torch.bfloat16)   # io.py:864-874
+    out[f"fp8_{tag}_w"] = w8.view(torch.uint8)
+    out[f"fp8_{tag}_sinv"] = sinv
+    out[f"fp8_{tag}_out_bits"] = w.view(torch.int16)
 path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "io_materialise.npz")
 np.savez_compressed(path, **{k: v.numpy() for k, v in out.items()})
 print(path, os.path.getsize(path), "bytes")

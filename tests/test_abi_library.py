@@ -2,6 +2,7 @@
 import ctypes
 import os
 import re
+import sys
 
 import pytest
 
@@ -58,3 +59,43 @@ def test_product_does_not_import_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 txt = open(os.path.join(dirpath, f)).read()
                 assert "ref_port" not in txt and "forge_oracle" not in txt, f
+
+
+REFERENCE = os.environ.get("FORGE_REFERENCE_ROOT", os.path.join(os.path.dirname(ROOT), "reference"))
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REFERENCE, "forge", "utils")), reason="no reference checkout here")
+def test_package_coexists_with_the_reference_checkout():
+    """The reference driver's imports (quant.py:15-17: `import forge.utils`, `from forge.gptq import GPTQ`) with this
+    package AHEAD of the reference on sys.path: forge.gptq / forge.backend come from here, forge.utils from the
+    reference.  Run in a child interpreter so that this process's import state does not matter; third-party packages
+    the reference's utils import at module level and that are not installed here get empty stand-ins."""
+    import subprocess
+    import textwrap
+    code = textwrap.dedent(f"""
+        import sys, types, importlib.machinery
+        import transformers  # before the stand-ins: it probes for optional packages with find_spec
+        sys.path[:0] = [{os.path.join(ROOT, '4bit-forge_b200')!r}, {REFERENCE!r}]
+        for name, attrs in (("accelerate", ("init_empty_weights",)), ("accelerate.utils", ("set_module_tensor_to_device",)),
+                            ("huggingface_hub", ("hf_hub_download",)), ("datasets", ("load_dataset",))):
+            try:
+                __import__(name)
+            except Exception:
+                m = types.ModuleType(name)
+                m.__spec__ = importlib.machinery.ModuleSpec(name, None)
+                for a in attrs:
+                    setattr(m, a, None)
+                sys.modules[name] = m
+        import forge.utils
+        from forge.gptq import GPTQ
+        from forge.backend.cuda import kernels
+        import forge, forge.moe
+        ours = {os.path.join(ROOT, '4bit-forge_b200', 'forge')!r}
+        assert forge.gptq.__file__.startswith(ours), forge.gptq.__file__
+        assert forge.utils.__file__.startswith({os.path.join(REFERENCE, 'forge', 'utils')!r}), forge.utils.__file__
+        assert hasattr(forge.utils.engine, "dequantize_forge_full") and hasattr(forge.utils.io, "_apply_block_scale_inv_2d")
+        assert hasattr(kernels, "gptq_solver") and hasattr(GPTQ, "quantize")
+        print("coexist ok")
+    """)
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "coexist ok" in r.stdout, r.stderr[-2000:]

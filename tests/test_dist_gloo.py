@@ -38,9 +38,10 @@ def _free_port():
 
 
 def _worker(rank, world, port, fail_rank):
+    import datetime
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=60))
     try:
         E, T, Hd = 5, 64, 16
         if rank == 0:
@@ -49,7 +50,10 @@ def _worker(rank, world, port, fail_rank):
         else:
             X = torch.zeros((T, Hd), dtype=torch.bfloat16)
             ids = torch.zeros((T, 2), dtype=torch.int32)
-        X, ids = fdist.broadcast_inputs(X, ids, src=0, chunks=4)
+        X, ids, ready = fdist.broadcast_inputs(X, ids, src=0, chunks=4)
+        assert [t1 for t1, _ in ready] == [16, 32, 48, 64]
+        for _, wait in ready:
+            wait()
         X_ref = synth.student_t_activations(T, Hd, seed=3)
         assert torch.equal(X.view(torch.int16), X_ref.view(torch.int16))
         b, e = fdist.shard_experts(E, world, rank)
@@ -61,7 +65,25 @@ def _worker(rank, world, port, fail_rank):
             bb, ee = fdist.shard_experts(E, world, r)
             return {"packed": ((ee - bb, 3, 2), torch.int32), "scale": ((ee - bb,), torch.float16)}
 
-        got = fdist.gather_to_rank0(local, shapes)
+        # a rank whose local work raised: every rank learns of it BEFORE the gather and raises, nobody waits forever
+        ok = True
+        try:
+            if rank == fail_rank:
+                raise RuntimeError("injected: this rank's solve failed on the host")
+        except RuntimeError:
+            ok = False
+        if fail_rank >= 0:
+            try:
+                fdist.agree_ok(ok, "solve")
+            except RuntimeError as exc:
+                assert "rank(s) failed" in str(exc)
+                assert ("this rank among them" in str(exc)) == (rank == fail_rank)
+                return
+            raise AssertionError("agree_ok did not raise although a rank failed")
+        fdist.agree_ok(ok, "solve")
+        plan = fdist.GatherPlan(shapes, "cpu")
+        for _ in range(2):      # the plan's buffers are reused by every step
+            got = fdist.gather_to_rank0(local, shapes, plan)
         if rank == 0:
             packed = torch.cat(got["packed"])
             assert packed.shape == (E, 3, 2)
@@ -77,6 +99,20 @@ def _worker(rank, world, port, fail_rank):
 def test_broadcast_and_gather_two_ranks():
     port = _free_port()
     mp.spawn(_worker, args=(2, port, -1), nprocs=2, join=True)
+
+
+def test_a_rank_that_fails_on_the_host_stops_every_rank_before_the_gather():
+    port = _free_port()
+    mp.spawn(_worker, args=(2, port, 1), nprocs=2, join=True)
+
+
+def test_gather_plan_layout_is_padded_and_aligned():
+    shapes = lambda r: {"a": ((r + 1, 3), torch.int32), "b": ((2 * r,), torch.float16)}
+    plan = fdist.GatherPlan(shapes, "cpu", world=3, rank=0)
+    assert plan.max_bytes % 256 == 0 and plan.max_bytes >= 3 * 3 * 4 + 4 * 2
+    for r in range(3):
+        lay, total = plan.layouts[r]
+        assert total <= plan.max_bytes and all(off % 256 == 0 for off, *_ in lay.values())
 
 
 def test_balanced_placement_covers_all_and_evens_out_load():

@@ -147,8 +147,9 @@ def test_moe_layer_against_per_expert_oracle(algorithm, order, scale, sym):
     for e in range(7):
         xe = X[lists[e]]
         # the down-projection input is model output: take the engine's own bf16 activations for both sides
-        act = moe.swiglu_expert_forward(X.to(DEV), lists[e].to(torch.int32).to(DEV), torch.tensor([0, len(lists[e])]),
-                                        Wg_d[e:e + 1], Wu_d[e:e + 1]).cpu()[:len(lists[e])]
+        act = moe.swiglu_expert_forward(X.to(DEV), lists[e].to(torch.int32).to(DEV),
+                                        torch.tensor([0, len(lists[e])], dtype=torch.int64, device=DEV),
+                                        Wg_d[e:e + 1], Wu_d[e:e + 1], len(lists[e])).cpu()[:len(lists[e])]
         if len(lists[e]):
             assert rel_fro(act.float(), O.swiglu_down_input(xe, Wg[e], Wu[e]).float()) < 2e-2
         for name, Wm, xin in (("gate", Wg[e], xe), ("up", Wu[e], xe), ("down", Wd[e], act)):

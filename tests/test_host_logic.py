@@ -79,3 +79,57 @@ def test_checkpoint_layouts(tmp_path):
     assert torch.equal(back[k + ".weight_packed"], t[k + ".weight_packed"])
     cfg = checkpoint.quantization_config(4, 128, symmetric=False)
     assert cfg["format"] == "pack-quantized" and cfg["config_groups"]["group_0"]["weights"]["symmetric"] is False
+
+
+def test_writers_driver_dict_index_and_resume(tmp_path):
+    """quantized_weight.pt with the driver's keys (quant.py:498-511), the incrementally rewritten index
+    (forge/utils/io.py:630-672), dropped dense expert keys, resume by existing shard, gather re-ordering."""
+    import json
+    import torch
+    from safetensors.torch import load_file
+    from forge import checkpoint
+    g = torch.Generator().manual_seed(1)
+    R, C, gs = 8, 64, 32
+    q = torch.randint(0, 16, (R, C), generator=g, dtype=torch.uint8)
+    s, z = torch.rand(R * C // gs, generator=g), torch.randint(0, 16, (R * C // gs,), generator=g).float()
+    res = {"mlp.experts.0.gate_proj": (q, s, z), "mlp.experts.0.gate_proj.info": torch.tensor(0)}
+    paths = checkpoint.write_linear_results(str(tmp_path / "save"), 3, res, gs, 4)
+    assert paths == [str(tmp_path / "save" / "block.3" / "mlp.experts.0.gate_proj" / "quantized_weight.pt")]
+    d = torch.load(paths[0])
+    assert set(d) == {"qweight", "scales", "qzeros", "group_size", "bits", "shape"}
+    assert d["qweight"].dtype == torch.int8 and d["scales"].dtype == torch.float32 and d["qzeros"].dtype == torch.int32
+    assert d["shape"] == (R, C) and d["group_size"] == gs and d["bits"] == 4 and torch.equal(d["qweight"], q.to(torch.int8))
+    assert checkpoint.write_linear_results(str(tmp_path / "save"), 3, res, gs, 4) == []          # resume: kept
+    assert torch.load(checkpoint.write_run_metadata(str(tmp_path / "save"), 4, gs, True))["quantize_only_experts"] is True
+
+    n, I, H = 2, 32, 64
+    fam = lambda R_, C_: {"qweight": torch.zeros(n, R_, C_, dtype=torch.uint8),
+                          "weight_packed": torch.randint(0, 99, (n, R_, C_ // 8), generator=g, dtype=torch.int32),
+                          "weight_scale": torch.rand(n, R_, C_ // gs, generator=g).to(torch.float16),
+                          "qzeros": torch.full((n, R_, C_ // gs), 8.0)}
+    out = {"gate": fam(I, H), "up": fam(I, H), "down": fam(H, I)}
+    prefix = "model.layers.5."
+    base = {"metadata": {"total_size": 1}, "weight_map": {
+        f"{prefix}mlp.experts.0.gate_proj.weight": "a.safetensors", f"{prefix}mlp.experts.1.down_proj.weight_scale_inv": "a.safetensors",
+        f"{prefix}mlp.shared_experts.gate_proj.weight": "a.safetensors", f"{prefix}self_attn.q_proj.weight": "a.safetensors",
+        "model.layers.6.mlp.experts.0.gate_proj.weight": "b.safetensors"}}
+    w = checkpoint.IncrementalIndexWriter(str(tmp_path / "base"), str(tmp_path / "out"), base)
+    assert not w.block_done(5)
+    path = checkpoint.write_moe_block(w, 5, prefix, out, n_routed=n, symmetric=True, sparse=False)
+    assert path.endswith("block_005.safetensors") and w.block_done(5)
+    idx = json.load(open(tmp_path / "out" / "model.safetensors.index.json"))
+    wm = idx["weight_map"]
+    assert wm[f"{prefix}mlp.experts.1.down_proj.weight_packed"] == "block_005.safetensors"
+    assert f"{prefix}mlp.experts.0.gate_proj.weight" not in wm and f"{prefix}mlp.experts.1.down_proj.weight_scale_inv" not in wm
+    assert wm[f"{prefix}mlp.shared_experts.gate_proj.weight"] == "a.safetensors"       # shared experts are never dropped
+    assert wm[f"{prefix}self_attn.q_proj.weight"] == "a.safetensors" and "model.layers.6.mlp.experts.0.gate_proj.weight" in wm
+    back = load_file(path)
+    assert torch.equal(back[f"{prefix}mlp.experts.1.gate_proj.weight_packed"], out["gate"]["weight_packed"][1])
+    assert checkpoint.write_moe_block(w, 5, prefix, out, n_routed=n, symmetric=True, sparse=False) is None   # resume
+    w2 = checkpoint.IncrementalIndexWriter(str(tmp_path / "base"), str(tmp_path / "out"), base)               # rerun
+    assert w2.block_done(5) and f"{prefix}mlp.experts.0.gate_proj.weight" not in w2.weight_map
+    assert w2.weight_map[f"{prefix}mlp.experts.0.up_proj.weight_packed"] == "block_005.safetensors"
+
+    owned = [[0, 3], [1, 2, 4]]
+    gathered = {"x": [torch.tensor([[0.], [3.]]), torch.tensor([[1.], [2.], [4.]])]}
+    assert checkpoint.reorder_gathered(gathered, owned)["x"].flatten().tolist() == [0., 1., 2., 3., 4.]

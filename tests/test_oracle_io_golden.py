@@ -29,3 +29,12 @@ def test_mxfp4_dequant_bit_exact(gold):
     w = O.mxfp4_dequant(gold["mx_blocks"], gold["mx_scales"])
     assert w.shape == gold["mx_out"].shape
     assert torch.equal(w, gold["mx_out"])
+
+
+@pytest.mark.parametrize("tag", ["sq", "ragged", "tall"])
+def test_fp8_block_dequant_bit_exact(gold, tag):
+    """O.fp8_block_dequant against _apply_block_scale_inv_2d + the bf16 cast of the reference (forge/utils/io.py:533-563,
+    :864-874), run on the CPU by make_golden_io.py."""
+    w8 = gold[f"fp8_{tag}_w"].view(torch.float8_e4m3fn)
+    got = O.fp8_block_dequant(w8, gold[f"fp8_{tag}_sinv"])
+    assert torch.equal(got.view(torch.int16), gold[f"fp8_{tag}_out_bits"])
