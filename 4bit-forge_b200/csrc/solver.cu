@@ -60,6 +60,8 @@ struct SolveParams {
     int64_t R, C, G;
     int gs, maxq, write_deq, uvec_is_diag;
     int alt;               // 1: U holds -Vt (inversion-free form) and the propagated quantity is w - deq
+    const uint8_t *usplit; // [nu] pre-split hi/lo operand pieces of U (forge_solve_split_u), or null
+    int64_t usplit_stride; // bytes per Hessian slot
 };
 
 __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc, bool pred) {
@@ -347,39 +349,53 @@ __global__ void __launch_bounds__(128, 3) solve_kernel(const SolveParams p) {
 // ================================================================================================
 constexpr int kTcThreads = 160;
 constexpr int kTcStageBytes = 4 * kPieceBytes;      // Ehi, Elo, Uhi, Ulo
-constexpr int kTcStages = 2;
+// Operand ring depth.  Two stages keep three CTAs per SM (the serial column chain wants the warps); with the U pieces
+// pre-split in global memory and brought in by bulk copies, a four-stage ring (two CTAs per SM) keeps the tensor
+// pipe fed through the long far phases of wide matrices.
+constexpr int kTcStagesShallow = 2, kTcStagesDeep = 4;
 constexpr int kUsubLd = kSub;                        // staged triangle: row t holds U[t][t+1 ...], zero padded
 constexpr int kUsubFloats = kSub * kUsubLd;
 // raw fp32 k-steps in flight (cp.async) in the far phase: 2 where the launch fills the GPU (a third would cost the third
 // CTA per SM its shared memory), 6 where there are at most two CTAs per SM anyway and latency is all that counts
 constexpr int kTcRawFull = 2, kTcRawDeep = 6;
-constexpr int kTcRawBytes = 4 * 128 * 16;            // [E row jA, E row jA+4, U row jA, U row jA+4][128 threads]
-constexpr size_t tc_smem_bytes(int raw) {
-    return (size_t)kTcStages * kTcStageBytes + 1024 + 2 * kUsubFloats * sizeof(float) + kSub * kBlk * sizeof(float) +
-           kBlk * sizeof(float) + 256 + (size_t)raw * kTcRawBytes;
+// one raw k-step: [E row jA, E row jA+4 (, U row jA, U row jA+4)][128 threads][16 B]; U only when it is not pre-split
+constexpr int tc_raw_bytes(bool tmau) { return (tmau ? 2 : 4) * 128 * 16; }
+constexpr size_t tc_smem_bytes(int stages, int raw, bool tmau) {
+    return (size_t)stages * kTcStageBytes + 1024 + 2 * kUsubFloats * sizeof(float) + kSub * kBlk * sizeof(float) +
+           kBlk * sizeof(float) + 256 + (size_t)raw * tc_raw_bytes(tmau);
+}
+// Pre-split U: for column block cb (128 columns) the k-steps ks = 0 .. 16 (cb + 1) - 1 (8 rows of U each: every row
+// above the block, then the block's own rows for the near updates), one [hi piece | lo piece] pair of 8 KB per
+// k-step, k-steps of a block contiguous, blocks in order: pair index = 8 cb (cb + 1) + ks.
+constexpr int kPairBytes = 2 * kPieceBytes;
+__host__ __device__ inline int64_t usplit_pair_index(int64_t cb, int64_t ks) { return 8 * cb * (cb + 1) + ks; }
+__host__ __device__ inline int64_t usplit_bytes_per_slot(int64_t C) {
+    const int64_t nblk = (C + kBlk - 1) / kBlk;
+    return 8 * nblk * (nblk + 1) * (int64_t)kPairBytes;
 }
 
 __device__ __forceinline__ void rows_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
-template <int MODE, bool SPARSE, int kTcRaw>
-__global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolveParams p, int32_t *status) {
+template <int MODE, bool SPARSE, int kTcRaw, int kTcStages, bool TMAU>
+__global__ void __launch_bounds__(kTcThreads, (kTcStages > 2 ? 2 : 3)) solve_tc_kernel(const SolveParams p, int32_t *status) {
     using namespace forge::tc;
     extern __shared__ uint8_t smem_raw[];
+    constexpr int kTcRawBytes = tc_raw_bytes(TMAU);
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *ring = smem_raw + (smem_base - smem_u32(smem_raw));
     float *Usub = reinterpret_cast<float *>(ring + kTcStages * kTcStageBytes);  // [2][32][32]
     float *es = Usub + 2 * kUsubFloats;                                          // [32][128] errors of a sub-block
     float *uinv_s = es + kSub * kBlk;                                            // [128]
-    uint64_t *bars = reinterpret_cast<uint64_t *>(uinv_s + kBlk);                // full[4], empty[4], acc
+    uint64_t *bars = reinterpret_cast<uint64_t *>(uinv_s + kBlk);                // full[<=4], empty[<=4] at +4, acc at +8
     uint8_t *raw = reinterpret_cast<uint8_t *>(bars) + 256;                      // [kTcRaw][8 KB]
     uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + 9);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
-    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + kTcStages), bar_acc = smem_u32(bars + 8);
+    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + 4), bar_acc = smem_u32(bars + 8);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
         for (int s = 0; s < kTcStages; ++s) {
-            mbar_init(bar_full + 8 * s, kBlk);
+            mbar_init(bar_full + 8 * s, kBlk + (TMAU ? 1 : 0));   // + the thread that announces the bulk copy of U
             mbar_init(bar_empty + 8 * s, 1);
         }
         mbar_init(bar_acc, 1);
@@ -404,6 +420,7 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
     float *Wt = p.Wt + (int64_t)b * C * R;
     float *E = p.E + (int64_t)b * C * R;
     const float *U = p.U + (int64_t)u * C * C;
+    const uint8_t *usp = TMAU ? p.usplit + (int64_t)u * p.usplit_stride : nullptr;
     uint32_t it = 0;       // k-steps pushed through the ring (same sequence in both roles)
     uint32_t acc_it = 0;   // accumulator hand-overs (commits by warp 4 / waits by the row warps)
 
@@ -424,19 +441,24 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
             // ---------------- far phase: every column before the block ----------------
             if (bs > 0 && ok) {
                 // operands travel global -> raw ring (cp.async, kTcRaw k-steps ahead, no registers held) -> hi/lo split
-                // -> operand stage; a thread reads back only the 16-byte chunks it copied itself (no barrier needed)
+                // -> operand stage; a thread reads back only the 16-byte chunks it copied itself (no barrier needed).
+                // TMAU: only the errors go that way; the U pieces were split once for all row strips
+                // (forge_solve_split_u) and one thread brings each [hi | lo] pair in with a bulk copy.
                 const int nks = (int)(bs / kKS);
                 const uint32_t raw_u32 = smem_u32(raw) + (uint32_t)tid * 16u;
                 const float *srcE = E + (int64_t)jA * R + r0 + 4 * c4;
                 const float *srcU = U + (int64_t)jA * C + bs + 4 * c4;
+                const uint8_t *upair = TMAU ? usp + usplit_pair_index(bs / kBlk, 0) * kPairBytes : nullptr;
                 auto issue = [&](int ks) {
                     if (ks < nks) {
                         const uint32_t dst = raw_u32 + (uint32_t)(ks % kTcRaw) * kTcRawBytes;
                         const int64_t j = (int64_t)ks * kKS;
                         cp_async16_zfill(dst, e_ok ? srcE + j * R : E, e_ok);
                         cp_async16_zfill(dst + 2048, e_ok ? srcE + (j + 4) * R : E, e_ok);
-                        cp_async16_zfill(dst + 4096, u_ok ? srcU + j * C : U, u_ok);
-                        cp_async16_zfill(dst + 6144, u_ok ? srcU + (j + 4) * C : U, u_ok);
+                        if (!TMAU) {
+                            cp_async16_zfill(dst + 4096, u_ok ? srcU + j * C : U, u_ok);
+                            cp_async16_zfill(dst + 6144, u_ok ? srcU + (j + 4) * C : U, u_ok);
+                        }
                     }
                     cp_async_commit();
                 };
@@ -449,21 +471,30 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
                     float4 ve[2], vu[2];
                     ve[0] = *reinterpret_cast<const float4 *>(rs);
                     ve[1] = *reinterpret_cast<const float4 *>(rs + 2048);
-                    vu[0] = *reinterpret_cast<const float4 *>(rs + 4096);
-                    vu[1] = *reinterpret_cast<const float4 *>(rs + 6144);
+                    if (!TMAU) {
+                        vu[0] = *reinterpret_cast<const float4 *>(rs + 4096);
+                        vu[1] = *reinterpret_cast<const float4 *>(rs + 6144);
+                    }
                     const uint32_t s = it % kTcStages, ph = (it / kTcStages) & 1u;
                     ok = mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag);
                     if (!ok) break;
                     uint8_t *stage = ring + s * kTcStageBytes;
+                    if (TMAU && tid == 0) {
+                        mbar_arrive_expect_tx(bar_full + 8 * s, (uint32_t)kPairBytes);
+                        bulk_copy_g2s(smem_base + s * kTcStageBytes + 2 * kPieceBytes, upair + (int64_t)ks * kPairBytes,
+                                      (uint32_t)kPairBytes, bar_full + 8 * s);
+                    }
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         float4 hi, lo;
                         split4(ve[h], hi, lo);
                         *reinterpret_cast<float4 *>(stage + 0 * kPieceBytes + sw_off[h]) = hi;
                         *reinterpret_cast<float4 *>(stage + 1 * kPieceBytes + sw_off[h]) = lo;
-                        split4(vu[h], hi, lo);
-                        *reinterpret_cast<float4 *>(stage + 2 * kPieceBytes + sw_off[h]) = hi;
-                        *reinterpret_cast<float4 *>(stage + 3 * kPieceBytes + sw_off[h]) = lo;
+                        if (!TMAU) {
+                            split4(vu[h], hi, lo);
+                            *reinterpret_cast<float4 *>(stage + 2 * kPieceBytes + sw_off[h]) = hi;
+                            *reinterpret_cast<float4 *>(stage + 3 * kPieceBytes + sw_off[h]) = lo;
+                        }
                     }
                     fence_proxy_async();
                     mbar_arrive(bar_full + 8 * s);
@@ -500,14 +531,16 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
                 // (2) near update: the previous sub-block's errors go to the later columns of the block
                 if (sb > 0 && ok) {
                     float4 nu[4][2];
+                    if (!TMAU) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i)
+                        for (int i = 0; i < 4; ++i)
 #pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            const int64_t j = cs - kSub + i * kKS + jA + 4 * h;
-                            nu[i][h] = (u_ok && j < C) ? *reinterpret_cast<const float4 *>(U + j * C + bs + 4 * c4)
-                                                       : make_float4(0.f, 0.f, 0.f, 0.f);
-                        }
+                            for (int h = 0; h < 2; ++h) {
+                                const int64_t j = cs - kSub + i * kKS + jA + 4 * h;
+                                nu[i][h] = (u_ok && j < C) ? *reinterpret_cast<const float4 *>(U + j * C + bs + 4 * c4)
+                                                           : make_float4(0.f, 0.f, 0.f, 0.f);
+                            }
+                    }
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         if (ok) {
@@ -515,6 +548,13 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
                             ok = mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag);
                             if (ok) {
                                 uint8_t *stage = ring + s * kTcStageBytes;
+                                if (TMAU && tid == 0) {
+                                    // the block's own rows follow the far k-steps in the pre-split layout
+                                    const int64_t pair = usplit_pair_index(bs / kBlk, bs / kKS + (sb - 1) * 4 + i);
+                                    mbar_arrive_expect_tx(bar_full + 8 * s, (uint32_t)kPairBytes);
+                                    bulk_copy_g2s(smem_base + s * kTcStageBytes + 2 * kPieceBytes, usp + pair * kPairBytes,
+                                                  (uint32_t)kPairBytes, bar_full + 8 * s);
+                                }
 #pragma unroll
                                 for (int jj = 0; jj < kKS; ++jj) {
                                     const float v = es[(i * kKS + jj) * kBlk + tid];
@@ -524,12 +564,14 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
                                     *reinterpret_cast<float *>(stage + 0 * kPieceBytes + off) = hi;
                                     *reinterpret_cast<float *>(stage + 1 * kPieceBytes + off) = lo;
                                 }
+                                if (!TMAU) {
 #pragma unroll
-                                for (int h = 0; h < 2; ++h) {
-                                    float4 hi, lo;
-                                    split4(nu[i][h], hi, lo);
-                                    *reinterpret_cast<float4 *>(stage + 2 * kPieceBytes + sw_off[h]) = hi;
-                                    *reinterpret_cast<float4 *>(stage + 3 * kPieceBytes + sw_off[h]) = lo;
+                                    for (int h = 0; h < 2; ++h) {
+                                        float4 hi, lo;
+                                        split4(nu[i][h], hi, lo);
+                                        *reinterpret_cast<float4 *>(stage + 2 * kPieceBytes + sw_off[h]) = hi;
+                                        *reinterpret_cast<float4 *>(stage + 3 * kPieceBytes + sw_off[h]) = lo;
+                                    }
                                 }
                                 fence_proxy_async();
                                 mbar_arrive(bar_full + 8 * s);
@@ -717,10 +759,42 @@ __global__ void __launch_bounds__(kTcThreads, 3) solve_tc_kernel(const SolvePara
     }
     tc_fence_before();
     __syncthreads();
-    if (*abort_flag && tid == 0 && status) atomicExch(status, FORGE_ERR_TIMEOUT);
+    if (*abort_flag) {
+        if (tid == 0 && status) atomicExch(status, FORGE_ERR_TIMEOUT);
+        if (TMAU) {
+            // a CTA that gave up may still have bulk copies of U in flight towards its shared memory: give them time
+            // to land (bounded; they take microseconds) before the CTA returns
+            const long long t0 = clock64();
+            while (clock64() - t0 < 2000000LL) {}
+        }
+    }
     if (warp == 4) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(128u) : "memory");
+    }
+}
+
+// [hi | lo] operand pieces of U for the tensor-core solver (layout: usplit_pair_index).  One CTA per pair: 128 threads,
+// each two 16-byte chunks (rows j and j + 4 of the k-step), exactly the slots the solver's own producers would write.
+__global__ void __launch_bounds__(128) split_u_kernel(const float *__restrict__ Uall, int64_t C, uint8_t *__restrict__ out,
+                                                      int64_t out_stride) {
+    const int64_t ks = blockIdx.x, cb = blockIdx.y;
+    if (ks >= 16 * (cb + 1)) return;
+    const int u = blockIdx.z;
+    const float *U = Uall + (int64_t)u * C * C;
+    uint8_t *pair = out + (int64_t)u * out_stride + usplit_pair_index(cb, ks) * kPairBytes;
+    const int tid = threadIdx.x, jA = tid >> 5, c4 = tid & 31;
+    const int64_t col = cb * kBlk + 4 * c4;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int64_t j = ks * kKS + jA + 4 * h;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (j < C && col < C) v = *reinterpret_cast<const float4 *>(U + j * C + col);
+        float4 hi, lo;
+        split4(v, hi, lo);
+        const uint32_t off = piece_offset(jA + 4 * h, c4);
+        *reinterpret_cast<float4 *>(pair + off) = hi;
+        *reinterpret_cast<float4 *>(pair + kPieceBytes + off) = lo;
     }
 }
 
@@ -798,22 +872,26 @@ inline bool use_tc_solver(const SolveParams &p) {
 
 template <int MODE, bool SPARSE>
 int launch_solve(const SolveParams &p, int nb, int32_t *status, cudaStream_t st) {
-    // per-device attributes: set on the device that is current for this call
-    cudaFuncSetAttribute(solve_kernel<MODE, SPARSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSolveSmem);
-    cudaFuncSetAttribute(solve_tc_kernel<MODE, SPARSE, kTcRawFull>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         (int)tc_smem_bytes(kTcRawFull));
-    cudaFuncSetAttribute(solve_tc_kernel<MODE, SPARSE, kTcRawDeep>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         (int)tc_smem_bytes(kTcRawDeep));
     dim3 grid((unsigned)cdiv(p.R, kBlk), (unsigned)nb);
-    if (use_tc_solver(p)) {
-        if ((int64_t)grid.x * grid.y <= 2 * 148) {
-            solve_tc_kernel<MODE, SPARSE, kTcRawDeep><<<grid, kTcThreads, tc_smem_bytes(kTcRawDeep), st>>>(p, status);
-        } else {
-            solve_tc_kernel<MODE, SPARSE, kTcRawFull><<<grid, kTcThreads, tc_smem_bytes(kTcRawFull), st>>>(p, status);
-        }
-        FORGE_NOTE_LAUNCH();
-    } else {
+    if (!use_tc_solver(p)) {
+        cudaFuncSetAttribute(solve_kernel<MODE, SPARSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSolveSmem);
         solve_kernel<MODE, SPARSE><<<grid, kBlk, kSolveSmem, st>>>(p); FORGE_NOTE_LAUNCH();
+        return check_launch("forge_gptq_solve");
+    }
+    // per-device attributes (more than 48 KB of dynamic shared memory): set on the device that is current for this call
+    auto go = [&](auto kernel, size_t smem) {
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        kernel<<<grid, kTcThreads, smem, st>>>(p, status); FORGE_NOTE_LAUNCH();
+    };
+    const bool few = (int64_t)grid.x * grid.y <= 2 * 148;
+    if (p.usplit) {
+        // U pre-split: wide matrices (long far phases) take the deep ring, two CTAs per SM; others keep three per SM
+        if (p.C >= 4096 || few) go(solve_tc_kernel<MODE, SPARSE, 4, kTcStagesDeep, true>, tc_smem_bytes(kTcStagesDeep, 4, true));
+        else go(solve_tc_kernel<MODE, SPARSE, 4, kTcStagesShallow, true>, tc_smem_bytes(kTcStagesShallow, 4, true));
+    } else if (few) {
+        go(solve_tc_kernel<MODE, SPARSE, kTcRawDeep, kTcStagesShallow, false>, tc_smem_bytes(kTcStagesShallow, kTcRawDeep, false));
+    } else {
+        go(solve_tc_kernel<MODE, SPARSE, kTcRawFull, kTcStagesShallow, false>, tc_smem_bytes(kTcStagesShallow, kTcRawFull, false));
     }
     return check_launch("forge_gptq_solve");
 }
@@ -821,6 +899,22 @@ int launch_solve(const SolveParams &p, int nb, int32_t *status, cudaStream_t st)
 inline int64_t align256(int64_t x) { return (x + 255) & ~(int64_t)255; }
 
 }  // namespace
+
+extern "C" int64_t forge_solve_split_u_bytes(int nu, int64_t C) {
+    return (C > 0 && C % 4 == 0 && nu > 0) ? (int64_t)nu * usplit_bytes_per_slot(C) : 0;
+}
+
+extern "C" int forge_solve_split_u(const float *U, int nu, int64_t C, void *usplit, void *stream) {
+    FORGE_REQUIRE(U && usplit, "null pointer");
+    FORGE_REQUIRE(nu > 0 && C > 0 && C % 4 == 0, "C must be a positive multiple of 4");
+    FORGE_REQUIRE((uintptr_t)U % 16 == 0 && (uintptr_t)usplit % 16 == 0, "U and usplit must be 16-byte aligned");
+    const int64_t nblk = cdiv(C, kBlk);
+    FORGE_REQUIRE(nblk <= 65535 && nu <= 65535, "too many column blocks / slots for one launch");
+    split_u_kernel<<<dim3((unsigned)(16 * nblk), (unsigned)nblk, (unsigned)nu), 128, 0, (cudaStream_t)stream>>>(
+        U, C, (uint8_t *)usplit, usplit_bytes_per_slot(C));
+    FORGE_NOTE_LAUNCH();
+    return check_launch("forge_solve_split_u");
+}
 
 extern "C" int64_t forge_solve_workspace_bytes(int nb, int64_t R, int64_t C) {
     return align256((int64_t)nb * C * R * 4) + align256((int64_t)nb * C * R) + align256((int64_t)nb * C * 4) + 256;
@@ -844,9 +938,11 @@ extern "C" int forge_gptq_solve_cr(float *Wt, const float *U, const float *uinv,
 extern "C" int forge_gptq_solve_batched(const void *W, int w_dtype, int nb, int64_t R, int64_t C, const float *U,
                                         const float *udiag, const int32_t *u_map, const int32_t *perm, int nu,
                                         const float *scales, const float *qzeros, int gs, int bits, int sparse14,
-                                        int form, uint8_t *qweight, uint32_t *M, void *ws, int32_t *status,
-                                        void *stream) {
+                                        int form, const void *usplit, uint8_t *qweight, uint32_t *M, void *ws,
+                                        int32_t *status, void *stream) {
     FORGE_REQUIRE(W && U && scales && qzeros && qweight && ws, "null pointer");
+    FORGE_REQUIRE(!usplit || ((uintptr_t)usplit % 16 == 0 && C % 4 == 0 && R % 4 == 0),
+                  "usplit needs 16-byte alignment and R, C multiples of 4");
     FORGE_REQUIRE(nb > 0 && R > 0 && C > 0 && gs > 0 && bits >= 1 && bits <= 8, "bad sizes");
     FORGE_REQUIRE(!sparse14 || (udiag && M), "sparse14 needs udiag and M");
     FORGE_REQUIRE(w_dtype == FORGE_DTYPE_F32 || w_dtype == FORGE_DTYPE_BF16, "bad dtype");
@@ -870,6 +966,8 @@ extern "C" int forge_gptq_solve_batched(const void *W, int w_dtype, int nb, int6
     p.scales = scales; p.qzeros = qzeros; p.perm = perm; p.q = qt; p.M = M;
     p.R = R; p.C = C; p.G = cdiv(C, gs); p.gs = gs; p.maxq = (1 << bits) - 1; p.write_deq = 0; p.uvec_is_diag = 1;
     p.alt = form ? 1 : 0;
+    p.usplit = (const uint8_t *)usplit;
+    p.usplit_stride = usplit ? usplit_bytes_per_slot(C) : 0;
     if (p.alt && !use_tc_solver(p)) {
         set_error("forge_gptq_solve_batched: the inversion-free form needs R %% 4 == 0 and C %% 4 == 0");
         return FORGE_ERR_UNSUPPORTED;

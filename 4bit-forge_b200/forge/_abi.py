@@ -55,8 +55,10 @@ _PROTOS = {
     "forge_quant_grid_mse": (_c_int, [_ptr, _c_int, _c_i64, _c_i64, _c_int, _c_int, _c_int, _ptr, _c_int, _c_f32, _ptr, _ptr, _ptr]),
     "forge_solve_workspace_bytes": (_c_i64, [_c_int, _c_i64, _c_i64]),
     "forge_gptq_solve_cr": (_c_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_i64, _c_i64, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr]),
+    "forge_solve_split_u_bytes": (_c_i64, [_c_int, _c_i64]),
+    "forge_solve_split_u": (_c_int, [_ptr, _c_int, _c_i64, _ptr, _ptr]),
     "forge_gptq_solve_batched": (_c_int, [_ptr, _c_int, _c_int, _c_i64, _c_i64, _ptr, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr,
-                                          _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr]),
+                                          _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr]),
     "forge_dequantize": (_c_int, [_ptr, _ptr, _ptr, _c_i64, _c_i64, _c_int, _ptr, _c_int, _ptr]),
     "forge_pack_int4": (_c_int, [_ptr, _ptr, _c_i64, _c_i64, _c_int, _ptr, _ptr]),
     "forge_pack_sparse14": (_c_int, [_ptr, _ptr, _ptr, _c_i64, _c_i64, _ptr, _ptr]),

@@ -41,6 +41,7 @@ class MoEQuantConfig:
     overlap_streams: bool = True           # scale search on a second stream beside the (latency-bound) factorisation
     merge_gate_up: Optional[bool] = None   # gate and up in one solver launch (None: when the last wave would be thin)
     keep_codes: bool = True                # keep the unpacked uint8 codes in the result (tests, write-back)
+    presplit_factor: bool = True           # split each factor into tensor-core operand pieces once, for all row strips
 
 
 def swiglu_expert_forward(X, token_lists, offsets, Wg, Wu, out_rows, status=None):
@@ -61,6 +62,31 @@ class MoELayerQuantizer:
         self._h2d = None           # copy streams of quantize_experts_host
         self._d2h = None
         self._host_out = {}
+        self._arena = {}           # the large per-pass work buffers, kept across passes and steps
+
+    def _buf(self, name, nbytes, device):
+        """A named work buffer of at least nbytes (uint8), allocated once and reused by every pass and every step:
+        Hessians, factor copy, operand pieces and solver workspace are tens of GB that would otherwise go through
+        the caching allocator several times per step, on two streams.  Reuse is safe because each pass orders its
+        two streams explicitly (the factorisation's stream waits for the main one when it starts, and the main one
+        waits for it before the solve)."""
+        buf = self._arena.get(name)
+        if buf is None or buf.numel() < nbytes or buf.device != device:
+            self._arena.pop(name, None)
+            buf = None
+            buf = torch.empty(int(nbytes), dtype=torch.uint8, device=device)
+            self._arena[name] = buf
+        return buf[:int(nbytes)]
+
+    def _buf_f32(self, name, shape, device):
+        n = 1
+        for v in shape:
+            n *= int(v)
+        return self._buf(name, 4 * n, device).view(torch.float32).view(*shape)
+
+    def release_buffers(self):
+        """Drop the cached work buffers (they are re-created on the next call)."""
+        self._arena.clear()
 
     def _side_stream(self):
         if self._side is None:
@@ -95,7 +121,10 @@ class MoELayerQuantizer:
         groups = wz if separate else [wz[0]]
         for gi, wzero in enumerate(groups):
             last = gi == len(groups) - 1
-            A, _, _ = ops.hessian_gather_damp(H, perm32, pruned, wzero, invalid, cfg.rel_damp)
+            A = None
+            if form == 1 and len(groups) == 1:
+                A = self._buf_f32("factor", H.shape, H.device)
+            A, _, _ = ops.hessian_gather_damp(H, perm32, pruned, wzero, invalid, cfg.rel_damp, A=A)
             if form == 1:
                 # factor only: the solver works from the scaled reverse-Cholesky factor
                 U, udiag, info = ops.chol_factor(A)
@@ -108,11 +137,14 @@ class MoELayerQuantizer:
             outs = outs * len(Ws)
         return outs
 
-    def _solve_family(self, H, n_samples, Ws, names=(), gates=None, between=None, separate=False):
-        """Everything after the Hessian for the weight batches Ws that share it.  names[i]: input name to wait for
+    def _solve_family(self, Hbox, n_samples, Ws, names=(), gates=None, between=None, separate=False):
+        """Everything after the Hessian for the weight batches Ws that share it.  Hbox: one-element list holding the
+        Hessian batch; the list is emptied as soon as the factorisation is queued, so that the Hessians' memory is
+        free again during the solve (the inversion-free form factors a copy).  names[i]: input name to wait for
         (gates.need) before Ws[i] is touched.  between(): extra work for the main stream while the factorisation
         runs beside it (the expert forward)."""
         cfg = self.cfg
+        H = Hbox[0]
         sparse = cfg.algorithm == "sparsegptq"
         cand = None
         if cfg.quantization_scale == "mse":
@@ -154,6 +186,8 @@ class MoELayerQuantizer:
                 between()
             for t in [H, pruned, invalid] + ([perm32] if perm32 is not None else []) + list(Ws):
                 t.record_stream(side)
+            Hbox.clear()
+            del H
             main.wait_stream(side)
             for U, udiag, info in factors:
                 for t in (U, udiag, info):
@@ -161,12 +195,21 @@ class MoELayerQuantizer:
         else:
             wz = [ops.weight_zero_cols(W) for W in Ws]
             factors = self._factor(H, perm32, pruned, invalid, Ws, wz, form, separate)
+            Hbox.clear()
+            del H
             for W in Ws[len(grids):]:
                 grids.append(grid_of(W))
             if between is not None:
                 between()
         results = []
-        merged = self._solve_merged(Ws, factors, grids, perm32, form) if len(Ws) == 2 and not sparse else None
+        # tensor-core operand pieces of each distinct factor, split once for all row strips (and for gate and up)
+        splits = {}
+        for U, _, _ in factors:
+            if id(U) not in splits:
+                splits[id(U)] = (ops.solve_split_u(U, out=(lambda n, d=U.device: self._buf("pieces", n, d))
+                                                   if len(factors) == 1 or factors[0][0] is factors[-1][0] else None)
+                                 if cfg.presplit_factor else None)
+        merged = (self._solve_merged(Ws, factors, grids, perm32, form, splits) if len(Ws) == 2 and not sparse else None)
         for i, (W, (U, udiag, info), (scales, qzeros)) in enumerate(zip(Ws, factors, grids)):
             nb, R, C = W.shape
             if merged is not None:
@@ -174,7 +217,8 @@ class MoELayerQuantizer:
             else:
                 out = ops.gptq_solve_batched(W, U, scales, qzeros, cfg.group_size, cfg.bits, perm=perm32,
                                              udiag=udiag if sparse else None, sparse14=sparse, status=self._status,
-                                             form=form)
+                                             form=form, usplit=splits[id(U)],
+                                             ws=lambda n, d=W.device: self._buf("solve", n, d))
             q, M = out if sparse else (out, None)
             G = (C + cfg.group_size - 1) // cfg.group_size
             res = {"qweight": q, "scales": scales.view(nb, R, G), "qzeros": qzeros.view(nb, R, G), "info": info,
@@ -195,7 +239,7 @@ class MoELayerQuantizer:
         waves = nb * ((R + 127) // 128) / (3.0 * sm_count)
         return 0.0 < waves - int(waves) < 0.35
 
-    def _solve_merged(self, Ws, factors, grids, perm32, form):
+    def _solve_merged(self, Ws, factors, grids, perm32, form, splits):
         """Two weight batches that share one factor (gate and up) in ONE solver launch.  Same arithmetic per
         matrix, so the codes are identical to two launches; only the launch shape differs.
         Returns the codes [2 nb, R, C] or None (not worth it / not applicable)."""
@@ -215,7 +259,8 @@ class MoELayerQuantizer:
         qzeros = torch.cat([grids[0][1], grids[1][1]])
         u_map = torch.arange(nb, dtype=torch.int32, device=W.device).repeat(2)
         return ops.gptq_solve_batched(W, U0, scales, qzeros, cfg.group_size, cfg.bits, perm=perm32, u_map=u_map,
-                                      status=self._status, form=form)
+                                      status=self._status, form=form, usplit=splits[id(U0)],
+                                      ws=lambda n, d=W.device: self._buf("solve", n, d))
 
     def _pack(self, q, scales, qzeros, M):
         cfg = self.cfg
@@ -281,7 +326,7 @@ class MoELayerQuantizer:
         """Layer-input Hessians of all local slots, accumulated over the row chunks of X as they arrive."""
         T, Hd = X.shape
         n_local = n_routed + dense_tail
-        H1 = torch.empty((n_local, Hd, Hd), dtype=torch.float32, device=X.device)
+        H1 = self._buf_f32("hessian", (n_local, Hd, Hd), X.device)
         n_prev = torch.zeros(n_local, dtype=torch.int64, device=X.device)
         t0 = 0
         for t1, wait in x_chunks:
@@ -330,7 +375,7 @@ class MoELayerQuantizer:
             if H1_all is not None:
                 H1, H1_all = H1_all, None
             else:
-                H1 = torch.empty((nb, Hd, Hd), dtype=torch.float32, device=dev)
+                H1 = self._buf_f32("hessian", (nb, Hd, Hd), dev)
                 ops.hessian_grouped(X, Hd, lists, offs, H1, mirror=True, status=status)
 
             def forward():
@@ -340,14 +385,16 @@ class MoELayerQuantizer:
                 if act is None:
                     act = swiglu_expert_forward(X, lists, offsets, Wg, Wu, act_rows, status=status)
 
-            g, u = self._solve_family(H1, n_samples, [Wg[c0:c1], Wu[c0:c1]], ("gate", "up"), _gates, forward, separate)
+            Hbox = [H1]
             del H1
+            g, u = self._solve_family(Hbox, n_samples, [Wg[c0:c1], Wu[c0:c1]], ("gate", "up"), _gates, forward, separate)
             if _gates is not None:
                 _gates.done({"gate": g, "up": u}, c0, n_local)
-            H2 = torch.empty((nb, I, I), dtype=torch.float32, device=dev)
+            H2 = self._buf_f32("hessian", (nb, I, I), dev)
             ops.hessian_grouped(act, I, None, offs, H2, mirror=True, status=status)
-            (d,) = self._solve_family(H2, n_samples, [Wd[c0:c1]], ("down",), _gates)
+            Hbox = [H2]
             del H2
+            (d,) = self._solve_family(Hbox, n_samples, [Wd[c0:c1]], ("down",), _gates)
             if _gates is not None:
                 _gates.done({"down": d}, c0, n_local)
             res["gate"].append(g)
@@ -489,20 +536,20 @@ class MoELayerQuantizer:
 
         arrived = set()
 
-        class Gates:
-            def need(self, name):
-                if name in arrived:
-                    return
-                arrived.add(name)
-                torch.cuda.current_stream().wait_event(events[name])
-                materialise((("gate", "up", "down").index(name),))
+        def need(name):
+            if name in arrived:
+                return
+            arrived.add(name)
+            torch.cuda.current_stream().wait_event(events[name])
+            materialise((("gate", "up", "down").index(name),))
 
-            def done(self, results, c0, n_total):
-                for nm, r in results.items():
-                    ship(nm, r, c0, n_total)
+        def done(results, c0, n_total):
+            for nm, r in results.items():
+                ship(nm, r, c0, n_total)
 
+        gates = _Gates(need, done)
         main.wait_event(events["x"])
-        out = self._quantize_experts(Xd, idd, Wg, Wu, Wd, e_begin, dense_tail, Gates(), separate=False)
+        out = self._quantize_experts(Xd, idd, Wg, Wu, Wd, e_begin, dense_tail, gates, separate=False)
 
         def redo():
             # gate and up disagree on their all-zero columns: same layer again with one factor per matrix
@@ -514,7 +561,17 @@ class MoELayerQuantizer:
 
         out = self._finish(out, redo)
         d2h.synchronize()
+        gates.need = gates.done = None      # the closures hold this call's device buffers: drop them now
         return out, host
+
+
+class _Gates:
+    """need(name) / done(results, c0, n) callbacks of quantize_experts_host.  A module-level class on purpose: a class
+    defined inside the call would be a reference cycle, and the tens of GB of device buffers its closures reach
+    would stay allocated until Python's cycle collector happens to run."""
+
+    def __init__(self, need, done):
+        self.need, self.done = need, done
 
 
 def _cat_results(parts):

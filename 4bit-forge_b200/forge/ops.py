@@ -228,8 +228,21 @@ def gptq_solve_cr(Wt, U, scales_el, qzeros_el, bits: int, uinv=None, status=None
     return (q, M) if sparse else q
 
 
+def solve_split_u(U: torch.Tensor, out=None):
+    """Tensor-core operand pieces of U [nu,C,C] for gptq_solve_batched(usplit=...) (forge_solve_split_u); None when
+    the shape does not take the tensor-core path (C not a multiple of 4).  out: callable nbytes -> uint8 buffer, or
+    None (a fresh tensor)."""
+    nu, C, _ = U.shape
+    nbytes = query("forge_solve_split_u_bytes", nu, C)
+    if nbytes == 0:
+        return None
+    out = torch.empty(nbytes, dtype=torch.uint8, device=_dev(U)) if out is None else out(nbytes)
+    call("forge_solve_split_u", ptr(U), nu, C, ptr(out), stream_ptr())
+    return out
+
+
 def gptq_solve_batched(W, U, scales, qzeros, gs: int, bits: int, perm=None, u_map=None, udiag=None,
-                       sparse14: bool = False, ws=None, status=None, form: int = 0):
+                       sparse14: bool = False, ws=None, status=None, form: int = 0, usplit=None):
     """W [nb,R,C] original order; U [nu,C,C]; scales/qzeros [nb*R*G] -> qweight [nb,R,C] (+ M [nb,G32,R])."""
     nb, R, C = W.shape
     dev = _dev(W)
@@ -238,8 +251,11 @@ def gptq_solve_batched(W, U, scales, qzeros, gs: int, bits: int, perm=None, u_ma
     M = torch.zeros((nb, (C + 31) // 32, R), dtype=torch.int32, device=dev) if sparse14 else None
     if ws is None:
         ws = torch.empty(query("forge_solve_workspace_bytes", nb, R, C), dtype=torch.uint8, device=dev)
+    elif callable(ws):
+        ws = ws(query("forge_solve_workspace_bytes", nb, R, C))
     call("forge_gptq_solve_batched", ptr(W), dtype_code(W), nb, R, C, ptr(U), ptr(udiag), ptr(u_map), ptr(perm), nu,
-         ptr(scales), ptr(qzeros), gs, bits, int(sparse14), int(form), ptr(q), ptr(M), ptr(ws), ptr(status), stream_ptr())
+         ptr(scales), ptr(qzeros), gs, bits, int(sparse14), int(form), ptr(usplit if (R % 4 == 0 and C % 4 == 0) else None),
+         ptr(q), ptr(M), ptr(ws), ptr(status), stream_ptr())
     return (q, M) if sparse14 else q
 
 

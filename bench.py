@@ -12,6 +12,10 @@ Rank 0 prints one JSON line.  `--impl reference` times the CPU restatement of th
 import argparse
 import json
 import os
+
+# the layer is processed in passes of a few tens of GB whose buffers come and go on two streams: growable segments
+# keep the caching allocator from stranding that memory in fixed-size blocks
+os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
 import subprocess
 import sys
 import threading
@@ -253,11 +257,11 @@ class PhaseTimer:
 
 
 def pick_expert_chunk(n_local, Hd, I, free_bytes, sparse):
-    """Experts factorised / solved per pass so that the per-pass working set fits the free memory: two fp32 [Hd,Hd]
-    matrices (Hessian and its factor copy; a third for the triangular inverse of the sparse path) plus the solver's
-    work buffers of the gate and up batches (fp32 transposed weights + codes)."""
-    per_expert = (3 if sparse else 2) * Hd * Hd * 4 + 2 * I * Hd * 5 + (1 << 20)
-    fit = max(1, int(0.55 * free_bytes // per_expert))
+    """Experts factorised / solved per pass so that the per-pass working set fits the free memory: three fp32 [Hd,Hd]
+    matrices (Hessian, its factor copy, the factor's tensor-core operand pieces) plus the solver's work buffers of
+    a weight batch (fp32 transposed weights + codes)."""
+    per_expert = 3 * Hd * Hd * 4 + I * Hd * 8 + (1 << 20)
+    fit = max(1, int(0.5 * free_bytes // per_expert))
     if fit >= n_local:
         return 0
     passes = -(-n_local // fit)
@@ -423,6 +427,13 @@ def run_ours(args, rank, world, local_rank):
         per_step = max_over_ranks([evs[i].elapsed_time(evs[i + 1]) for i in range(steps)])
         return total, per_step
 
+    def mem(tag):
+        if os.environ.get("BENCH_DEBUG_MEM"):
+            print(f"[mem] {tag}: allocated {torch.cuda.memory_allocated() / 2**30:.1f} GiB, peak "
+                  f"{torch.cuda.max_memory_allocated() / 2**30:.1f} GiB, reserved "
+                  f"{torch.cuda.memory_reserved() / 2**30:.1f} GiB, chunk {chunk}", file=sys.stderr, flush=True)
+
+    mem("inputs ready")
     # ---- device-resident timing
     for _ in range(max(args.warmup, 1)):
         out, _ = step()     # every step checks the status word (quantize_experts raises on a non-zero status)
@@ -440,6 +451,7 @@ def run_ours(args, rank, world, local_rank):
     # ---- per-entry-point device time of one more step (rank 0's slice) and the roofline of the top kernel
     # (streams not overlapped in this one step, so that every entry point's events bracket its own kernels only)
     qz_serial = moe.MoELayerQuantizer(moe.MoEQuantConfig(**{**cfg.__dict__, "overlap_streams": False}))
+    qz_serial._arena = qz._arena        # the same work buffers: a second set would not fit beside the first
     pt = PhaseTimer()
     pt.install()
     pt.enabled = True
@@ -449,6 +461,7 @@ def run_ours(args, rank, world, local_rank):
     counts = out["counts"].cpu().double()
     del out
     barrier()
+    mem("after the device-resident phases")
 
     # ---- end to end: host buffers in, packed results out (pinned memory, copies inside the timed region).
     # The call a user makes: MoELayerQuantizer.quantize_experts_host — weights (fp8 + block scales where the
@@ -468,6 +481,7 @@ def run_ours(args, rank, world, local_rank):
         del Wg, Wu, Wd
         fp8 = None
         torch.cuda.empty_cache()
+        mem("device-resident weights freed")
         bytes_in = sum(w.numel() * w.element_size() for w in hW) + sum(t.numel() * 4 for t in (hS or []))
         if rank == 0:
             bytes_in += hX.numel() * 2 + hlog.numel() * 4

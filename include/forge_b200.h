@@ -228,11 +228,17 @@ int forge_gptq_solve_cr(float *Wt, const float *U, const float *uinv, const floa
  * (forge_chol_inv_upper_batched) and the column errors x - deq are propagated, as in the reference;
  * form = 1: U is the output of forge_chol_factor_batched and w - deq is propagated (same recurrence without
  * the triangular inverse; needs R % 4 == 0 and C % 4 == 0).  Replaces the glue of GPTQ.quantize/_solver,
- * forge/gptq.py:129-139,231-276, together with the two solvers above. */
+ * forge/gptq.py:129-139,231-276, together with the two solvers above.
+ * usplit (may be NULL): the tensor-core operand pieces of U prepared once per Hessian slot by forge_solve_split_u
+ * (forge_solve_split_u_bytes(nu, C) bytes).  With it the solver's row strips fetch U with bulk copies instead of each
+ * re-splitting the same rows; gate and up of an expert, which share U, share the pieces too.  Needs R, C % 4 == 0. */
+int64_t forge_solve_split_u_bytes(int nu, int64_t C);
+int forge_solve_split_u(const float *U, int nu, int64_t C, void *usplit, void *stream);
 int forge_gptq_solve_batched(const void *W, int w_dtype, int nb, int64_t R, int64_t C, const float *U,
                              const float *udiag, const int32_t *u_map, const int32_t *perm, int nu,
                              const float *scales, const float *qzeros, int gs, int bits, int sparse14,
-                             int form, uint8_t *qweight, uint32_t *M, void *ws, int32_t *status, void *stream);
+                             int form, const void *usplit, uint8_t *qweight, uint32_t *M, void *ws, int32_t *status,
+                             void *stream);
 
 /* ---- checkpoint weight materialisation on the device (callers of the path) -----
  * Packed int4 ("pack-quantized", e.g. Kimi-K2): packed int32 [O, I/8] + scales fp32 [O, I/gs] -> dense [O, I]

@@ -335,3 +335,30 @@ def test_bounds_checks_skip_bad_claims_and_report_them():
     ops.expert_swiglu_grouped(X, tl, offsets, Wg, Wg, 210, out=out, status=status)
     assert int(status.item()) == _abi.ERR_INVALID
     assert bool((out[100:].float() == 3.0).all())
+
+
+@pytest.mark.parametrize("nb,R,C,sparse", [(3, 256, 640, False), (40, 1024, 256, False), (3, 128, 384, True)])
+def test_presplit_factor_pieces_give_identical_codes(nb, R, C, sparse):
+    """forge_solve_split_u + bulk copies of the operand pieces against the solver splitting U itself: the same values
+    reach the same MMAs in the same order, so the codes are identical.  (3 x 2 strips: the deep ring; 40 x 8 strips:
+    the shallow ring, three CTAs per SM.)"""
+    from forge import ops
+    from helpers import random_spd
+    g = torch.Generator().manual_seed(nb + C)
+    W = (torch.randn(nb, R, C, generator=g) * 0.02).to(torch.bfloat16).to(DEV)
+    nu = min(nb, 3)
+    H = torch.stack([random_spd(C, 10 + i) for i in range(nu)]).to(DEV)
+    A, _, _ = ops.hessian_gather_damp(H, None, None, None, None, 0.01)
+    U, udiag, info = ops.chol_inv_upper(A, zero_lower=False) if sparse else ops.chol_factor(A)
+    assert int(info.abs().sum()) == 0
+    u_map = (torch.arange(nb, dtype=torch.int32) % nu).to(DEV)
+    s, z = ops.quant_grid(W.view(nb * R, C), 128, 4, True)
+    kw = dict(perm=None, u_map=u_map, udiag=udiag if sparse else None, sparse14=sparse, form=0 if sparse else 1)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    a = ops.gptq_solve_batched(W, U, s, z, 128, 4, status=status, **kw)
+    b = ops.gptq_solve_batched(W, U, s, z, 128, 4, status=status, usplit=ops.solve_split_u(U), **kw)
+    assert int(status.item()) == 0
+    if sparse:
+        assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+    else:
+        assert torch.equal(a, b)
