@@ -146,19 +146,20 @@ __global__ void __launch_bounds__(kThreads, 1) expert_swiglu_tc_kernel(const Fwd
             for (int64_t t = ((int64_t)blockIdx.x - base % grid + grid) % grid; t < tb && ok; t += grid) {
                 const int64_t m0 = (t / P.ntn) * kMT, n0 = (t % P.ntn) * kNT;
                 const __nv_bfloat16 *arow[8];
+                int64_t tokv[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {     // all loads first, the checks after: eight latencies overlap
+                    const int64_t kidx = m0 + rbase + 16 * i;
+                    tokv[i] = (kidx < n) ? (tl ? (int64_t)tl[kidx] : off + kidx) : INT64_MIN;
+                }
+                bool bad_token = false;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    const int64_t kidx = m0 + rbase + 16 * i;
-                    int64_t tok = -1;
-                    if (kidx < n) {
-                        tok = tl ? (int64_t)tl[kidx] : off + kidx;
-                        if (tok < 0 || tok >= P.n_rows) {   // not a row of X: contributes zeros
-                            if (P.status) atomicExch(P.status, FORGE_ERR_INVALID);
-                            tok = -1;
-                        }
-                    }
-                    arow[i] = tok >= 0 ? P.X + tok * P.ldx + chunk * 8 : nullptr;
+                    const bool valid = tokv[i] >= 0 && tokv[i] < P.n_rows;   // else: not a row of X, contributes zeros
+                    bad_token |= (!valid && tokv[i] != INT64_MIN);
+                    arow[i] = valid ? P.X + tokv[i] * P.ldx + chunk * 8 : nullptr;
                 }
+                if (bad_token && P.status) atomicExch(P.status, FORGE_ERR_INVALID);
                 for (int kt = 0; kt < nkt && ok; ++kt) {
                     const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
                     ok = mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag);

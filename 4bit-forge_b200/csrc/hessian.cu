@@ -28,6 +28,7 @@ using namespace forge::tc;
 
 namespace {
 
+constexpr int32_t kNoRow = INT32_MIN;         // padding slot of a k-tile (past the end of the token list)
 constexpr int kTile = 256;                    // output tile edge (channels)
 constexpr int kKT = 64;                       // tokens per k-tile
 constexpr int kSubBytes = kKT * 128;          // one 64-channel x 64-token sub-tile: 8 KB
@@ -146,6 +147,8 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_tc_kernel(const HessParam
             const int nkt = (int)((n + kKT - 1) / kKT);
             const int32_t *tl = P.token_idx ? P.token_idx + off : nullptr;
             bool ok = true;
+            bool bad_token = false;
+            const uint32_t n_rows_u = (uint32_t)P.n_rows;
             // Token indices of the k-tile about to be issued; the ones of the NEXT k-tile are loaded right after
             // this tile's copies are issued, so that their latency never sits between two stages.
             int32_t tok_cur[4], tok_nxt[4];
@@ -153,14 +156,9 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_tc_kernel(const HessParam
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int64_t kidx = (int64_t)kt * kKT + warp * 16 + i * 4 + rsub;
-                    int32_t t = -1;
-                    if (kidx < n) {
-                        t = tl ? tl[kidx] : (int32_t)(off + kidx);
-                        if ((int64_t)t < 0 || (int64_t)t >= P.n_rows) {  // not a row of X: contributes zeros
-                            if (P.status) atomicExch(P.status, FORGE_ERR_INVALID);
-                            t = -1;
-                        }
-                    }
+                    // no check here: the value is first looked at one k-tile later, so the load's latency stays hidden
+                    int32_t t = kNoRow;
+                    if (kidx < n) t = tl ? tl[kidx] : (int32_t)(off + kidx);
                     dst[i] = t;
                 }
             };
@@ -175,7 +173,9 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_tc_kernel(const HessParam
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int row = warp * 16 + i * 4 + rsub;  // token row inside the k-tile
-                    const bool rvalid = tok_cur[i] >= 0;
+                    // a list entry that is not a row of X contributes zeros (and is reported once per tile)
+                    const bool rvalid = (uint32_t)tok_cur[i] < n_rows_u;
+                    bad_token |= (!rvalid && tok_cur[i] != kNoRow);
                     const __nv_bfloat16 *xrow = P.X + (int64_t)(rvalid ? tok_cur[i] : 0) * P.ldx;
                     const uint32_t drow = (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4));
 #pragma unroll
@@ -206,6 +206,7 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_tc_kernel(const HessParam
                 mbar_arrive(bar_full + 8 * ((it - pend) % kStages));
                 --pend;
             }
+            if (bad_token && P.status) atomicExch(P.status, FORGE_ERR_INVALID);
             if (!ok) break;
             // ---- epilogue: TMEM -> registers -> global
             ok = mbar_wait(bar_acc_full, tile_iter & 1u, abort_flag);
