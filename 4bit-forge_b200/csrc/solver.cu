@@ -36,6 +36,8 @@ using forge::tc::idesc_tf32;
 using forge::tc::make_desc_tf32;
 using forge::tc::piece_offset;
 using forge::tc::umma_tf32;
+using forge::tc::umma_tf32_ts;
+using forge::tc::idesc_tf32_ts;
 using forge::tc::tf32_round;
 using forge::tc::split4;
 
@@ -60,6 +62,8 @@ struct SolveParams {
     int64_t R, C, G;
     int gs, maxq, write_deq, uvec_is_diag;
     int alt;               // 1: U holds -Vt (inversion-free form) and the propagated quantity is w - deq
+    int meta_t;            // MODE 0: the tables are transposed, [nb][G][R] (a column's 128 rows are contiguous)
+    int gs_shift;          // log2(gs) when gs is a power of two, else -1
     const uint8_t *usplit; // [nu] pre-split hi/lo operand pieces of U (forge_solve_split_u), or null
     int64_t usplit_stride; // bytes per Hessian slot
 };
@@ -139,8 +143,9 @@ __device__ __forceinline__ void load_meta(const SolveParams &p, int b, int u, in
     if (!active || c >= p.C) return;
     int64_t gi;
     if (MODE == 0) {
-        const int64_t oc = p.perm ? (int64_t)p.perm[(int64_t)u * p.C + c] : c;
-        gi = ((int64_t)b * p.R + r) * p.G + oc / p.gs;
+        const uint32_t oc = p.perm ? (uint32_t)p.perm[(int64_t)u * p.C + c] : (uint32_t)c;
+        const int64_t g = p.gs_shift >= 0 ? (int64_t)(oc >> p.gs_shift) : (int64_t)(oc / (uint32_t)p.gs);
+        gi = p.meta_t ? ((int64_t)b * p.G + g) * p.R + r : ((int64_t)b * p.R + r) * p.G + g;
     } else {
         gi = ((int64_t)b * p.C + c) * p.R + r;
     }
@@ -360,10 +365,26 @@ constexpr int kUsubFloats = kSub * kUsubLd;
 constexpr int kTcRawFull = 2, kTcRawDeep = 6;
 // one raw k-step: [E row jA, E row jA+4 (, U row jA, U row jA+4)][128 threads][16 B]; U only when it is not pre-split
 constexpr int tc_raw_bytes(bool tmau) { return (tmau ? 2 : 4) * 128 * 16; }
-constexpr size_t tc_smem_bytes(int stages, int raw, bool tmau) {
-    return (size_t)stages * kTcStageBytes + 1024 + 2 * kUsubFloats * sizeof(float) + kSub * kBlk * sizeof(float) +
-           kBlk * sizeof(float) + 256 + (size_t)raw * tc_raw_bytes(tmau);
+constexpr size_t tc_smem_bytes(int stages, int raw, bool tmau, bool tmema = false) {
+    return (size_t)stages * (tmema ? 4 * 2 * kPieceBytes : kTcStageBytes) + 1024 + 2 * kUsubFloats * sizeof(float) +
+           kSub * kBlk * sizeof(float) + kBlk * sizeof(float) + 512 +
+           (tmema ? (size_t)kSub * kBlk * 5 : (size_t)raw * tc_raw_bytes(tmau));   // TMEMA: staged (scale, zero) pairs
 }
+// TMEMA build: the error operand of the MMAs lives in tensor memory.  A row thread owns one TMEM lane, so it can put
+// its own row's eight errors of a k-step (hi and lo parts, 16 columns) there with one tcgen05.st, straight from the
+// registers that loaded or produced them: no shared-memory staging of the errors at all (the shared-memory pipe,
+// not the tensor pipe, is what bounds the build that stages both operands).  Columns [0,128) hold the accumulator,
+// [128, 128 + 16 stages) the error stages.
+// A sixth warp does nothing but bring the [Uhi | Ulo] pairs in, as far ahead as the ring allows and independently of
+// the row threads: a row thread that is waiting for its error rows from HBM must not hold back the requests for U.
+// A stage of this build is FOUR k-steps (32 error rows: 64 TMEM columns, four pairs = 32 KB of U, twelve MMAs): the
+// hand-over between the row threads, the loader and the MMA warp (two barrier waits, fences, one commit) costs
+// several hundred cycles whatever it carries, more than the three MMAs of a single k-step take.
+constexpr int kTmemaStages = 2;
+constexpr int kTmemaKPerStage = 4;
+constexpr uint32_t kTmemaCols = 256;
+constexpr int kTmemaThreads = 192;
+constexpr int kPrefetchGroups = 4;   // error rows are requested into L2 this many 32-row groups ahead of their use
 // Pre-split U: for column block cb (128 columns) the k-steps ks = 0 .. 16 (cb + 1) - 1 (8 rows of U each: every row
 // above the block, then the block's own rows for the near updates), one [hi piece | lo piece] pair of 8 KB per
 // k-step, k-steps of a block contiguous, blocks in order: pair index = 8 cb (cb + 1) + ks.
@@ -375,28 +396,65 @@ __host__ __device__ inline int64_t usplit_bytes_per_slot(int64_t C) {
 }
 
 __device__ __forceinline__ void rows_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// A load the compiler must issue where it is written (volatile asm keeps its place among the barrier waits): the far
+// phase asks for the next group of error rows BEFORE it works on the current one; left to the scheduler, the loads
+// sink to their first use and every group pays a full HBM latency.
+// The error rows stream through once per column block and are gone from L2 long before the next block wants them:
+// no L1 allocation, first to be evicted from L2 (policy from l2_policy_evict_first).
+__device__ __forceinline__ float ldg_here(const float *p, uint64_t policy) {
+    float v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.f32 %0, [%1], %2;" : "=f"(v) : "l"(p), "l"(policy));
+    return v;
+}
 
-template <int MODE, bool SPARSE, int kTcRaw, int kTcStages, bool TMAU>
-__global__ void __launch_bounds__(kTcThreads, (kTcStages > 2 ? 2 : 3)) solve_tc_kernel(const SolveParams p, int32_t *status) {
+// Cycle accounting of one CTA of the tensor-memory build (-DFORGE_SOLVER_PROFILE only; never in the shipped library):
+// where the row threads, the MMA warp and the U loader spend their time.  Read back with forge_debug_solver_profile.
+#ifdef FORGE_SOLVER_PROFILE
+__device__ unsigned long long g_prof[32];
+__device__ int g_prof_dbg;   // bit 0: skip the Elo*Uhi MMA, bit 1: skip the Ehi*Ulo MMA, bit 2: N = 64 (timing experiments)
+#define PROF_T0() const long long _pt0 = clock64()
+#define PROF_ADD(slot) do { pacc[slot] += (unsigned long long)(clock64() - _pt0); } while (0)
+#else
+#define PROF_T0() do {} while (0)
+#define PROF_ADD(slot) do {} while (0)
+#endif
+
+template <int MODE, bool SPARSE, int kTcRaw, int kTcStages, bool TMAU, bool TMEMA = false>
+__global__ void __launch_bounds__(TMEMA ? kTmemaThreads : kTcThreads, ((TMEMA || kTcStages > 2) ? 2 : 3))
+solve_tc_kernel(const SolveParams p, int32_t *status) {
     using namespace forge::tc;
+    static_assert(!TMEMA || TMAU, "the tensor-memory build takes U from the pre-split pieces");
+    static_assert(kTcStages <= 8, "eight barriers per kind");
     extern __shared__ uint8_t smem_raw[];
     constexpr int kTcRawBytes = tc_raw_bytes(TMAU);
+    constexpr int kStageStride = TMEMA ? kTmemaKPerStage * kPairBytes : kTcStageBytes;   // TMEMA: four [Uhi | Ulo] pairs
+    constexpr int kUoff = TMEMA ? 0 : 2 * kPieceBytes;
+    constexpr uint32_t kTmemCols = TMEMA ? kTmemaCols : 128u;
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *ring = smem_raw + (smem_base - smem_u32(smem_raw));
-    float *Usub = reinterpret_cast<float *>(ring + kTcStages * kTcStageBytes);  // [2][32][32]
+    float *Usub = reinterpret_cast<float *>(ring + kTcStages * kStageStride);  // [2][32][32]
     float *es = Usub + 2 * kUsubFloats;                                          // [32][128] errors of a sub-block
     float *uinv_s = es + kSub * kBlk;                                            // [128]
-    uint64_t *bars = reinterpret_cast<uint64_t *>(uinv_s + kBlk);                // full[<=4], empty[<=4] at +4, acc at +8
-    uint8_t *raw = reinterpret_cast<uint8_t *>(bars) + 256;                      // [kTcRaw][8 KB]
-    uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + 9);
+    // barriers: full[<=8] (operands staged by the row threads), empty[<=8] at +8, acc at +16, full_u[<=8] at +24
+    // (TMEMA: the bulk copies of U, tracked apart from the rows' arrivals)
+    uint64_t *bars = reinterpret_cast<uint64_t *>(uinv_s + kBlk);
+    uint8_t *raw = reinterpret_cast<uint8_t *>(bars) + 512;                      // [kTcRaw][8 KB]
+    // TMEMA (no raw ring): the scale and the zero point of the 32 columns of a sub-block for this CTA's rows, staged
+    // before the column chain; each thread writes and reads its own column of the two arrays
+    float *meta_s = reinterpret_cast<float *>(raw);                              // [32][128]
+    uint8_t *meta_z = raw + kSub * kBlk * sizeof(float);                          // [32][128], zero points are integers
+    uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + 40);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
-    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + 4), bar_acc = smem_u32(bars + 8);
+    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + 8), bar_acc = smem_u32(bars + 16);
+    const uint32_t bar_full_u = smem_u32(bars + 24);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
         for (int s = 0; s < kTcStages; ++s) {
-            mbar_init(bar_full + 8 * s, kBlk + (TMAU ? 1 : 0));   // + the thread that announces the bulk copy of U
+            // TMAU without TMEMA: + the row thread that announces the bulk copy of U
+            mbar_init(bar_full + 8 * s, kBlk + ((TMAU && !TMEMA) ? 1 : 0));
             mbar_init(bar_empty + 8 * s, 1);
+            if (TMEMA) mbar_init(bar_full_u + 8 * s, 1);
         }
         mbar_init(bar_acc, 1);
         *abort_flag = 0;
@@ -404,7 +462,7 @@ __global__ void __launch_bounds__(kTcThreads, (kTcStages > 2 ? 2 : 3)) solve_tc_
     }
     if (warp == 4) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
-                     "r"(128u)
+                     "r"(kTmemCols)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -412,6 +470,14 @@ __global__ void __launch_bounds__(kTcThreads, (kTcStages > 2 ? 2 : 3)) solve_tc_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_holder;
+    const uint32_t tmem_e = tmem_base + 128u;      // TMEMA: error stages of 4 k-steps x 16 columns (hi 8, lo 8)
+#ifdef FORGE_SOLVER_PROFILE
+    const bool prof_on = TMEMA && blockIdx.x == 3 && blockIdx.y == 5 && (threadIdx.x & 31) == 0 &&
+                         ((threadIdx.x >> 5) == 0 || (threadIdx.x >> 5) >= 4);
+    const long long prof_start = clock64();
+    unsigned long long pacc[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+    const int prof_dbg = g_prof_dbg;
+#endif
 
     const int b = blockIdx.y;
     const int u = p.u_map ? p.u_map[b] : b;
@@ -439,7 +505,69 @@ __global__ void __launch_bounds__(kTcThreads, (kTcStages > 2 ? 2 : 3)) solve_tc_
         for (int64_t bs = 0; bs < C; bs += kBlk) {
             const bool u_ok = (bs + 4 * c4) < C;
             // ---------------- far phase: every column before the block ----------------
-            if (bs > 0 && ok) {
+            if (TMEMA && bs > 0 && ok) {
+#ifdef FORGE_SOLVER_PROFILE
+                const long long _pfar0 = clock64();
+#endif
+                // Far phase, errors through tensor memory.  A thread reads its own row's errors straight from global
+                // memory (a warp's 32 rows are one 128-byte line per error row), 32 error rows = 4 k-steps at a time,
+                // the next group in flight while this one is split and stored.
+                const int ngroups = (int)(bs / 32);
+                const uint64_t stream_pol = forge::tc::l2_policy_evict_first();
+                const float *srcE = E + r;
+                float cur[32], nxt[32];
+                // this warp's 32 rows are one 128-byte line per error row: lane i asks for error row i of a group
+                const float *pfE = E + r0 + warp * 32 + (int64_t)lane * R;
+                for (int g = 0; g < kPrefetchGroups && g < ngroups; ++g)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(pfE + (int64_t)g * 32 * R));
+#pragma unroll
+                for (int i = 0; i < 32; ++i) cur[i] = active ? ldg_here(srcE + (int64_t)i * R, stream_pol) : 0.0f;
+#pragma unroll 1
+                for (int g = 0; g < ngroups && ok; ++g) {
+                    if (g + kPrefetchGroups < ngroups)
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(pfE + (int64_t)(g + kPrefetchGroups) * 32 * R));
+                    if (g + 1 < ngroups) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            nxt[i] = active ? ldg_here(srcE + ((int64_t)(g + 1) * 32 + i) * R, stream_pol) : 0.0f;
+                    }
+                    {
+                        const uint32_t s = it % kTcStages, ph = (it / kTcStages) & 1u;
+                        {
+                            PROF_T0();
+                            ok = mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag);
+                            PROF_ADD(1);
+                        }
+                        ok = __all_sync(0xffffffffu, ok);   // tcgen05.st is warp-aligned: the whole warp goes or none
+                        if (!ok) break;
+                        tc_fence_after();
+                        PROF_T0();
+#pragma unroll
+                        for (int k = 0; k < kTmemaKPerStage; ++k) {
+                            uint32_t v16[16];
+#pragma unroll
+                            for (int jj = 0; jj < 8; ++jj) {
+                                const float v = cur[8 * k + jj];
+                                const float hi = tf32_round(v);
+                                v16[jj] = __float_as_uint(hi);
+                                v16[8 + jj] = __float_as_uint(tf32_round(__fsub_rn(v, hi)));
+                            }
+                            tmem_st16(tmem_e + ((uint32_t)(warp * 32) << 16) + s * 64u + (uint32_t)k * 16u, v16);
+                        }
+                        tmem_st_wait();
+                        tc_fence_before();
+                        mbar_arrive(bar_full + 8 * s);
+                        PROF_ADD(2);
+                        ++it;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) cur[i] = nxt[i];
+                }
+#ifdef FORGE_SOLVER_PROFILE
+                pacc[0] += (unsigned long long)(clock64() - _pfar0);
+#endif
+            }
+            if (!TMEMA && bs > 0 && ok) {
                 // operands travel global -> raw ring (cp.async, kTcRaw k-steps ahead, no registers held) -> hi/lo split
                 // -> operand stage; a thread reads back only the 16-byte chunks it copied itself (no barrier needed).
                 // TMAU: only the errors go that way; the U pieces were split once for all row strips
@@ -515,6 +643,9 @@ __global__ void __launch_bounds__(kTcThreads, (kTcStages > 2 ? 2 : 3)) solve_tc_
             // ---------------- the four sub-blocks ----------------
 #pragma unroll 1
             for (int sb = 0; sb < 4; ++sb) {
+#ifdef FORGE_SOLVER_PROFILE
+                const long long _pnr0 = clock64();
+#endif
                 const int64_t cs = bs + (int64_t)sb * kSub;
                 float *us = Usub + (sb & 1) * kUsubFloats;
                 // (1) the strict upper triangle of U[cs.., cs..] for the in-register part, row t stored from its
@@ -529,7 +660,32 @@ __global__ void __launch_bounds__(kTcThreads, (kTcStages > 2 ? 2 : 3)) solve_tc_
                 }
                 cp_async_commit();
                 // (2) near update: the previous sub-block's errors go to the later columns of the block
-                if (sb > 0 && ok) {
+                if (TMEMA && sb > 0 && ok) {
+                    // near update, errors of the previous sub-block from this thread's own column of the scratch: one stage
+                    const uint32_t s = it % kTcStages, ph = (it / kTcStages) & 1u;
+                    ok = mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (ok) {
+                        tc_fence_after();
+#pragma unroll
+                        for (int i = 0; i < kTmemaKPerStage; ++i) {
+                            uint32_t v16[16];
+#pragma unroll
+                            for (int jj = 0; jj < 8; ++jj) {
+                                const float v = es[(i * kKS + jj) * kBlk + tid];
+                                const float hi = tf32_round(v);
+                                v16[jj] = __float_as_uint(hi);
+                                v16[8 + jj] = __float_as_uint(tf32_round(__fsub_rn(v, hi)));
+                            }
+                            tmem_st16(tmem_e + ((uint32_t)(warp * 32) << 16) + s * 64u + (uint32_t)i * 16u, v16);
+                        }
+                        tmem_st_wait();
+                        tc_fence_before();
+                        mbar_arrive(bar_full + 8 * s);
+                        ++it;
+                    }
+                }
+                if (!TMEMA && sb > 0 && ok) {
                     float4 nu[4][2];
                     if (!TMAU) {
 #pragma unroll
@@ -580,6 +736,57 @@ __global__ void __launch_bounds__(kTcThreads, (kTcStages > 2 ? 2 : 3)) solve_tc_
                         }
                     }
                 }
+                // (2b) with permuted columns (activation order) every column has its own group: its scale is a
+                // dependent global load (permutation -> group -> scale).  One column of look-ahead cannot hide that, and
+                // the chain then runs at one such latency per column; so the 32 pairs are fetched here, eight at a time,
+                // where the thread is about to wait for the accumulator anyway
+                const bool staged_meta = TMEMA && !uniform_meta;
+#ifdef FORGE_SOLVER_PROFILE
+                const long long _pst0 = clock64();
+                pacc[7] += (unsigned long long)(_pst0 - _pnr0);
+#endif
+                if (staged_meta) {
+#pragma unroll 1
+                    for (int i0 = 0; i0 < kSub; i0 += 8) {
+                        // branch-free, so that the eight permutation loads, then the sixteen table loads, are all in
+                        // flight together (indices are clamped into range; out-of-range slots get the neutral pair)
+                        const int64_t rr = active ? r : (R - 1);
+                        int64_t gi[8];
+                        float sv[8], zv[8];
+                        if (MODE == 0) {
+                            uint32_t oc[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const int64_t c = imin64(cs + i0 + i, C - 1);
+                                oc[i] = p.perm ? (uint32_t)__ldg(p.perm + (int64_t)u * C + c) : (uint32_t)c;
+                            }
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const int64_t g = p.gs_shift >= 0 ? (int64_t)(oc[i] >> p.gs_shift)
+                                                                  : (int64_t)(oc[i] / (uint32_t)p.gs);
+                                gi[i] = p.meta_t ? ((int64_t)b * p.G + g) * R + rr : ((int64_t)b * R + rr) * p.G + g;
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) gi[i] = ((int64_t)b * C + imin64(cs + i0 + i, C - 1)) * R + rr;
+                        }
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            sv[i] = __ldg(p.scales + gi[i]);
+                            zv[i] = __ldg(p.qzeros + gi[i]);
+                        }
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const bool in = active && (cs + i0 + i < C);
+                            meta_s[(i0 + i) * kBlk + tid] = in ? sv[i] : 1.0f;
+                            meta_z[(i0 + i) * kBlk + tid] = in ? (uint8_t)(int)zv[i] : (uint8_t)0;
+                        }
+                    }
+                }
+#ifdef FORGE_SOLVER_PROFILE
+                pacc[6] += (unsigned long long)(clock64() - _pst0);
+                const long long _px0 = clock64();
+#endif
                 // (3) x = W - acc for the 32 columns of this sub-block
                 // es[.][tid] is this thread's own column of the scratch: the near update above has consumed the previous
                 // sub-block's errors, so it now holds this sub-block's original weights until each is replaced by its error
@@ -590,7 +797,9 @@ __global__ void __launch_bounds__(kTcThreads, (kTcStages > 2 ? 2 : 3)) solve_tc_
                     es[i * kBlk + tid] = x[i];
                 }
                 if (bs > 0 || sb > 0) {
+                    PROF_T0();
                     if (ok) ok = mbar_wait(bar_acc, acc_it & 1u, abort_flag);
+                    PROF_ADD(4);
                     ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld is warp-aligned: the whole warp goes or none
                     if (ok) {
                         tc_fence_after();
@@ -608,12 +817,16 @@ __global__ void __launch_bounds__(kTcThreads, (kTcStages > 2 ? 2 : 3)) solve_tc_
                 cp_async_wait<0>();
                 rows_barrier();
                 if (*abort_flag) break;
+#ifdef FORGE_SOLVER_PROFILE
+                const long long _pch0 = clock64();
+                pacc[3] += (unsigned long long)(_pch0 - _px0);
+#endif
                 // (5) sequential solve of the 32 columns.  The loop is rolled: x and w slide down by one register per
                 // column, so that the column being solved is always x[0] and every index is static.  (Fully unrolled,
                 // the 32 x ~80 instructions run once per pass and the warp stalls on instruction fetch.)
                 uint32_t maskbits = 0u;
-                float s_nx, q0_nx;
-                load_meta<MODE>(p, b, u, r, cs, active, s_nx, q0_nx);
+                float s_nx = 1.0f, q0_nx = 0.0f;
+                if (!staged_meta) load_meta<MODE>(p, b, u, r, cs, active, s_nx, q0_nx);
                 uint8_t *qp = p.q + ((int64_t)b * C + cs) * R + r;
                 float *ep = E + cs * R + r;
                 float *wp = Wt + cs * R + r;
@@ -631,12 +844,13 @@ __global__ void __launch_bounds__(kTcThreads, (kTcStages > 2 ? 2 : 3)) solve_tc_
 #pragma unroll
                     for (int k4 = 0; k4 < kFirst; ++k4) u4[k4] = urow[k4];
                     const float w_t = es[t * kBlk + tid];   // the column's original weight; replaced by its error below
-                    const float sc = s_nx, q0 = q0_nx;
+                    const float sc = staged_meta ? meta_s[t * kBlk + tid] : s_nx;
+                    const float q0 = staged_meta ? (float)meta_z[t * kBlk + tid] : q0_nx;
                     if (!uniform_meta || t == 0) {
                         inv_s = __fdiv_rn(1.0f, __fadd_rn(sc, kEps));
                         nq0s = -__fmul_rn(q0, sc);
                     }
-                    if (!uniform_meta && t + 1 < kSub) load_meta<MODE>(p, b, u, r, c + 1, active, s_nx, q0_nx);
+                    if (!staged_meta && !uniform_meta && t + 1 < kSub) load_meta<MODE>(p, b, u, r, c + 1, active, s_nx, q0_nx);
                     float err = 0.0f;
                     if (c < C) {
                         if (SPARSE && (t & 3) == 0) {
@@ -694,12 +908,113 @@ __global__ void __launch_bounds__(kTcThreads, (kTcStages > 2 ? 2 : 3)) solve_tc_
 #pragma unroll 1
                 for (int t = 24; t < 32; ++t) column(std::integral_constant<int, 8>{}, t);
                 if (SPARSE && active && (cs < C)) p.M[((int64_t)b * ((C + 31) / 32) + (cs >> 5)) * R + r] = maskbits;
+#ifdef FORGE_SOLVER_PROFILE
+                pacc[5] += (unsigned long long)(clock64() - _pch0);
+#endif
             }
             // the errors of this block must be visible to the far-phase loads of the next one
             rows_barrier();
             if (*abort_flag) break;
         }
         cp_async_wait<0>();
+    } else if (TMEMA && warp == 5) {
+        // ---- U loader: the pairs of every k-step in the order the MMAs take them (per block: the far k-steps, then the
+        // twelve near ones), each into its ring slot as soon as the MMAs that last read the slot have completed
+        if (lane == 0) {
+            bool ok = true;
+            const uint64_t keep = l2_policy_evict_last();
+            for (int64_t bs = 0; bs < C && ok; bs += kBlk) {
+                const int64_t first = usplit_pair_index(bs / kBlk, 0);
+                const int n_stages = (int)(bs / kKS) / kTmemaKPerStage + 3;    // far stages, then the three near ones
+                for (int sg = 0; sg < n_stages && ok; ++sg) {
+                    const uint32_t s = it % kTcStages, ph = (it / kTcStages) & 1u;
+                    {
+                        PROF_T0();
+                        ok = mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag);
+                        PROF_ADD(8);
+                    }
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(bar_full_u + 8 * s, (uint32_t)kStageStride);
+                    bulk_copy_g2s_hint(smem_base + s * kStageStride,
+                                       usp + (first + (int64_t)sg * kTmemaKPerStage) * kPairBytes, (uint32_t)kStageStride,
+                                       bar_full_u + 8 * s, keep);
+                    ++it;
+                }
+            }
+        }
+        __syncwarp();
+    } else if (TMEMA) {
+        // ---- MMA issuer, stages of four k-steps: errors from tensor memory, U pairs from the ring
+        bool ok = true;
+        const uint32_t id_far = idesc_tf32_ts(128);
+        auto stage_mmas = [&](uint32_t s, uint32_t d, uint32_t boff, uint32_t id, bool first_accumulates) {
+            const uint32_t e0 = tmem_e + s * 64u;
+            const uint64_t u0 = make_desc_tf32(smem_base + s * kStageStride + boff);
+#pragma unroll
+            for (int k = 0; k < kTmemaKPerStage; ++k) {
+                // descriptors address in 16-byte units: a pair is 8 KB = 512 units on, its lo piece 256 units on
+                const uint64_t uhi = u0 + (uint64_t)(k * (kPairBytes >> 4));
+                const uint64_t ulo = uhi + (uint64_t)(kPieceBytes >> 4);
+                const uint32_t ehi = e0 + (uint32_t)k * 16u, elo = ehi + 8u;
+#ifdef FORGE_SOLVER_PROFILE
+                umma_tf32_ts(d, ehi, uhi, id, (k > 0 || first_accumulates) ? 1u : 0u);
+                if (!(prof_dbg & 1)) umma_tf32_ts(d, elo, uhi, id, 1u);
+                if (!(prof_dbg & 2)) umma_tf32_ts(d, ehi, ulo, id, 1u);
+#else
+                umma_tf32_ts(d, ehi, uhi, id, (k > 0 || first_accumulates) ? 1u : 0u);
+                umma_tf32_ts(d, elo, uhi, id, 1u);
+                umma_tf32_ts(d, ehi, ulo, id, 1u);
+#endif
+            }
+        };
+        for (int64_t bs = 0; bs < C && ok; bs += kBlk) {
+            if (bs > 0) {
+                const int nst = (int)(bs / kKS) / kTmemaKPerStage;
+                for (int sg = 0; sg < nst && ok; ++sg) {
+                    const uint32_t s = it % kTcStages, ph = (it / kTcStages) & 1u;
+                    {
+                        PROF_T0();
+                        ok = mbar_wait(bar_full + 8 * s, ph, abort_flag);
+                        PROF_ADD(9);
+                    }
+                    {
+                        PROF_T0();
+                        if (ok) ok = mbar_wait(bar_full_u + 8 * s, ph, abort_flag);
+                        PROF_ADD(10);
+                    }
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (lane == 0) {
+                        PROF_T0();
+                        stage_mmas(s, tmem_base, 0u, id_far, sg > 0);
+                        umma_commit(bar_empty + 8 * s);
+                        PROF_ADD(11);
+                    }
+                    __syncwarp();
+                    ++it;
+                }
+                if (!ok) break;
+                if (lane == 0) umma_commit(bar_acc);
+                __syncwarp();
+            }
+            for (int sb = 1; sb < 4 && ok; ++sb) {
+                const uint32_t s = it % kTcStages, ph = (it / kTcStages) & 1u;
+                ok = mbar_wait(bar_full + 8 * s, ph, abort_flag);
+                if (ok) ok = mbar_wait(bar_full_u + 8 * s, ph, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                if (lane == 0) {
+                    // skip the MN blocks of the solved sub-blocks; block 0 has no far phase: its first near stage
+                    // starts the accumulator columns it covers
+                    stage_mmas(s, tmem_base + (uint32_t)(sb * kSub), (uint32_t)sb * 1024u,
+                               idesc_tf32_ts((uint32_t)(kBlk - sb * kSub)), bs > 0 || sb > 1);
+                    umma_commit(bar_empty + 8 * s);
+                    umma_commit(bar_acc);
+                }
+                __syncwarp();
+                ++it;
+            }
+        }
     } else {
         bool ok = true;
         for (int64_t bs = 0; bs < C && ok; bs += kBlk) {
@@ -707,17 +1022,28 @@ __global__ void __launch_bounds__(kTcThreads, (kTcStages > 2 ? 2 : 3)) solve_tc_
                 const int nks = (int)(bs / kKS);
                 for (int ks = 0; ks < nks && ok; ++ks) {
                     const uint32_t s = it % kTcStages, ph = (it / kTcStages) & 1u;
-                    ok = mbar_wait(bar_full + 8 * s, ph, abort_flag);
+                    {
+                        PROF_T0();
+                        ok = mbar_wait(bar_full + 8 * s, ph, abort_flag);
+                        PROF_ADD(9);
+                    }
+                    {
+                        PROF_T0();
+                        if (ok && TMEMA) ok = mbar_wait(bar_full_u + 8 * s, ph, abort_flag);
+                        PROF_ADD(10);
+                    }
                     if (!ok) break;
                     tc_fence_after();
                     if (lane == 0) {
-                        const uint32_t st = smem_base + s * kTcStageBytes;
-                        const uint64_t ehi = make_desc_tf32(st), elo = make_desc_tf32(st + kPieceBytes);
-                        const uint64_t uhi = make_desc_tf32(st + 2 * kPieceBytes), ulo = make_desc_tf32(st + 3 * kPieceBytes);
-                        const uint32_t id = idesc_tf32(128);
-                        umma_tf32(tmem_base, ehi, uhi, id, ks > 0 ? 1u : 0u);
-                        umma_tf32(tmem_base, elo, uhi, id, 1u);
-                        umma_tf32(tmem_base, ehi, ulo, id, 1u);
+                        const uint32_t st = smem_base + s * kStageStride;
+                        const uint64_t uhi = make_desc_tf32(st + kUoff), ulo = make_desc_tf32(st + kUoff + kPieceBytes);
+                        {
+                            const uint64_t ehi = make_desc_tf32(st), elo = make_desc_tf32(st + kPieceBytes);
+                            const uint32_t id = idesc_tf32(128);
+                            umma_tf32(tmem_base, ehi, uhi, id, ks > 0 ? 1u : 0u);
+                            umma_tf32(tmem_base, elo, uhi, id, 1u);
+                            umma_tf32(tmem_base, ehi, ulo, id, 1u);
+                        }
                         umma_commit(bar_empty + 8 * s);
                     }
                     __syncwarp();
@@ -731,21 +1057,24 @@ __global__ void __launch_bounds__(kTcThreads, (kTcStages > 2 ? 2 : 3)) solve_tc_
                 for (int i = 0; i < 4 && ok; ++i) {
                     const uint32_t s = it % kTcStages, ph = (it / kTcStages) & 1u;
                     ok = mbar_wait(bar_full + 8 * s, ph, abort_flag);
+                    if (ok && TMEMA) ok = mbar_wait(bar_full_u + 8 * s, ph, abort_flag);
                     if (!ok) break;
                     tc_fence_after();
                     if (lane == 0) {
-                        const uint32_t st = smem_base + s * kTcStageBytes;
+                        const uint32_t st = smem_base + s * kStageStride;
                         const uint32_t boff = (uint32_t)sb * 1024u;  // skip the MN blocks of the solved sub-blocks
-                        const uint64_t ehi = make_desc_tf32(st), elo = make_desc_tf32(st + kPieceBytes);
-                        const uint64_t uhi = make_desc_tf32(st + 2 * kPieceBytes + boff);
-                        const uint64_t ulo = make_desc_tf32(st + 3 * kPieceBytes + boff);
-                        const uint32_t id = idesc_tf32((uint32_t)(kBlk - sb * kSub));
+                        const uint64_t uhi = make_desc_tf32(st + kUoff + boff);
+                        const uint64_t ulo = make_desc_tf32(st + kUoff + kPieceBytes + boff);
                         const uint32_t d = tmem_base + (uint32_t)(sb * kSub);
                         // block 0 has no far phase: its first near step starts the accumulator columns it covers
                         const uint32_t acc = (bs > 0 || sb > 1 || i > 0) ? 1u : 0u;
-                        umma_tf32(d, ehi, uhi, id, acc);
-                        umma_tf32(d, elo, uhi, id, 1u);
-                        umma_tf32(d, ehi, ulo, id, 1u);
+                        {
+                            const uint64_t ehi = make_desc_tf32(st), elo = make_desc_tf32(st + kPieceBytes);
+                            const uint32_t id = idesc_tf32((uint32_t)(kBlk - sb * kSub));
+                            umma_tf32(d, ehi, uhi, id, acc);
+                            umma_tf32(d, elo, uhi, id, 1u);
+                            umma_tf32(d, ehi, ulo, id, 1u);
+                        }
                         umma_commit(bar_empty + 8 * s);
                     }
                     __syncwarp();
@@ -757,6 +1086,13 @@ __global__ void __launch_bounds__(kTcThreads, (kTcStages > 2 ? 2 : 3)) solve_tc_
             }
         }
     }
+#ifdef FORGE_SOLVER_PROFILE
+    if (prof_on) {
+        const int slot = warp == 0 ? 16 : (warp == 4 ? 17 : (warp == 5 ? 18 : 19));
+        g_prof[slot] += (unsigned long long)(clock64() - prof_start);
+        for (int i = 0; i < 12; ++i) g_prof[i] += pacc[i];
+    }
+#endif
     tc_fence_before();
     __syncthreads();
     if (*abort_flag) {
@@ -770,7 +1106,7 @@ __global__ void __launch_bounds__(kTcThreads, (kTcStages > 2 ? 2 : 3)) solve_tc_
     }
     if (warp == 4) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(128u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
 }
 
@@ -795,6 +1131,33 @@ __global__ void __launch_bounds__(128) split_u_kernel(const float *__restrict__ 
         const uint32_t off = piece_offset(jA + 4 * h, c4);
         *reinterpret_cast<float4 *>(pair + off) = hi;
         *reinterpret_cast<float4 *>(pair + kPieceBytes + off) = lo;
+    }
+}
+
+// [nb][R][G] -> [nb][G][R] for the scale and zero tables: the solver's 128 row threads then read one column's
+// entries from consecutive addresses
+__global__ void transpose_meta_kernel(const float *__restrict__ s_in, const float *__restrict__ z_in, int64_t R, int64_t G,
+                                      float *__restrict__ s_out, float *__restrict__ z_out) {
+    __shared__ float ts[32][33], tz[32][33];
+    const int b = blockIdx.z;
+    const int64_t g0 = (int64_t)blockIdx.x * 32, r0 = (int64_t)blockIdx.y * 32;
+    const int tx = threadIdx.x, ty = threadIdx.y;  // block (32, 8)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int64_t r = r0 + ty + 8 * i, g = g0 + tx;
+        if (r < R && g < G) {
+            ts[ty + 8 * i][tx] = s_in[((int64_t)b * R + r) * G + g];
+            tz[ty + 8 * i][tx] = z_in[((int64_t)b * R + r) * G + g];
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int64_t g = g0 + ty + 8 * i, r = r0 + tx;
+        if (r < R && g < G) {
+            s_out[((int64_t)b * G + g) * R + r] = ts[tx][ty + 8 * i];
+            z_out[((int64_t)b * G + g) * R + r] = tz[tx][ty + 8 * i];
+        }
     }
 }
 
@@ -879,14 +1242,22 @@ int launch_solve(const SolveParams &p, int nb, int32_t *status, cudaStream_t st)
         return check_launch("forge_gptq_solve");
     }
     // per-device attributes (more than 48 KB of dynamic shared memory): set on the device that is current for this call
-    auto go = [&](auto kernel, size_t smem) {
+    auto go = [&](auto kernel, size_t smem, int threads = kTcThreads) {
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        kernel<<<grid, kTcThreads, smem, st>>>(p, status); FORGE_NOTE_LAUNCH();
+        kernel<<<grid, threads, smem, st>>>(p, status); FORGE_NOTE_LAUNCH();
     };
     const bool few = (int64_t)grid.x * grid.y <= 2 * 148;
     if (p.usplit) {
-        // U pre-split: wide matrices (long far phases) take the deep ring, two CTAs per SM; others keep three per SM
-        if (p.C >= 4096 || few) go(solve_tc_kernel<MODE, SPARSE, 4, kTcStagesDeep, true>, tc_smem_bytes(kTcStagesDeep, 4, true));
+        // U pre-split.  Wide matrices (long far phases) and small launches: errors through tensor memory, two CTAs per
+        // SM (256 TMEM columns each); FORGE_SOLVER_IMPL=smem keeps the shared-memory staging of the errors there too
+        // (cross-checks).  Other launches keep three CTAs per SM for the serial column chain.
+        const char *e = getenv("FORGE_SOLVER_IMPL");
+        const bool smem_e = e && strcmp(e, "smem") == 0;
+        if ((p.C >= 4096 || few) && !smem_e)
+            go(solve_tc_kernel<MODE, SPARSE, 1, kTmemaStages, true, true>, tc_smem_bytes(kTmemaStages, 0, true, true),
+               kTmemaThreads);
+        else if (p.C >= 4096 || few)
+            go(solve_tc_kernel<MODE, SPARSE, 4, kTcStagesDeep, true>, tc_smem_bytes(kTcStagesDeep, 4, true));
         else go(solve_tc_kernel<MODE, SPARSE, 4, kTcStagesShallow, true>, tc_smem_bytes(kTcStagesShallow, 4, true));
     } else if (few) {
         go(solve_tc_kernel<MODE, SPARSE, kTcRawDeep, kTcStagesShallow, false>, tc_smem_bytes(kTcStagesShallow, kTcRawDeep, false));
@@ -899,6 +1270,21 @@ int launch_solve(const SolveParams &p, int nb, int32_t *status, cudaStream_t st)
 inline int64_t align256(int64_t x) { return (x + 255) & ~(int64_t)255; }
 
 }  // namespace
+
+#ifdef FORGE_SOLVER_PROFILE
+// profiling build only: copy the cycle counters out (32 x u64) and clear them
+extern "C" int forge_debug_solver_set(int dbg) {
+    cudaMemcpyToSymbol(g_prof_dbg, &dbg, sizeof(int));
+    return 0;
+}
+extern "C" int forge_debug_solver_profile(unsigned long long *out32) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out32, g_prof, sizeof(unsigned long long) * 32);
+    unsigned long long zero[32] = {0};
+    cudaMemcpyToSymbol(g_prof, zero, sizeof(zero));
+    return 0;
+}
+#endif
 
 extern "C" int64_t forge_solve_split_u_bytes(int nu, int64_t C) {
     return (C > 0 && C % 4 == 0 && nu > 0) ? (int64_t)nu * usplit_bytes_per_slot(C) : 0;
@@ -916,8 +1302,12 @@ extern "C" int forge_solve_split_u(const float *U, int nu, int64_t C, void *uspl
     return check_launch("forge_solve_split_u");
 }
 
+// transposed scale / zero tables: the group size is not known here, 32 (the smallest the grid kernels take) bounds it
+static inline int64_t meta_t_bytes(int nb, int64_t R, int64_t C) { return align256((int64_t)nb * R * (C / 32 + 1) * 4); }
+
 extern "C" int64_t forge_solve_workspace_bytes(int nb, int64_t R, int64_t C) {
-    return align256((int64_t)nb * C * R * 4) + align256((int64_t)nb * C * R) + align256((int64_t)nb * C * 4) + 256;
+    return align256((int64_t)nb * C * R * 4) + align256((int64_t)nb * C * R) + align256((int64_t)nb * C * 4) +
+           2 * meta_t_bytes(nb, R, C) + 256;
 }
 
 extern "C" int forge_gptq_solve_cr(float *Wt, const float *U, const float *uinv, const float *scales,
@@ -931,6 +1321,7 @@ extern "C" int forge_gptq_solve_cr(float *Wt, const float *U, const float *uinv,
     p.Wt = Wt; p.E = (float *)ws; p.U = U; p.uvec = uinv; p.u_map = nullptr;
     p.scales = scales; p.qzeros = qzeros; p.perm = nullptr; p.q = q; p.M = M;
     p.R = R; p.C = C; p.G = 0; p.gs = 1; p.maxq = (1 << bits) - 1; p.write_deq = 1; p.uvec_is_diag = 0;
+    p.gs_shift = 0;
     cudaStream_t st = (cudaStream_t)stream;
     return sparse14 ? launch_solve<1, true>(p, 1, status, st) : launch_solve<1, false>(p, 1, status, st);
 }
@@ -953,18 +1344,32 @@ extern "C" int forge_gptq_solve_batched(const void *W, int w_dtype, int nb, int6
     wsp += align256((int64_t)nb * C * R * 4);
     uint8_t *qt = (uint8_t *)wsp;
     wsp += align256((int64_t)nb * C * R);
-    int32_t *perm_inv = nullptr;
+    int32_t *perm_inv = (int32_t *)wsp;
+    wsp += align256((int64_t)nb * C * 4);
+    float *scales_t = nullptr, *qzeros_t = nullptr;
+    const int64_t G = cdiv(C, gs);
+    if (gs >= 32) {
+        scales_t = (float *)wsp;
+        qzeros_t = (float *)(wsp + meta_t_bytes(nb, R, C));
+        transpose_meta_kernel<<<dim3((unsigned)cdiv(G, 32), (unsigned)cdiv(R, 32), nb), dim3(32, 8), 0, st>>>(
+            scales, qzeros, R, G, scales_t, qzeros_t);
+        FORGE_NOTE_LAUNCH();
+    }
+    if (!perm) perm_inv = nullptr;
     if (perm) {
         FORGE_REQUIRE(nu > 0 && nu <= nb, "nu must be in [1, nb]");
-        perm_inv = (int32_t *)wsp;
         perm_inverse_kernel<<<dim3((unsigned)cdiv(C, 256), nu), 256, 0, st>>>(perm, C, perm_inv); FORGE_NOTE_LAUNCH();
     }
     dim3 tgrid((unsigned)cdiv(C, 32), (unsigned)cdiv(R, 32), nb);
     transpose_gather_kernel<<<tgrid, dim3(32, 8), 0, st>>>(W, w_dtype, R, C, perm_inv, u_map, Wt); FORGE_NOTE_LAUNCH();
     SolveParams p{};
     p.Wt = Wt; p.E = Wt; p.U = U; p.uvec = udiag; p.u_map = u_map;
-    p.scales = scales; p.qzeros = qzeros; p.perm = perm; p.q = qt; p.M = M;
-    p.R = R; p.C = C; p.G = cdiv(C, gs); p.gs = gs; p.maxq = (1 << bits) - 1; p.write_deq = 0; p.uvec_is_diag = 1;
+    p.scales = scales_t ? scales_t : scales; p.qzeros = scales_t ? qzeros_t : qzeros; p.meta_t = scales_t ? 1 : 0;
+    p.perm = perm; p.q = qt; p.M = M;
+    p.R = R; p.C = C; p.G = G; p.gs = gs; p.maxq = (1 << bits) - 1; p.write_deq = 0; p.uvec_is_diag = 1;
+    p.gs_shift = -1;
+    for (int sft = 0; sft < 31; ++sft)
+        if ((1 << sft) == gs) p.gs_shift = sft;
     p.alt = form ? 1 : 0;
     p.usplit = (const uint8_t *)usplit;
     p.usplit_stride = usplit ? usplit_bytes_per_slot(C) : 0;

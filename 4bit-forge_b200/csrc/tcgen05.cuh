@@ -34,6 +34,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     const long long t0 = clock64();
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
+        // back off between polls: a waiting warp must not take issue slots from the warps it is waiting for (the
+        // serial column chain of a co-resident CTA is bound by exactly those slots)
+        __nanosleep(64);
         if (*abort_flag) return false;
         if (clock64() - t0 > budget) {
             *abort_flag = 1;
@@ -52,6 +55,27 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst_smem, const void *src
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
                  "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
+}
+
+// The same copy with an L2 policy: data that many CTAs re-read (the pre-split factor pieces, shared by all row strips of
+// an expert) should outlive the streams that pass through L2 once.
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void bulk_copy_g2s_hint(uint32_t dst_smem, const void *src, uint32_t bytes, uint32_t bar,
+                                                   uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+            dst_smem),
+        "l"(src), "r"(bytes), "r"(bar), "l"(policy)
+        : "memory");
 }
 
 __device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void *src, bool pred) {
@@ -81,6 +105,17 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// 16 consecutive 32-bit TMEM columns of this thread's lane (32x32b shape: lane = 32 * (warp % 4) + lane id)
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        :
+        : "r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+          "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 
 
@@ -115,6 +150,22 @@ __device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t adesc, uint6
         "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
         :
         : "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+
+// The same MMA with the A operand read from tensor memory: A is [128 lanes (M)] x [8 columns (K)] of 32-bit tf32
+// values at a_tmem (K along the columns, so A counts as K-major); B stays an MN-major shared-memory piece.
+__device__ __forceinline__ uint32_t idesc_tf32_ts(uint32_t n) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | (1u << 16) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+}
+__device__ __forceinline__ void umma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        :
+        : "r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
         : "memory");
 }
 
