@@ -1,6 +1,7 @@
 """`kernels`: the reference's extension-module surface (forge/backend/cuda/kernels.cpp:92-150) re-created
 over the sm_100a C ABI.  Function names, argument order, in-place behaviour and return values follow the
-pybind module; inference GEMMs and the Babai solver are not part of the solver path and are absent.
+pybind module; the per-expert inference GEMM over the Wpair layout is here too, the fused MoE inference GEMMs and the
+Babai solver are not part of the solver path and are absent.
 
 Like the reference stub (forge/backend/cuda/__init__.py:74-87) every call raises RuntimeError when CUDA
 or the library is unavailable: there is no CPU fallback.
@@ -70,6 +71,21 @@ class _Kernels:
         out = ops.pack_sparse14(qweight_rc.to(torch.uint8).contiguous(), Mi,
                                 scales.to(torch.float32).contiguous())
         return out.view(torch.uint64)
+
+
+    @staticmethod
+    def sparsegptq14_gemm(qW2S1u64, X):
+        """sparse14_gemm.cu:282-374 — Wpair [G2, R, 2] uint64, X bf16 [N, C] -> Y bf16 [N, R]."""
+        if not (qW2S1u64.dim() == 3 and qW2S1u64.size(2) == 2):
+            raise RuntimeError("qW2S1u64 must be [G2, R, 2]")
+        if X.dim() != 2:
+            raise RuntimeError("X must be [N, C]")
+        if X.dtype != torch.bfloat16:
+            raise RuntimeError("X must be bfloat16")
+        w = qW2S1u64.contiguous()
+        if w.dtype != torch.int64:
+            w = w.view(torch.int64)
+        return ops.sparse14_gemm(w, X)
 
 
 kernels = _Kernels()

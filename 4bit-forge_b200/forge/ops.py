@@ -286,3 +286,16 @@ def pack_sparse14(q_rc, M, scales32):
     out = torch.empty(((G32 + 1) // 2, R, 2), dtype=torch.int64, device=_dev(q_rc))
     call("forge_pack_sparse14", ptr(q_rc), ptr(M), ptr(scales32), R, C, ptr(out), stream_ptr())
     return out
+
+
+def sparse14_gemm(wpair: torch.Tensor, X: torch.Tensor) -> torch.Tensor:
+    """Y = X @ What^T with What decoded from the Wpair words [G2, R, 2] (forge_sparse14_gemm).  X bf16 [N, C]."""
+    assert X.dtype == torch.bfloat16 and X.dim() == 2 and wpair.dim() == 3 and wpair.shape[2] == 2
+    G2, R, _ = wpair.shape
+    N, C = X.shape
+    if G2 != (C + 63) // 64:
+        raise RuntimeError(f"Wpair G2 mismatch: got {G2} expected {(C + 63) // 64}")
+    X = X.contiguous()
+    Y = torch.empty((N, R), dtype=torch.bfloat16, device=_dev(X))
+    call("forge_sparse14_gemm", ptr(wpair.contiguous()), ptr(X), X.stride(0), N, R, C, ptr(Y), stream_ptr())
+    return Y

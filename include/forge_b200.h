@@ -285,6 +285,16 @@ int forge_pack_int4(const uint8_t *q, const float *qzeros, int64_t rows, int64_t
 int forge_pack_sparse14(const uint8_t *q, const uint32_t *M, const float *scales32, int64_t R, int64_t C,
                         uint64_t *out, void *stream);
 
+/* ---- inference over the Wpair layout ------------------------------------------
+ * Y[n, r] = bf16( sum_c X[n, c] * What[r, c] ), What decoded on the fly from wpair [ceil(C/64), R, 2] uint64
+ * (the output of forge_pack_sparse14): per 32-channel half  scale * sum_{i<8} X[n, base + 4 i + pos_i] * (code_i - 8),
+ * fp32 fused multiply-adds in that order, one rounding at the end.  X bf16 [N, ldx >= C], Y bf16 [N, R]; no padding
+ * of N, R or C is required.  Bit-identical to kernels.sparsegptq14_gemm
+ * (moe_proj_unstructured_sparse14_int4symq_gemm, forge/backend/cuda/sparse14_gemm.cu:49-140, :282-374), which it
+ * replaces. */
+int forge_sparse14_gemm(const uint64_t *wpair, const void *X_bf16, int64_t ldx, int64_t N, int64_t R, int64_t C,
+                        void *Y_bf16, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -324,3 +324,46 @@ void fo_pack_int4(const uint8_t *q, const float *zeros, int64_t R, int64_t C, in
         }
     }
 }
+
+/* ------------------------------------------------------------------------- *
+ * Inference GEMM over the Wpair layout.
+ * Follows forge/backend/cuda/sparse14_gemm.cu:49-140 (the kernel; the launcher's zero padding of X, :318-336, is
+ * the bounds check below).  Per output row r, token n and 32-channel half: sum = fma(x, q4 - 8, sum) over the eight
+ * groups in order, acc = fma(sum, scale, acc); Y = bf16_rn(acc).  nvcc's default contraction fuses the kernel's
+ * `sum += x * w` and `acc += sum * scale`, hence the explicit fmaf here.
+ *   wpair [G2,R,2] uint64, X bf16 bits [N,C] (uint16), Y bf16 bits [N,R] (uint16)
+ * ------------------------------------------------------------------------- */
+static inline float bf16_bits_to_f32(uint16_t b) {
+    uint32_t u = ((uint32_t)b) << 16;
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
+void fo_sparse14_gemm(const uint64_t *wpair, const uint16_t *X, int64_t N, int64_t R, int64_t C, uint16_t *Y) {
+    const int64_t G2 = (C + 63) / 64;
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < R; ++r) {
+        for (int64_t n = 0; n < N; ++n) {
+            float acc = 0.0f;
+            for (int64_t g2 = 0; g2 < G2; ++g2) {
+                for (int half = 0; half < 2; ++half) {
+                    const uint64_t u = wpair[(g2 * R + r) * 2 + half];
+                    const uint32_t qw32 = (uint32_t)(u & 0xFFFFFFFFull), hi = (uint32_t)(u >> 32);
+                    const uint32_t idx16 = hi & 0xFFFFu;
+                    const float scale = bf16_bits_to_f32((uint16_t)(hi >> 16));
+                    const int64_t base = g2 * 64 + half * 32;
+                    float sum = 0.0f;
+                    for (int i = 0; i < 8; ++i) {
+                        const int64_t c = base + 4 * i + ((idx16 >> (2 * i)) & 3u);
+                        const float w = (float)(int)((qw32 >> (4 * i)) & 0xFu) - 8.0f;
+                        const float x = (c < C) ? bf16_bits_to_f32(X[n * C + c]) : 0.0f;
+                        sum = fmaf(x, w, sum);
+                    }
+                    acc = fmaf(sum, scale, acc);
+                }
+            }
+            Y[n * R + r] = f32_to_bf16_rn(acc);
+        }
+    }
+}

@@ -1,6 +1,6 @@
 """Build oracle/_ref/forge_ref_kernels.so: the reference's own solver-path CUDA kernels for sm_100a.
 
-Test infrastructure.  The four .cu files are compiled where they lie in the reference checkout (nothing is copied
+Test infrastructure.  The five .cu files are compiled where they lie in the reference checkout (nothing is copied
 into this repository); the only source of ours is the pybind stub oracle/ref_binding.cpp.  The reference builds the
 same files with torch.utils.cpp_extension.load at import time (forge/backend/cuda/__init__.py:48-75); this recipe
 does the same with an explicit sm_100a arch and an in-tree output folder, so that the library travels to the GPU
@@ -17,7 +17,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_ref")
 NAME = "forge_ref_kernels"
-KERNEL_FILES = ("quant_grid.cu", "solver.cu", "solver_sparsegptq14.cu", "bitpacking_sparsegptq14.cu")
+KERNEL_FILES = ("quant_grid.cu", "solver.cu", "solver_sparsegptq14.cu", "bitpacking_sparsegptq14.cu", "sparse14_gemm.cu")
 
 
 def built_path():

@@ -132,6 +132,19 @@ def pack_sparsegptq14_to_u64x2(qweight_rc, M, scales):
     return out
 
 
+def sparsegptq14_gemm(wpair: torch.Tensor, X: torch.Tensor) -> torch.Tensor:
+    """kernels.sparsegptq14_gemm, forge/backend/cuda/sparse14_gemm.cu:49-140, :282-374.  wpair [G2,R,2] (uint64 bit
+    pattern as int64), X bf16 [N,C] -> Y bf16 [N,R]."""
+    G2, R, _ = wpair.shape
+    N, C = X.shape
+    assert G2 == (C + 63) // 64
+    w = wpair.contiguous().view(torch.int64)
+    xb = X.contiguous().view(torch.int16)
+    y = torch.empty((N, R), dtype=torch.int16)
+    lib().fo_sparse14_gemm(_p(w), _p(xb), ctypes.c_int64(N), ctypes.c_int64(R), ctypes.c_int64(C), _p(y))
+    return y.view(torch.bfloat16)
+
+
 def pack_int4(qweight_rc, zeros_rg, group_size):
     """weight_packed of pack_quantized.py:279-313 via compressed_tensors.pack_to_int32 semantics."""
     q = qweight_rc.to(torch.uint8).contiguous()

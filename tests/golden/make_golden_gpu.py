@@ -1,7 +1,9 @@
 """Golden vectors from the reference's OWN CUDA kernels, run on a B200.
 
     python oracle/ref_build.py <reference checkout>        # on the build machine: oracle/_ref/forge_ref_kernels.so
-    python tests/golden/make_golden_gpu.py                 # on a GPU machine: writes tests/golden/ref_kernels_b200.npz
+    python tests/golden/make_golden_gpu.py [out dir]       # on a GPU machine: writes ref_kernels_b200.npz (solver-path
+                                                           # kernels) and ref_sparse14_gemm_b200.npz (inference GEMM
+                                                           # over the Wpair layout) into tests/golden/ (or out dir)
 
 Every case stores its inputs (small) next to the reference's outputs, so that the CPU tests can replay the oracle on
 exactly the same numbers without the reference and without a GPU.
@@ -65,15 +67,42 @@ def cases(ref, dev):
     return out
 
 
+def gemm_cases(ref, dev):
+    """kernels.sparsegptq14_gemm (forge/backend/cuda/sparse14_gemm.cu) on Wpair words made by the reference's own
+    packer: C a multiple of 64 and not, R not a multiple of the CTA's 128 rows, token counts around every tile size of
+    the launcher's heuristic (1, 2, 3, 4 tokens per CTA)."""
+    out = {}
+    g = torch.Generator().manual_seed(4242)
+    for tag, (R, C, Ns) in {"c256": (130, 256, (1, 5)), "c160": (96, 160, (3, 70, 300)), "c320": (40, 320, (800,))}.items():
+        G32 = (C + 31) // 32
+        q = torch.randint(0, 16, (R, C), generator=g, dtype=torch.uint8)
+        pos = torch.randint(0, 4, (G32, R, 8), generator=g)                       # surviving channel of each group
+        keep = (torch.rand(G32, R, 8, generator=g) > 0.1)                         # a few groups fully pruned
+        M = ((keep.long() << (4 * torch.arange(8) + pos)).sum(-1)).to(torch.int64)
+        M = (M & 0xFFFFFFFF).to(torch.int32)
+        s32 = (torch.rand(G32, R, generator=g) * 0.01 + 1e-3).float()
+        wp = ref.pack_sparsegptq14_to_u64x2(q.to(dev), M.to(dev).view(torch.uint32), s32.to(dev))
+        out[f"{tag}_wpair"] = wp.cpu().view(torch.int64)
+        for N in Ns:
+            X = (torch.randn(N, C, generator=g) * 0.7).to(torch.bfloat16)
+            Y = ref.sparsegptq14_gemm(wp, X.to(dev))
+            out[f"{tag}_X{N}"] = X.view(torch.int16)
+            out[f"{tag}_Y{N}"] = Y.cpu().contiguous().view(torch.int16)
+    return out
+
+
 def main():
     ref = ref_build.load_built()
     if ref is None:
         raise SystemExit("oracle/_ref/forge_ref_kernels.so is missing: run oracle/ref_build.py first")
     dev = torch.device("cuda")
-    arrays = {k: v.numpy() for k, v in cases(ref, dev).items()}
-    path = os.path.join(ROOT, "tests", "golden", "ref_kernels_b200.npz")
-    np.savez_compressed(path, **arrays)
-    print(path, os.path.getsize(path), "bytes;", torch.cuda.get_device_name(0))
+    out_dir = sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "tests", "golden")
+    os.makedirs(out_dir, exist_ok=True)
+    for name, fn in (("ref_kernels_b200.npz", cases), ("ref_sparse14_gemm_b200.npz", gemm_cases)):
+        arrays = {k: v.numpy() for k, v in fn(ref, dev).items()}
+        path = os.path.join(out_dir, name)
+        np.savez_compressed(path, **arrays)
+        print(path, os.path.getsize(path), "bytes;", torch.cuda.get_device_name(0))
 
 
 if __name__ == "__main__":

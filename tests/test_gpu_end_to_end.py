@@ -51,7 +51,10 @@ def test_gptq_class_on_reference_golden_cases(golden, name):
         agree = float((outs_g[0].cpu() == outs_o[0]).float().mean())
         assert agree >= 0.995, agree
         if inp["algorithm"] == "sparsegptq":
-            assert float((outs_g[3].view(torch.int32).cpu() == outs_o[3].view(torch.int32)).float().mean()) >= 0.99
+            mg, mo = outs_g[3].view(torch.int32).cpu(), outs_o[3].view(torch.int32)
+            nib = lambda m: torch.stack([(m >> (4 * i)) & 0xF for i in range(8)], -1)
+            assert float((nib(mg) == nib(mo)).float().mean()) >= 0.995     # 1-of-4 choices
+            assert float((mg == mo).float().mean()) >= 0.99                 # whole 32-column mask words
 
 
 def test_empty_handle_quantizes_with_identity_hessian():

@@ -348,6 +348,10 @@ def test_sparse14_solver_reference_operator(C, R):
     Td = T.clone().to(DEV)
     q, M = kernels.sparsegptq14_solver(Wt.to(DEV), Td, S.to(DEV), Z.to(DEV), 4)
     Mi, Mr = M.view(torch.int32).cpu(), M_ref.view(torch.int32)
+    # a mask word holds eight 1-of-4 choices: >= 99.5 % of the CHOICES agree (the acceptance bar for codes), which is
+    # what the per-group comparison states; whole words (all eight choices equal) agree on >= 99 %
+    nib = lambda m: torch.stack([(m >> (4 * i)) & 0xF for i in range(8)], -1)
+    assert float((nib(Mi) == nib(Mr)).float().mean()) >= 0.995
     assert float((Mi == Mr).float().mean()) >= 0.99
     assert float((q.cpu() == q_ref).float().mean()) >= 0.995
     # U was row-normalised in place like the reference does

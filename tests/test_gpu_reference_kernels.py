@@ -94,12 +94,65 @@ def test_sparse_solver_and_packer_against_reference_kernels(ref):
     Wt = W.T.contiguous()
     q_ref, M_ref = ref.sparsegptq14_solver(Wt.clone(), U.clone(), s_el, z_el, 4)
     q, M = kernels.sparsegptq14_solver(Wt.clone(), U.clone(), s_el, z_el, 4)
-    m_same = float((M.view(torch.int32) == M_ref.view(torch.int32)).float().mean())
-    assert m_same >= 0.99, m_same
-    assert float((q == q_ref).float().mean()) >= 0.99
+    Mi, Mr = M.view(torch.int32), M_ref.view(torch.int32)
+    nib = lambda m: torch.stack([(m >> (4 * i)) & 0xF for i in range(8)], -1)
+    # >= 99.5 % of the 1-of-4 choices and of the codes agree; whole 32-column mask words on >= 99 %
+    assert float((nib(Mi) == nib(Mr)).float().mean()) >= 0.995
+    assert float((Mi == Mr).float().mean()) >= 0.99
+    assert float((q == q_ref).float().mean()) >= 0.995
     # the packer is integer work: bit-exact on identical inputs
     s32 = s.view(R, C // 32).T.contiguous()
     qrc = q_ref.T.contiguous()
     wp_ref = ref.pack_sparsegptq14_to_u64x2(qrc, M_ref, s32)
     wp = kernels.pack_sparsegptq14_to_u64x2(qrc, M_ref, s32)
     assert torch.equal(wp.view(torch.int64), wp_ref.view(torch.int64))
+
+
+def _random_wpair(ref, R, C, seed):
+    g = torch.Generator().manual_seed(seed)
+    G32 = (C + 31) // 32
+    q = torch.randint(0, 16, (R, C), generator=g, dtype=torch.uint8)
+    pos = torch.randint(0, 4, (G32, R, 8), generator=g)
+    keep = torch.rand(G32, R, 8, generator=g) > 0.1
+    M = ((keep.long() << (4 * torch.arange(8) + pos)).sum(-1) & 0xFFFFFFFF).to(torch.int32)
+    s32 = (torch.rand(G32, R, generator=g) * 0.01 + 1e-3).float()
+    return ref.pack_sparsegptq14_to_u64x2(q.to(DEV), M.to(DEV).view(torch.uint32), s32.to(DEV))
+
+
+@pytest.mark.parametrize("R,C,N", [(130, 256, 1), (96, 160, 3), (96, 160, 70), (1536, 3072, 1), (1536, 3072, 8),
+                                   (3072, 1536, 37), (40, 1088, 800)])
+def test_inference_gemm_over_wpair_bit_exact(ref, R, C, N):
+    """forge_sparse14_gemm against the reference's inference kernel (forge/backend/cuda/sparse14_gemm.cu) on the same
+    packed words: identical bf16 outputs, for every token tile of either launcher, ragged R and C included."""
+    from forge.backend.cuda import kernels
+    import ref_port as O
+    wp = _random_wpair(ref, R, C, R + C + N)
+    g = torch.Generator().manual_seed(N)
+    X = (torch.randn(N, C, generator=g) * 0.7).to(torch.bfloat16).to(DEV)
+    Y_ref = ref.sparsegptq14_gemm(wp, X)
+    Y = kernels.sparsegptq14_gemm(wp, X)
+    assert Y.shape == (N, R) and torch.equal(Y.view(torch.int16), Y_ref.contiguous().view(torch.int16))
+    if R * C <= 64 * 1024:
+        Yo = O.sparsegptq14_gemm(wp.cpu().view(torch.int64), X.cpu())
+        assert torch.equal(Yo.view(torch.int16), Y.cpu().view(torch.int16))
+
+
+def test_packed_sparse_layer_is_consumed_end_to_end():
+    """SparseGPT 1:4 + int4 through forge.moe, then the packed Wpair words through the inference GEMM: the product
+    equals X times the de-quantised, masked weights (the bf16 scale of the packed layout is the only difference)."""
+    from forge import synth, moe, ops
+    shape = synth.LayerShape("s", 4, 0, 256, 128, 2048, 2)
+    X = synth.student_t_activations(shape.tokens, shape.hidden, seed=91).to(DEV)
+    ids = synth.route(shape, shape.tokens, seed=91).to(DEV)
+    Wg, Wu, Wd = [w.to(DEV) for w in synth.expert_weights(shape, range(4), seed=91)]
+    cfg = moe.MoEQuantConfig(bits=4, group_size=32, symmetric=True, algorithm="sparsegptq", rel_damp=0.01)
+    out = moe.MoELayerQuantizer(cfg).quantize_experts(X, ids, Wg, Wu, Wd)
+    e = 1
+    xin = X[:64].contiguous()
+    Y = ops.sparse14_gemm(out["gate"]["wpair"][e], xin).float()
+    r = out["gate"]
+    What = ops.dequantize(r["qweight"][e], r["scales"][e].contiguous(), r["qzeros"][e].contiguous(), 32, torch.float32)
+    Mi = r["M"][e].view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    keep = ((Mi.unsqueeze(-1) >> torch.arange(32, device=DEV)) & 1).permute(1, 0, 2).reshape(What.shape[0], -1).float()
+    ref_y = xin.float() @ (What * keep[:, :What.shape[1]]).T
+    assert float((Y - ref_y).norm() / ref_y.norm()) < 1e-2

@@ -60,3 +60,39 @@ def test_sparse_packer_bit_exact(ref):
     M = ref["sparse_M"]
     wp = O.pack_sparsegptq14_to_u64x2(ref["pack_q_rc"], M, ref["pack_scales"])
     assert torch.equal(wp.view(torch.int64), ref["pack_wpair"])
+
+
+GEMM_PATH = os.path.join(os.path.dirname(__file__), "golden", "ref_sparse14_gemm_b200.npz")
+
+
+@pytest.mark.skipif(not os.path.exists(GEMM_PATH), reason="inference-GEMM vectors not generated yet")
+@pytest.mark.parametrize("tag,N", [("c256", 1), ("c256", 5), ("c160", 3), ("c160", 70), ("c160", 300), ("c320", 800)])
+def test_sparse14_gemm_bit_exact(tag, N):
+    """O.sparsegptq14_gemm against the reference's inference kernel over the Wpair layout (sparse14_gemm.cu), run on a
+    B200 by make_golden_gpu.py: identical bf16 outputs."""
+    z = np.load(GEMM_PATH)
+    wp = torch.from_numpy(z[f"{tag}_wpair"])
+    X = torch.from_numpy(z[f"{tag}_X{N}"]).view(torch.bfloat16)
+    Y = O.sparsegptq14_gemm(wp, X)
+    assert torch.equal(Y.view(torch.int16), torch.from_numpy(z[f"{tag}_Y{N}"]))
+
+
+def test_sparse14_gemm_equals_dense_product_of_the_decoded_weights():
+    """Independent of any stored vector: decode the Wpair words to a dense matrix and multiply in float64."""
+    g = torch.Generator().manual_seed(9)
+    R, C, N = 50, 192, 7
+    q = torch.randint(0, 16, (R, C), generator=g, dtype=torch.uint8)
+    pos = torch.randint(0, 4, (C // 32, R, 8), generator=g)
+    M = ((1 << (4 * torch.arange(8) + pos)).sum(-1)).to(torch.int32)
+    s32 = (torch.rand(C // 32, R, generator=g) * 0.01 + 1e-3).float()
+    wp = O.pack_sparsegptq14_to_u64x2(q, M, s32)
+    X = torch.randn(N, C, generator=g).to(torch.bfloat16)
+    Y = O.sparsegptq14_gemm(wp, X).double()
+    keep = torch.zeros(R, C, dtype=torch.bool)
+    for gI in range(C // 32):
+        for i in range(8):
+            keep[torch.arange(R), gI * 32 + 4 * i + pos[gI, :, i]] = True
+    s_bf = s32.to(torch.bfloat16).double().T.repeat_interleave(32, 1)            # the packed scale is bf16
+    What = (q.double() - 8.0) * s_bf * keep
+    ref = X.double() @ What.T
+    assert float((Y - ref).abs().max()) <= 0.01 * float(ref.abs().max()) + 1e-6
