@@ -569,19 +569,39 @@ __global__ void rotate_upper_kernel(float *__restrict__ Uall, int64_t C, const i
 // 1 on the diagonal.  Sources are on or below the diagonal, destinations above it, so it may run in place.
 __global__ void rotate_scale_neg_kernel(const float *__restrict__ Lall, float *__restrict__ Oall, int64_t C,
                                         const int32_t *__restrict__ info, float *__restrict__ udiag) {
+    // a thread handles four consecutive destination columns t .. t+3 of row s (sources are four consecutive, reversed,
+    // elements of one row of L); vector accesses where C is a multiple of 4
     const int b = blockIdx.z;
     const float *L = Lall + (int64_t)b * C * C;
     float *O = Oall + (int64_t)b * C * C;
     const bool bad = info[b] != 0;
     const int64_t s = (int64_t)blockIdx.y * 8 + threadIdx.y;
-    const int64_t t = (int64_t)blockIdx.x * 32 + threadIdx.x;
-    if (s >= C || t >= C) return;
+    const int64_t t0 = ((int64_t)blockIdx.x * 32 + threadIdx.x) * 4;
+    if (s >= C || t0 >= C) return;
     if (bad) {
-        if (t >= s) O[s * C + t] = (t == s) ? 1.0f : 0.0f;
-        if (t == s) udiag[(int64_t)b * C + t] = 1.0f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int64_t t = t0 + e;
+            if (t < C && t >= s) O[s * C + t] = (t == s) ? 1.0f : 0.0f;
+            if (t == s) udiag[(int64_t)b * C + t] = 1.0f;
+        }
         return;
     }
-    if (t > s) O[s * C + t] = -__fmul_rn(L[(C - 1 - s) * C + (C - 1 - t)], udiag[(int64_t)b * C + t]);
+    if (t0 + 3 <= s) return;                       // nothing of this quad lies above the diagonal
+    const float *ud = udiag + (int64_t)b * C;
+    if ((C & 3) == 0 && t0 > s) {
+        // whole quad above the diagonal: destination columns t0..t0+3 <- source columns C-1-t0 .. C-4-t0 (one float4)
+        const float4 src = *reinterpret_cast<const float4 *>(L + (C - 1 - s) * C + (C - 4 - t0));
+        const float4 d = *reinterpret_cast<const float4 *>(ud + t0);
+        *reinterpret_cast<float4 *>(O + s * C + t0) =
+            make_float4(-__fmul_rn(src.w, d.x), -__fmul_rn(src.z, d.y), -__fmul_rn(src.y, d.z), -__fmul_rn(src.x, d.w));
+        return;
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const int64_t t = t0 + e;
+        if (t < C && t > s) O[s * C + t] = -__fmul_rn(L[(C - 1 - s) * C + (C - 1 - t)], ud[t]);
+    }
 }
 
 __global__ void unit_diag_kernel(float *__restrict__ Oall, int64_t C) {
@@ -671,7 +691,7 @@ extern "C" int forge_chol_factor_batched(float *A, int nb, int64_t C, float *udi
     cudaStream_t st = (cudaStream_t)stream;
     const int vec = (C % 4 == 0) && ((uintptr_t)A % 16 == 0);
     launch_factor(A, nb, C, nullptr, udiag, info, (float *)ws, vec, st);
-    dim3 g2((unsigned)cdiv(C, 32), (unsigned)cdiv(C, 8), nb);
+    dim3 g2((unsigned)cdiv(C, 128), (unsigned)cdiv(C, 8), nb);
     rotate_scale_neg_kernel<<<g2, dim3(32, 8), 0, st>>>(A, A, C, info, udiag); FORGE_NOTE_LAUNCH();
     unit_diag_kernel<<<dim3((unsigned)cdiv(C, 256), nb), 256, 0, st>>>(A, C); FORGE_NOTE_LAUNCH();
     return check_launch("forge_chol_factor_batched");

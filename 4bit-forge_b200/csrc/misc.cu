@@ -43,10 +43,16 @@ __global__ void fp8_dequant_vec16(const uint8_t *__restrict__ w, const float *__
         const uint8_t *b = reinterpret_cast<const uint8_t *>(&raw);
         const float *srow = sinv + (o / so) * nI;
         __align__(16) __nv_bfloat16 r[16];
+        if (si % 16 == 0) {
+            const float s = srow[i0 / si];     // the 16 elements lie in one column tile
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-            const float s = srow[(i0 + e) / si];
-            r[e] = __float2bfloat16_rn(fp8_e4m3_to_f32(b[e]) * s);
+            for (int e = 0; e < 16; ++e) r[e] = __float2bfloat16_rn(fp8_e4m3_to_f32(b[e]) * s);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+                const float s = srow[(i0 + e) / si];
+                r[e] = __float2bfloat16_rn(fp8_e4m3_to_f32(b[e]) * s);
+            }
         }
         uint4 *dst = reinterpret_cast<uint4 *>(out + o * I + i0);
         dst[0] = reinterpret_cast<uint4 *>(r)[0];
@@ -574,8 +580,37 @@ extern "C" int forge_dequantize(const uint8_t *q, const float *scales, const flo
 }
 
 // --------------------------------------------------------------------------------------------
-// dense int4 packer: one thread per output word (8 codes)
+// dense int4 packer.  Fast path (C and gs multiples of 16, 16-byte aligned rows): one thread per 16 codes — one
+// 16-byte load, one zero point (the 16 codes share a group), two packed words in one 8-byte store.  General path:
+// one thread per output word (8 codes), every code with its own group index.
 // --------------------------------------------------------------------------------------------
+__global__ void pack_int4_vec16_kernel(const uint8_t *__restrict__ q, const float *__restrict__ qzeros, int64_t rows,
+                                       int C16, int gs16, int G, int32_t *__restrict__ packed) {
+    const int64_t total = rows * C16;      // 16-code chunks
+    for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < total;
+         w += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = w / C16;
+        const int j = (int)(w - r * C16);
+        const uint4 raw = reinterpret_cast<const uint4 *>(q)[w];
+        const int z = (int)__ldg(qzeros + r * G + j / gs16);
+        const uint32_t in[4] = {raw.x, raw.y, raw.z, raw.w};
+        uint32_t out[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            uint32_t acc = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int b = (int)((in[2 * h + (i >> 2)] >> (8 * (i & 3))) & 0xFFu);
+                // int8(code) - int8(zero) + 8, taken as a byte, shifted in: additions carry like pack_to_int32's sum
+                const uint32_t u = (uint32_t)(uint8_t)(int8_t)((int8_t)(int8_t)b - (int8_t)z + 8);
+                acc += u << (4 * i);
+            }
+            out[h] = acc;
+        }
+        reinterpret_cast<uint2 *>(packed)[w] = make_uint2(out[0], out[1]);
+    }
+}
+
 __global__ void pack_int4_kernel(const uint8_t *__restrict__ q, const float *__restrict__ qzeros, int64_t rows,
                                  int64_t C, int gs, int64_t G, int64_t CP, int32_t *__restrict__ packed,
                                  int aligned8) {
@@ -610,6 +645,14 @@ extern "C" int forge_pack_int4(const uint8_t *q, const float *qzeros, int64_t ro
     FORGE_REQUIRE(q && qzeros && packed, "null pointer");
     FORGE_REQUIRE(rows > 0 && C > 0 && gs > 0, "bad sizes");
     const int64_t G = cdiv(C, gs), CP = cdiv(C, 8);
+    if (C % 16 == 0 && gs % 16 == 0 && (uintptr_t)q % 16 == 0 && (uintptr_t)packed % 8 == 0 && C / 16 < (1 << 30)) {
+        const int64_t chunks = rows * (C / 16);
+        const int blocks = (int)imin64(cdiv(chunks, 256), 148 * 16);
+        pack_int4_vec16_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(q, qzeros, rows, (int)(C / 16), gs / 16, (int)G,
+                                                                         packed);
+        FORGE_NOTE_LAUNCH();
+        return check_launch("forge_pack_int4");
+    }
     const int aligned8 = (C % 8 == 0) && ((uintptr_t)q % 8 == 0);
     const int blocks = (int)imin64(cdiv(rows * CP, 256), 148 * 32);
     pack_int4_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(q, qzeros, rows, C, gs, G, CP, packed, aligned8); FORGE_NOTE_LAUNCH();

@@ -1168,57 +1168,108 @@ __global__ void perm_inverse_kernel(const int32_t *__restrict__ perm, int64_t C,
     if (i < C) perm_inv[(int64_t)u * C + perm[(int64_t)u * C + i]] = (int32_t)i;
 }
 
-// Wt[b][pos(c)][r] = float(W[b][r][c]); pos = perm_inv (identity when null).  32x32 tiles.
-__global__ void transpose_gather_kernel(const void *__restrict__ W, int dtype, int64_t R, int64_t C,
-                                        const int32_t *__restrict__ perm_inv, const int32_t *__restrict__ u_map,
-                                        float *__restrict__ Wt) {
-    __shared__ float tile[32][33];
+// Wt[b][pos(c)][r] = float(W[b][r][c]); pos = perm_inv (identity when null).  64 x 64 tiles, 256 threads: rows of W are
+// read in 8- or 16-byte pieces (four weights per thread), rows of Wt written as float4 (16 threads per 256-byte row).
+__global__ void __launch_bounds__(256) transpose_gather_kernel(const void *__restrict__ W, int dtype, int64_t R, int64_t C,
+                                                               const int32_t *__restrict__ perm_inv,
+                                                               const int32_t *__restrict__ u_map, float *__restrict__ Wt) {
+    __shared__ float tile[64][65];      // [r][c]
     const int b = blockIdx.z;
     const int u = u_map ? u_map[b] : b;
-    const int64_t c0 = (int64_t)blockIdx.x * 32, r0 = (int64_t)blockIdx.y * 32;
-    const int tx = threadIdx.x, ty = threadIdx.y;  // block (32, 8)
+    const int64_t c0 = (int64_t)blockIdx.x * 64, r0 = (int64_t)blockIdx.y * 64;
+    const int tid = threadIdx.x, q16 = tid & 15, row16 = tid >> 4;
+    const bool vec_in = (C % 4 == 0) && ((reinterpret_cast<uintptr_t>(W) & 15) == 0);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const int64_t r = r0 + ty + 8 * i, c = c0 + tx;
-        float v = 0.0f;
-        if (r < R && c < C) v = ld_as_f32(W, dtype, ((int64_t)b * R + r) * C + c);
-        tile[ty + 8 * i][tx] = v;
+        const int64_t r = r0 + row16 + 16 * i, c = c0 + 4 * q16;
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (r < R && c < C) {
+            const int64_t idx = ((int64_t)b * R + r) * C + c;
+            if (vec_in && c + 3 < C) {
+                if (dtype == FORGE_DTYPE_BF16) {
+                    const uint2 raw = *reinterpret_cast<const uint2 *>(reinterpret_cast<const __nv_bfloat16 *>(W) + idx);
+                    v[0] = __uint_as_float(raw.x << 16); v[1] = __uint_as_float(raw.x & 0xFFFF0000u);
+                    v[2] = __uint_as_float(raw.y << 16); v[3] = __uint_as_float(raw.y & 0xFFFF0000u);
+                } else {
+                    const float4 raw = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(W) + idx);
+                    v[0] = raw.x; v[1] = raw.y; v[2] = raw.z; v[3] = raw.w;
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (c + e < C) v[e] = ld_as_f32(W, dtype, idx + e);
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) tile[row16 + 16 * i][4 * q16 + e] = v[e];
     }
     __syncthreads();
+    const bool vec_out = (R % 4 == 0);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const int64_t c = c0 + ty + 8 * i, r = r0 + tx;
-        if (r < R && c < C) {
+        const int64_t c = c0 + row16 + 16 * i, r = r0 + 4 * q16;
+        if (c < C && r < R) {
             const int64_t pos = perm_inv ? (int64_t)perm_inv[(int64_t)u * C + c] : c;
-            Wt[((int64_t)b * C + pos) * R + r] = tile[tx][ty + 8 * i];
+            float *dst = Wt + ((int64_t)b * C + pos) * R + r;
+            const int cl = row16 + 16 * i;
+            if (vec_out && r + 3 < R) {
+                *reinterpret_cast<float4 *>(dst) =
+                    make_float4(tile[4 * q16][cl], tile[4 * q16 + 1][cl], tile[4 * q16 + 2][cl], tile[4 * q16 + 3][cl]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (r + e < R) dst[e] = tile[4 * q16 + e][cl];
+            }
         }
     }
 }
 
-// qweight[b][r][c] = qt[b][pos(c)][r]
-__global__ void untranspose_codes_kernel(const uint8_t *__restrict__ qt, int64_t R, int64_t C,
-                                         const int32_t *__restrict__ perm_inv, const int32_t *__restrict__ u_map,
-                                         uint8_t *__restrict__ qweight) {
-    __shared__ uint8_t tile[32][33];
+// qweight[b][r][c] = qt[b][pos(c)][r].  64 x 64 byte tiles, 256 threads, four codes (one 32-bit word) per access on both
+// sides.
+__global__ void __launch_bounds__(256) untranspose_codes_kernel(const uint8_t *__restrict__ qt, int64_t R, int64_t C,
+                                                                const int32_t *__restrict__ perm_inv,
+                                                                const int32_t *__restrict__ u_map,
+                                                                uint8_t *__restrict__ qweight) {
+    __shared__ uint8_t tile[64][68];    // [c][r]
     const int b = blockIdx.z;
     const int u = u_map ? u_map[b] : b;
-    const int64_t c0 = (int64_t)blockIdx.x * 32, r0 = (int64_t)blockIdx.y * 32;
-    const int tx = threadIdx.x, ty = threadIdx.y;
+    const int64_t c0 = (int64_t)blockIdx.x * 64, r0 = (int64_t)blockIdx.y * 64;
+    const int tid = threadIdx.x, q16 = tid & 15, row16 = tid >> 4;
+    const bool vec_in = (R % 4 == 0), vec_out = (C % 4 == 0);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const int64_t c = c0 + ty + 8 * i, r = r0 + tx;
-        uint8_t v = 0;
-        if (r < R && c < C) {
+        const int64_t c = c0 + row16 + 16 * i, r = r0 + 4 * q16;
+        uint32_t w = 0;
+        if (c < C && r < R) {
             const int64_t pos = perm_inv ? (int64_t)perm_inv[(int64_t)u * C + c] : c;
-            v = qt[((int64_t)b * C + pos) * R + r];
+            const uint8_t *src = qt + ((int64_t)b * C + pos) * R + r;
+            if (vec_in && r + 3 < R) {
+                w = *reinterpret_cast<const uint32_t *>(src);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (r + e < R) w |= (uint32_t)src[e] << (8 * e);
+            }
         }
-        tile[ty + 8 * i][tx] = v;
+        *reinterpret_cast<uint32_t *>(&tile[row16 + 16 * i][4 * q16]) = w;
     }
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const int64_t r = r0 + ty + 8 * i, c = c0 + tx;
-        if (r < R && c < C) qweight[((int64_t)b * R + r) * C + c] = tile[tx][ty + 8 * i];
+        const int64_t r = r0 + row16 + 16 * i, c = c0 + 4 * q16;
+        if (r < R && c < C) {
+            const int rl = row16 + 16 * i;
+            const uint32_t w = (uint32_t)tile[4 * q16][rl] | ((uint32_t)tile[4 * q16 + 1][rl] << 8) |
+                               ((uint32_t)tile[4 * q16 + 2][rl] << 16) | ((uint32_t)tile[4 * q16 + 3][rl] << 24);
+            uint8_t *dst = qweight + ((int64_t)b * R + r) * C + c;
+            if (vec_out && c + 3 < C) {
+                *reinterpret_cast<uint32_t *>(dst) = w;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (c + e < C) dst[e] = (uint8_t)(w >> (8 * e));
+            }
+        }
     }
 }
 
@@ -1360,8 +1411,8 @@ extern "C" int forge_gptq_solve_batched(const void *W, int w_dtype, int nb, int6
         FORGE_REQUIRE(nu > 0 && nu <= nb, "nu must be in [1, nb]");
         perm_inverse_kernel<<<dim3((unsigned)cdiv(C, 256), nu), 256, 0, st>>>(perm, C, perm_inv); FORGE_NOTE_LAUNCH();
     }
-    dim3 tgrid((unsigned)cdiv(C, 32), (unsigned)cdiv(R, 32), nb);
-    transpose_gather_kernel<<<tgrid, dim3(32, 8), 0, st>>>(W, w_dtype, R, C, perm_inv, u_map, Wt); FORGE_NOTE_LAUNCH();
+    dim3 tgrid((unsigned)cdiv(C, 64), (unsigned)cdiv(R, 64), nb);
+    transpose_gather_kernel<<<tgrid, 256, 0, st>>>(W, w_dtype, R, C, perm_inv, u_map, Wt); FORGE_NOTE_LAUNCH();
     SolveParams p{};
     p.Wt = Wt; p.E = Wt; p.U = U; p.uvec = udiag; p.u_map = u_map;
     p.scales = scales_t ? scales_t : scales; p.qzeros = scales_t ? qzeros_t : qzeros; p.meta_t = scales_t ? 1 : 0;
@@ -1379,6 +1430,6 @@ extern "C" int forge_gptq_solve_batched(const void *W, int w_dtype, int nb, int6
     }
     int rc = sparse14 ? launch_solve<0, true>(p, nb, status, st) : launch_solve<0, false>(p, nb, status, st);
     if (rc != FORGE_OK) return rc;
-    untranspose_codes_kernel<<<tgrid, dim3(32, 8), 0, st>>>(qt, R, C, perm_inv, u_map, qweight); FORGE_NOTE_LAUNCH();
+    untranspose_codes_kernel<<<tgrid, 256, 0, st>>>(qt, R, C, perm_inv, u_map, qweight); FORGE_NOTE_LAUNCH();
     return check_launch("forge_gptq_solve_batched");
 }
