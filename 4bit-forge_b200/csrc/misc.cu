@@ -318,23 +318,24 @@ __global__ void damp_kernel(const float *__restrict__ H, int64_t C, const int32_
     }
 }
 
-// One CTA per (output row i, matrix b): stage row perm[i] of H in shared memory, then emit
-// Hp[i, :] through the permutation, index-reversed, with the fix-ups and the damping applied.
+// One CTA per (four output rows i, matrix b): stage rows perm[i] of H in shared memory, then emit Hp[i, :] through
+// the permutation, index-reversed, with the fix-ups and the damping applied.  The per-column indices and flags
+// (permutation, dead channel, all-zero weight column) are fetched once per column and serve the four rows.
+constexpr int kGdRows = 4;
 __global__ void gather_damp_kernel(const float *__restrict__ H, int64_t C, const int32_t *__restrict__ perm,
                                    const uint8_t *__restrict__ pruned, const uint8_t *__restrict__ wzero,
                                    const int32_t *__restrict__ invalid, const float *__restrict__ damp,
                                    float *__restrict__ A, float *__restrict__ Hp_out) {
-    extern __shared__ float row[];
+    extern __shared__ float row[];     // [kGdRows][C]
     const int b = blockIdx.y;
-    const int64_t i = blockIdx.x;
+    const int64_t i0 = (int64_t)blockIdx.x * kGdRows;
     const float *Hb = H + (int64_t)b * C * C;
     const int32_t *pb = perm ? perm + (int64_t)b * C : nullptr;
     const uint8_t *prb = pruned ? pruned + (int64_t)b * C : nullptr;
     const uint8_t *wzb = wzero ? wzero + (int64_t)b * C : nullptr;
     const bool inv = invalid ? invalid[b] != 0 : false;
-    const int64_t pi = pb ? pb[i] : i;
-    // Fast path (the usual case): natural order and no dead channel / zero column anywhere in this matrix: a pure
-    // index reversal of the row with the damping on the diagonal, 16 bytes per access.
+    // Fast path (the usual case without activation order): natural order and no dead channel / zero column anywhere
+    // in this matrix: a pure index reversal of the rows with the damping on the diagonal, 16 bytes per access.
     if (!pb && (C & 3) == 0) {
         int flagged = inv ? 1 : 0;
         for (int64_t c = (int64_t)threadIdx.x * 16; c < C; c += (int64_t)blockDim.x * 16) {
@@ -347,43 +348,68 @@ __global__ void gather_damp_kernel(const float *__restrict__ H, int64_t C, const
         }
         if (!__syncthreads_or(flagged)) {
             const float dmp = damp[b];
-            const float4 *src = reinterpret_cast<const float4 *>(Hb + i * C);
-            float *Arow = A + (int64_t)b * C * C + (C - 1 - i) * C;
-            float *Hrow = Hp_out ? Hp_out + (int64_t)b * C * C + i * C : nullptr;
-            for (int64_t c4 = threadIdx.x; c4 < C / 4; c4 += blockDim.x) {
-                float4 v = src[c4];
-                const int64_t j = 4 * c4;
-                if (i >= j && i < j + 4) {
-                    const int k = (int)(i - j);
-                    if (k == 0) v.x += dmp; else if (k == 1) v.y += dmp; else if (k == 2) v.z += dmp; else v.w += dmp;
+            for (int rr = 0; rr < kGdRows; ++rr) {
+                const int64_t i = i0 + rr;
+                if (i >= C) break;
+                const float4 *src = reinterpret_cast<const float4 *>(Hb + i * C);
+                float *Arow = A + (int64_t)b * C * C + (C - 1 - i) * C;
+                float *Hrow = Hp_out ? Hp_out + (int64_t)b * C * C + i * C : nullptr;
+                for (int64_t c4 = threadIdx.x; c4 < C / 4; c4 += blockDim.x) {
+                    float4 v = src[c4];
+                    const int64_t j = 4 * c4;
+                    if (i >= j && i < j + 4) {
+                        const int k = (int)(i - j);
+                        if (k == 0) v.x += dmp; else if (k == 1) v.y += dmp; else if (k == 2) v.z += dmp; else v.w += dmp;
+                    }
+                    if (Hrow) *reinterpret_cast<float4 *>(Hrow + j) = v;
+                    *reinterpret_cast<float4 *>(Arow + (C - 4 - j)) = make_float4(v.w, v.z, v.y, v.x);
                 }
-                if (Hrow) *reinterpret_cast<float4 *>(Hrow + j) = v;
-                *reinterpret_cast<float4 *>(Arow + (C - 4 - j)) = make_float4(v.w, v.z, v.y, v.x);
             }
             return;
         }
     }
-    const bool row_dead = inv || (prb && prb[pi]);
-    const bool row_wz = wzb && wzb[i];
-    if (!row_dead && !row_wz) {
-        for (int64_t c = threadIdx.x; c < C; c += blockDim.x) row[c] = Hb[pi * C + c];
+    int64_t pi[kGdRows];
+    bool row_dead[kGdRows], row_wz[kGdRows], row_in[kGdRows];
+#pragma unroll
+    for (int rr = 0; rr < kGdRows; ++rr) {
+        const int64_t i = i0 + rr;
+        row_in[rr] = i < C;
+        pi[rr] = row_in[rr] ? (pb ? (int64_t)pb[i] : i) : 0;
+        row_dead[rr] = inv || (row_in[rr] && prb && prb[pi[rr]]);
+        row_wz[rr] = row_in[rr] && wzb && wzb[i];
+    }
+    const bool vec = (C & 3) == 0;
+#pragma unroll
+    for (int rr = 0; rr < kGdRows; ++rr) {
+        if (!row_in[rr] || row_dead[rr] || row_wz[rr]) continue;
+        const float *src = Hb + pi[rr] * C;
+        float *dst = row + (int64_t)rr * C;
+        if (vec) {
+            for (int64_t c4 = threadIdx.x; c4 < C / 4; c4 += blockDim.x)
+                reinterpret_cast<float4 *>(dst)[c4] = reinterpret_cast<const float4 *>(src)[c4];
+        } else {
+            for (int64_t c = threadIdx.x; c < C; c += blockDim.x) dst[c] = src[c];
+        }
     }
     __syncthreads();
     const float dmp = damp[b];
-    float *Arow = A + (int64_t)b * C * C + (C - 1 - i) * C;
-    float *Hrow = Hp_out ? Hp_out + (int64_t)b * C * C + i * C : nullptr;
     for (int64_t jo = threadIdx.x; jo < C; jo += blockDim.x) {
         const int64_t j = C - 1 - jo;  // output column jo of the reversed matrix <-> position j
-        float v;
-        if (row_wz || (wzb && wzb[j])) v = (i == j) ? 1.0f : 0.0f;
-        else {
-            const int64_t pj = pb ? pb[j] : j;
-            if (row_dead || (prb && prb[pj])) v = (pi == pj) ? 1.0f : 0.0f;
-            else v = row[pj];
+        const bool col_wz = wzb && wzb[j];
+        const int64_t pj = pb ? (int64_t)pb[j] : j;
+        const bool col_dead = prb && prb[pj];
+#pragma unroll
+        for (int rr = 0; rr < kGdRows; ++rr) {
+            if (!row_in[rr]) continue;
+            const int64_t i = i0 + rr;
+            float v;
+            if (row_wz[rr] || col_wz) v = (i == j) ? 1.0f : 0.0f;
+            else if (row_dead[rr] || col_dead) v = (pi[rr] == pj) ? 1.0f : 0.0f;
+            else v = row[(int64_t)rr * C + pj];
+            if (i == j) v += dmp;
+            A[(int64_t)b * C * C + (C - 1 - i) * C + jo] = v;
+            if (Hp_out) Hp_out[(int64_t)b * C * C + i * C + j] = v;
         }
-        if (i == j) v += dmp;
-        Arow[jo] = v;
-        if (Hrow) Hrow[j] = v;
     }
 }
 
@@ -392,16 +418,17 @@ extern "C" int forge_hessian_gather_damp(const float *H, int nb, int64_t C, cons
                                          float rel_damp, float *A, float *Hp_out, float *damp_out, void *stream) {
     FORGE_REQUIRE(H && A && damp_out, "null pointer");
     FORGE_REQUIRE(nb > 0 && C > 0, "empty batch");
-    FORGE_REQUIRE(C * 4 <= 200 * 1024, "C too large for the row staging buffer");
+    FORGE_REQUIRE(C * 4 * kGdRows <= 200 * 1024, "C too large for the row staging buffer");
     FORGE_REQUIRE(A != H, "A must not alias H");
     cudaStream_t st = (cudaStream_t)stream;
     damp_kernel<<<nb, 256, 0, st>>>(H, C, perm, pruned, wzero, invalid, rel_damp, damp_out); FORGE_NOTE_LAUNCH();
-    const size_t smem = (size_t)C * 4;
+    const size_t smem = (size_t)C * 4 * kGdRows;
     // the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute: set it on the device that is
     // current for this call (a process-wide "done" flag would leave a second GPU without it)
     cudaFuncSetAttribute(gather_damp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    gather_damp_kernel<<<dim3((unsigned)C, nb), 256, smem, st>>>(H, C, perm, pruned, wzero, invalid, damp_out, A,
-                                                                Hp_out); FORGE_NOTE_LAUNCH();
+    gather_damp_kernel<<<dim3((unsigned)cdiv(C, kGdRows), nb), 256, smem, st>>>(H, C, perm, pruned, wzero, invalid,
+                                                                              damp_out, A, Hp_out);
+    FORGE_NOTE_LAUNCH();
     return check_launch("forge_hessian_gather_damp");
 }
 

@@ -145,6 +145,58 @@ quant_grid_kernel(const void *__restrict__ Wv, int64_t rows, int64_t C, int64_t 
 }
 
 
+// Min-max grid only (no shrink-factor search), bf16 weights, groups of 128 columns that tile the row exactly: the
+// HBM-bound case of the layer path.  A lane reads four consecutive weights (8 bytes), so a warp reads a whole group in
+// one 256-byte access, and four groups are in flight per warp.  min / max do not depend on the order of the elements,
+// so the result is bit-identical to quant_grid_kernel's.
+__global__ void __launch_bounds__(256)
+minmax_grid_g128_bf16_kernel(const __nv_bfloat16 *__restrict__ W, int64_t n_groups, int bits, int symmetric,
+                             float *__restrict__ scales, float *__restrict__ qzeros) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps_total = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const int64_t warp_id = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const float maxq = (float)((1 << bits) - 1);
+    const uint2 *src = reinterpret_cast<const uint2 *>(W);
+    for (int64_t g0 = warp_id * 4; g0 < n_groups; g0 += warps_total * 4) {
+        uint2 raw[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            raw[k] = (g0 + k < n_groups) ? src[(g0 + k) * 32 + lane] : make_uint2(0u, 0u);
+        float mn[4], mx[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float a = __uint_as_float(raw[k].x << 16), b = __uint_as_float(raw[k].x & 0xFFFF0000u);
+            const float c = __uint_as_float(raw[k].y << 16), d = __uint_as_float(raw[k].y & 0xFFFF0000u);
+            mx[k] = fmaxf(fmaxf(a, b), fmaxf(c, d));
+            mn[k] = fminf(fminf(a, b), fminf(c, d));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                mx[k] = fmaxf(mx[k], __shfl_xor_sync(0xffffffffu, mx[k], o));
+                mn[k] = fminf(mn[k], __shfl_xor_sync(0xffffffffu, mn[k], o));
+            }
+        }
+        if (lane < 4 && g0 + lane < n_groups) {
+            const float hi = lane == 0 ? mx[0] : lane == 1 ? mx[1] : lane == 2 ? mx[2] : mx[3];
+            const float lo = lane == 0 ? mn[0] : lane == 1 ? mn[1] : lane == 2 ? mn[2] : mn[3];
+            float s, q0;
+            if (symmetric) {
+                const float amax = fmaxf(fabsf(lo), fabsf(hi));
+                s = fmaf(2.0f / maxq, amax, kEps);
+                q0 = 0.5f * (maxq + 1.0f);
+            } else {
+                s = __fadd_rn(__fdiv_rn(__fsub_rn(hi, lo), maxq), kEps);
+                const float q = rintf(__fdiv_rn(-lo, s));
+                q0 = fminf(fmaxf(q, 0.0f), maxq);
+            }
+            scales[g0 + lane] = s;
+            qzeros[g0 + lane] = q0;
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------------
 // Shrink-factor search, second layout: one THREAD per (group, candidate pair) instead of one warp per
 // group.  The per-candidate set-up (scale, reciprocal, zero) is then paid once per 128 elements instead
@@ -620,6 +672,14 @@ extern "C" int forge_quant_grid(const void *W, int w_dtype, int64_t rows, int64_
     FORGE_REQUIRE(rows > 0 && C > 0 && gs > 0 && bits >= 1 && bits <= 8, "bad sizes");
     FORGE_REQUIRE(n_cand == 0 || candidates, "candidates missing");
     FORGE_REQUIRE(w_dtype == FORGE_DTYPE_F32 || w_dtype == FORGE_DTYPE_BF16, "bad dtype");
+    if (n_cand == 0 && gs == 128 && C % 128 == 0 && w_dtype == FORGE_DTYPE_BF16 && (uintptr_t)W % 8 == 0) {
+        const int64_t n_groups = rows * (C / 128);
+        const int blocks = (int)imin64(cdiv(n_groups, 8 * 4), 148 * 16);
+        minmax_grid_g128_bf16_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16 *)W, n_groups, bits,
+                                                                               symmetric, scales, qzeros);
+        FORGE_NOTE_LAUNCH();
+        return check_launch("forge_quant_grid");
+    }
     return launch_grid<true>(W, w_dtype, rows, C, gs, bits, symmetric, candidates, n_cand, norm, scales, qzeros,
                              (cudaStream_t)stream);
 }
