@@ -322,6 +322,15 @@ __host__ __device__ __forceinline__ int syrk_tiles(int nti, int ntj) {
     return ntj * (ntj + 1) / 2 + (nti - ntj) * ntj;
 }
 
+// A 16-byte load the compiler must issue where it is written: the operand rows of four k-steps are requested together
+// BEFORE the first of them is split and staged; left to the scheduler the loads sink to their first use and every k-step
+// pays an L2 round trip.
+__device__ __forceinline__ float4 ldg128_here(const float *p) {
+    float4 v;
+    asm volatile("ld.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+    return v;
+}
+
 constexpr int kSyrkThreads = 160;
 constexpr int kSyrkStages = 4;
 constexpr int kSyrkStageBytes = 4 * forge::tc::kPieceBytes;   // Ahi, Alo, Bhi, Blo
@@ -391,8 +400,8 @@ __global__ void __launch_bounds__(kSyrkThreads, 3) chol_syrk_tc_kernel(float *__
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         const int64_t row = (int64_t)(half * 4 + d) * kKS + jA + 4 * h;
-                        ra[d][h] = a_ok ? *reinterpret_cast<const float4 *>(srcA + row * C) : make_float4(0.f, 0.f, 0.f, 0.f);
-                        if (!diag) rbv[d][h] = b_ok ? *reinterpret_cast<const float4 *>(srcB + row * C) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        ra[d][h] = a_ok ? ldg128_here(srcA + row * C) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (!diag) rbv[d][h] = b_ok ? ldg128_here(srcB + row * C) : make_float4(0.f, 0.f, 0.f, 0.f);
                     }
 #pragma unroll
                 for (int d = 0; d < 4; ++d) {

@@ -182,7 +182,9 @@ int forge_chol_inv_upper_batched(float *A, int nb, int64_t C, float *U, float *u
  * batches and must redo one expert (info > 0) with a larger damping, or a host application whose memory
  * manager forbids cudaMalloc (which would also stall its other streams).
  * C <= forge_noalloc_max_c() (4096), else FORGE_ERR_UNSUPPORTED.  The first call on a device looks up the
- * array's address (cudaGetSymbolAddress): make that call outside of stream capture.  All calls on a device
+ * array's address (cudaGetSymbolAddress): make that call outside of stream capture, and make it early — the CUDA
+ * runtime loads the library's code lazily, so the 2 MiB array itself is created on a device by that first call;
+ * a warm-up call at start-up, while device memory is still free, guarantees it exists when memory has run out.  All calls on a device
  * share the array, so calls that overlap on the GPU (different streams) race; calls on one stream are safe,
  * and nothing in the array needs clearing between calls. */
 int64_t forge_noalloc_max_c(void);
