@@ -34,7 +34,7 @@ UNIT = "experts/s"
 # DRAM bytes of forge_gptq_solve_batched per expert (gate + up + down launches), from ncu captures of small cuts of
 # the same matrix shapes (the full layers are too large to capture; traffic is per expert, so it scales with the
 # expert count).  The summaries and their commands are under profiles/.
-SOLVER_TRAFFIC_PER_EXPERT = {"qwen3_30b_a3b": 150.4e6}
+SOLVER_TRAFFIC_PER_EXPERT = {"deepseek_v3": 4.97e9}    # 84.5 GB over the 3 launches of a 17-expert cut
 
 # quantisation recipe per benchmark configuration
 RECIPES = {
