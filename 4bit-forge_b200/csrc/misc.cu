@@ -2,6 +2,7 @@
 // preparation (NaN scan, pruning, permutation gather + damping), code de-quantisation, and the
 // two bit-exact packers.  All are plain coalesced SIMT kernels; none is GEMM-shaped.
 #include "common.cuh"
+#include "tcgen05.cuh"
 #include <stdarg.h>
 
 namespace forge {
@@ -318,15 +319,20 @@ __global__ void damp_kernel(const float *__restrict__ H, int64_t C, const int32_
     }
 }
 
-// One CTA per (four output rows i, matrix b): stage rows perm[i] of H in shared memory, then emit Hp[i, :] through
-// the permutation, index-reversed, with the fix-ups and the damping applied.  The per-column indices and flags
-// (permutation, dead channel, all-zero weight column) are fetched once per column and serve the four rows.
-constexpr int kGdRows = 4;
+// One CTA per (three output rows i, matrix b): stage rows perm[i] of H in shared memory, then emit Hp[i, :] through
+// the permutation, index-reversed, with the fix-ups and the damping applied.  The per-column source index and flags
+// (permutation, dead channel, all-zero weight column) are gathered ONCE per CTA into a fourth shared-memory row, with
+// all their (dependent: permutation -> dead flag) global loads in flight together and beside the row loads; the output
+// loop then touches shared memory only.  (With the loads inside the output loop every column paid two L2 round trips
+// in sequence: the kernel ran at 0.3 of the HBM roofline.)
+constexpr int kGdRows = 3;
 __global__ void gather_damp_kernel(const float *__restrict__ H, int64_t C, const int32_t *__restrict__ perm,
                                    const uint8_t *__restrict__ pruned, const uint8_t *__restrict__ wzero,
                                    const int32_t *__restrict__ invalid, const float *__restrict__ damp,
                                    float *__restrict__ A, float *__restrict__ Hp_out) {
-    extern __shared__ float row[];     // [kGdRows][C]
+    extern __shared__ __align__(16) float row[];     // [kGdRows][C] rows, then [C] column codes
+    __shared__ __align__(8) uint64_t gd_bar;
+    __shared__ int gd_abort;
     const int b = blockIdx.y;
     const int64_t i0 = (int64_t)blockIdx.x * kGdRows;
     const float *Hb = H + (int64_t)b * C * C;
@@ -378,26 +384,98 @@ __global__ void gather_damp_kernel(const float *__restrict__ H, int64_t C, const
         row_dead[rr] = inv || (row_in[rr] && prb && prb[pi[rr]]);
         row_wz[rr] = row_in[rr] && wzb && wzb[i];
     }
+    // The rows come in by bulk copies that one thread issues (the whole 3 x 4C bytes of a CTA in flight at once, at
+    // no register cost; per-thread loads kept ~16 KB per CTA in flight and the kernel at 0.3 of the HBM roofline)
+    // while all threads gather the column codes.
     const bool vec = (C & 3) == 0;
+    const uint32_t bar = forge::tc::smem_u32(&gd_bar);
+    if (vec) {
+        if (threadIdx.x == 0) {
+            gd_abort = 0;
+            forge::tc::mbar_init(bar, 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            uint32_t bytes = 0;
 #pragma unroll
-    for (int rr = 0; rr < kGdRows; ++rr) {
-        if (!row_in[rr] || row_dead[rr] || row_wz[rr]) continue;
-        const float *src = Hb + pi[rr] * C;
-        float *dst = row + (int64_t)rr * C;
-        if (vec) {
-            for (int64_t c4 = threadIdx.x; c4 < C / 4; c4 += blockDim.x)
-                reinterpret_cast<float4 *>(dst)[c4] = reinterpret_cast<const float4 *>(src)[c4];
-        } else {
-            for (int64_t c = threadIdx.x; c < C; c += blockDim.x) dst[c] = src[c];
+            for (int rr = 0; rr < kGdRows; ++rr)
+                if (row_in[rr] && !row_dead[rr] && !row_wz[rr]) bytes += (uint32_t)(C * 4);
+            forge::tc::mbar_arrive_expect_tx(bar, bytes);
+            constexpr uint32_t kPiece = 8192;
+#pragma unroll
+            for (int rr = 0; rr < kGdRows; ++rr) {
+                if (!row_in[rr] || row_dead[rr] || row_wz[rr]) continue;
+                const char *src = reinterpret_cast<const char *>(Hb + pi[rr] * C);
+                const uint32_t dst = forge::tc::smem_u32(row + (int64_t)rr * C);
+                for (uint32_t off = 0; off < (uint32_t)(C * 4); off += kPiece) {
+                    const uint32_t n = min(kPiece, (uint32_t)(C * 4) - off);
+                    forge::tc::bulk_copy_g2s(dst + off, src + off, n, bar);
+                }
+            }
         }
     }
-    __syncthreads();
+    // column codes: source column pj in the low 30 bits, bit 31 = all-zero weight column at position j, bit 30 = dead
+    // channel pj
+    uint32_t *code = reinterpret_cast<uint32_t *>(row + (int64_t)kGdRows * C);
+    for (int64_t j = threadIdx.x; j < C; j += blockDim.x) {
+        const uint32_t pj = pb ? (uint32_t)__ldg(pb + j) : (uint32_t)j;
+        uint32_t cw = pj;
+        if (wzb && __ldg(wzb + j)) cw |= 0x80000000u;
+        if (prb && __ldg(prb + pj)) cw |= 0x40000000u;
+        code[j] = cw;
+    }
+    bool by_hand = !vec;
+    if (vec && !forge::tc::mbar_wait(bar, 0, &gd_abort)) by_hand = true;   // the wait is bounded; plain loads then
+    if (__syncthreads_or(by_hand ? 1 : 0)) {
+#pragma unroll
+        for (int rr = 0; rr < kGdRows; ++rr) {
+            if (!row_in[rr] || row_dead[rr] || row_wz[rr]) continue;
+            const float *src = Hb + pi[rr] * C;
+            float *dst = row + (int64_t)rr * C;
+            for (int64_t c = threadIdx.x; c < C; c += blockDim.x) dst[c] = src[c];
+        }
+        if (vec) {   // bulk copies may still be landing (with the same bytes): give them one more bounded wait
+            volatile int again = 0;
+            forge::tc::mbar_wait(bar, 0, &again);
+        }
+        __syncthreads();
+    }
     const float dmp = damp[b];
+    if (vec && !Hp_out) {
+        // four consecutive output columns per thread: one 16-byte read of the codes, one 16-byte store per row
+        for (int64_t jo = (int64_t)threadIdx.x * 4; jo < C; jo += (int64_t)blockDim.x * 4) {
+            const int64_t jlo = C - 4 - jo;   // positions jlo+3, jlo+2, jlo+1, jlo <-> output columns jo .. jo+3
+            const uint4 cq = *reinterpret_cast<const uint4 *>(code + jlo);
+            const uint32_t cws[4] = {cq.w, cq.z, cq.y, cq.x};
+#pragma unroll
+            for (int rr = 0; rr < kGdRows; ++rr) {
+                if (!row_in[rr]) continue;
+                const int64_t i = i0 + rr;
+                float v[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int64_t j = jlo + 3 - e;
+                    const uint32_t cw = cws[e];
+                    const int64_t pj = (int64_t)(cw & 0x3FFFFFFFu);
+                    float x;
+                    if (row_wz[rr] || (cw & 0x80000000u)) x = (i == j) ? 1.0f : 0.0f;
+                    else if (row_dead[rr] || (cw & 0x40000000u)) x = (pi[rr] == pj) ? 1.0f : 0.0f;
+                    else x = row[(int64_t)rr * C + pj];
+                    if (i == j) x += dmp;
+                    v[e] = x;
+                }
+                *reinterpret_cast<float4 *>(A + (int64_t)b * C * C + (C - 1 - i) * C + jo) =
+                    make_float4(v[0], v[1], v[2], v[3]);
+            }
+        }
+        return;
+    }
     for (int64_t jo = threadIdx.x; jo < C; jo += blockDim.x) {
         const int64_t j = C - 1 - jo;  // output column jo of the reversed matrix <-> position j
-        const bool col_wz = wzb && wzb[j];
-        const int64_t pj = pb ? (int64_t)pb[j] : j;
-        const bool col_dead = prb && prb[pj];
+        const uint32_t cw = code[j];
+        const bool col_wz = (cw & 0x80000000u) != 0u, col_dead = (cw & 0x40000000u) != 0u;
+        const int64_t pj = (int64_t)(cw & 0x3FFFFFFFu);
 #pragma unroll
         for (int rr = 0; rr < kGdRows; ++rr) {
             if (!row_in[rr]) continue;
@@ -413,16 +491,165 @@ __global__ void gather_damp_kernel(const float *__restrict__ H, int64_t C, const
     }
 }
 
+// The streaming form of the gather for permuted matrices (C a multiple of 4, no Hp output): persistent CTAs, each
+// walking a contiguous run of (matrix, group of R rows) items.  The column codes of a matrix are gathered once per
+// run of items of that matrix; the rows of item n+1 arrive by bulk copies while item n is written, so every SM keeps
+// 4RC bytes of reads in flight behind its stores.
+constexpr int kGsThreads = 512;
+constexpr int kGsMaxRows = 12;
+__global__ void __launch_bounds__(kGsThreads, 1)
+gather_damp_stream_kernel(const float *__restrict__ H, int64_t C, const int32_t *__restrict__ perm,
+                          const uint8_t *__restrict__ pruned, const uint8_t *__restrict__ wzero,
+                          const int32_t *__restrict__ invalid, const float *__restrict__ damp,
+                          float *__restrict__ A, int R, int64_t n_groups, int64_t total_items) {
+    extern __shared__ __align__(16) float gs_smem[];   // [C] codes, then [2][R][C] rows
+    __shared__ __align__(8) uint64_t gs_bar[2];
+    __shared__ int gs_abort;
+    uint32_t *code = reinterpret_cast<uint32_t *>(gs_smem);
+    float *rows = gs_smem + C;
+    const int64_t per = (total_items + gridDim.x - 1) / gridDim.x;
+    const int64_t it0 = (int64_t)blockIdx.x * per, it1 = min(total_items, it0 + per);
+    if (it0 >= it1) return;
+    if (threadIdx.x == 0) {
+        gs_abort = 0;
+        forge::tc::mbar_init(forge::tc::smem_u32(&gs_bar[0]), 1);
+        forge::tc::mbar_init(forge::tc::smem_u32(&gs_bar[1]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    int64_t cur_b = -1;
+    // code word of row position i of matrix b: source row in the low 30 bits, bit 31 = all-zero weight column at i,
+    // bit 30 = dead channel (or a matrix flagged invalid): either bit means "nothing to load, an identity row"
+    auto row_code = [&](int64_t b, int64_t i, bool inv) -> uint32_t {
+        uint32_t cw;
+        if (b == cur_b) cw = code[i];
+        else {
+            const uint32_t pi = (uint32_t)perm[b * C + i];
+            cw = pi;
+            if (wzero && wzero[b * C + i]) cw |= 0x80000000u;
+            if (pruned && pruned[b * C + pi]) cw |= 0x40000000u;
+        }
+        return inv ? (cw | 0x40000000u) : cw;
+    };
+    // thread 0: start the row copies of item `it` into buffer `s`
+    auto issue = [&](int64_t it, int s) {
+        const int64_t b = it / n_groups, g = it - b * n_groups;
+        const bool inv = invalid ? invalid[b] != 0 : false;
+        const float *Hb = H + b * C * C;
+        const uint32_t bar = forge::tc::smem_u32(&gs_bar[s]);
+        uint32_t bytes = 0;
+        constexpr uint32_t kPiece = 8192;
+        for (int rr = 0; rr < R; ++rr) {
+            const int64_t i = g * R + rr;
+            if (i >= C) break;
+            const uint32_t cw = row_code(b, i, inv);
+            if (cw & 0xC0000000u) continue;
+            const char *src = reinterpret_cast<const char *>(Hb + (int64_t)cw * C);
+            const uint32_t dst = forge::tc::smem_u32(rows + ((int64_t)s * R + rr) * C);
+            for (uint32_t off = 0; off < (uint32_t)(C * 4); off += kPiece)
+                forge::tc::bulk_copy_g2s(dst + off, src + off, min(kPiece, (uint32_t)(C * 4) - off), bar);
+            bytes += (uint32_t)(C * 4);
+        }
+        // the phase completes when this arrival AND the announced bytes are in (the byte count may run ahead of its
+        // announcement)
+        forge::tc::mbar_arrive_expect_tx(bar, bytes);
+    };
+    if (threadIdx.x == 0) issue(it0, 0);
+    for (int64_t it = it0; it < it1; ++it) {
+        const int s = (int)((it - it0) & 1);
+        const uint32_t parity = (uint32_t)(((it - it0) >> 1) & 1);
+        const int64_t b = it / n_groups, g = it - b * n_groups;
+        if (b != cur_b) {
+            // every thread has left the previous item's output loop (the barrier that ends an iteration)
+            const int32_t *pb = perm + b * C;
+            const uint8_t *prb = pruned ? pruned + b * C : nullptr;
+            const uint8_t *wzb = wzero ? wzero + b * C : nullptr;
+            for (int64_t j = threadIdx.x; j < C; j += blockDim.x) {
+                const uint32_t pj = (uint32_t)__ldg(pb + j);
+                uint32_t cw = pj;
+                if (wzb && __ldg(wzb + j)) cw |= 0x80000000u;
+                if (prb && __ldg(prb + pj)) cw |= 0x40000000u;
+                code[j] = cw;
+            }
+            __syncthreads();
+            cur_b = b;
+        }
+        if (threadIdx.x == 0 && it + 1 < it1) issue(it + 1, s ^ 1);
+        const bool inv = invalid ? invalid[b] != 0 : false;
+        const float dmp = damp[b];
+        float *buf = rows + (int64_t)s * R * C;
+        const bool ok = forge::tc::mbar_wait(forge::tc::smem_u32(&gs_bar[s]), parity, &gs_abort);
+        if (__syncthreads_or(ok ? 0 : 1)) {
+            // a bounded wait ran out: one more bounded wait, so that no copy into this buffer is left in flight, then
+            // fetch this item's rows by plain loads
+            volatile int again = 0;
+            forge::tc::mbar_wait(forge::tc::smem_u32(&gs_bar[s]), parity, &again);
+            for (int rr = 0; rr < R; ++rr) {
+                const int64_t i = g * R + rr;
+                if (i >= C) break;
+                const uint32_t cw = row_code(b, i, inv);
+                if (cw & 0xC0000000u) continue;
+                const float *src = H + b * C * C + (int64_t)cw * C;
+                for (int64_t c = threadIdx.x; c < C; c += blockDim.x) buf[(int64_t)rr * C + c] = src[c];
+            }
+            __syncthreads();
+        }
+        for (int64_t jo = (int64_t)threadIdx.x * 4; jo < C; jo += (int64_t)blockDim.x * 4) {
+            const int64_t jlo = C - 4 - jo;   // positions jlo+3 .. jlo <-> output columns jo .. jo+3
+            const uint4 cq = *reinterpret_cast<const uint4 *>(code + jlo);
+            const uint32_t cws[4] = {cq.w, cq.z, cq.y, cq.x};
+            for (int rr = 0; rr < R; ++rr) {
+                const int64_t i = g * R + rr;
+                if (i >= C) break;
+                const uint32_t cwi = code[i] | (inv ? 0x40000000u : 0u);
+                const bool row_wz = (cwi & 0x80000000u) != 0u, row_dead = (cwi & 0x40000000u) != 0u;
+                const uint32_t pi = cwi & 0x3FFFFFFFu;
+                const float *row = buf + (int64_t)rr * C;
+                float v[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int64_t j = jlo + 3 - e;
+                    const uint32_t cw = cws[e];
+                    const uint32_t pj = cw & 0x3FFFFFFFu;
+                    float x;
+                    if (row_wz || (cw & 0x80000000u)) x = (i == j) ? 1.0f : 0.0f;
+                    else if (row_dead || (cw & 0x40000000u)) x = (pi == pj) ? 1.0f : 0.0f;
+                    else x = row[pj];
+                    if (i == j) x += dmp;
+                    v[e] = x;
+                }
+                *reinterpret_cast<float4 *>(A + b * C * C + (C - 1 - i) * C + jo) = make_float4(v[0], v[1], v[2], v[3]);
+            }
+        }
+        __syncthreads();   // the buffer and (at a change of matrix) the code table are free again
+    }
+}
+
 extern "C" int forge_hessian_gather_damp(const float *H, int nb, int64_t C, const int32_t *perm,
                                          const uint8_t *pruned, const uint8_t *wzero, const int32_t *invalid,
                                          float rel_damp, float *A, float *Hp_out, float *damp_out, void *stream) {
     FORGE_REQUIRE(H && A && damp_out, "null pointer");
     FORGE_REQUIRE(nb > 0 && C > 0, "empty batch");
-    FORGE_REQUIRE(C * 4 * kGdRows <= 200 * 1024, "C too large for the row staging buffer");
+    FORGE_REQUIRE(C * 4 * (kGdRows + 1) <= 200 * 1024, "C too large for the row staging buffer");
     FORGE_REQUIRE(A != H, "A must not alias H");
+    FORGE_REQUIRE(C < (1 << 30), "C too large for the column codes");
     cudaStream_t st = (cudaStream_t)stream;
     damp_kernel<<<nb, 256, 0, st>>>(H, C, perm, pruned, wzero, invalid, rel_damp, damp_out); FORGE_NOTE_LAUNCH();
-    const size_t smem = (size_t)C * 4 * kGdRows;
+    const int64_t fit = ((int64_t)216 * 1024 / (C * 4) - 1) / 2;    // rows per buffer with codes + two buffers resident
+    if (perm && !Hp_out && (C & 3) == 0 && fit >= 1) {
+        const int R = (int)(fit < kGsMaxRows ? fit : (int64_t)kGsMaxRows);
+        int dev = 0, sms = 148;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const int64_t n_groups = cdiv(C, (int64_t)R), total = n_groups * nb;
+        const size_t smem_stream = (size_t)C * 4 * (2 * R + 1);
+        cudaFuncSetAttribute(gather_damp_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 216 * 1024);
+        gather_damp_stream_kernel<<<(unsigned)(total < sms ? total : (int64_t)sms), kGsThreads, smem_stream, st>>>(
+            H, C, perm, pruned, wzero, invalid, damp_out, A, R, n_groups, total);
+        FORGE_NOTE_LAUNCH();
+        return check_launch("forge_hessian_gather_damp");
+    }
+    const size_t smem = (size_t)C * 4 * (kGdRows + 1);
     // the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute: set it on the device that is
     // current for this call (a process-wide "done" flag would leave a second GPU without it)
     cudaFuncSetAttribute(gather_damp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
