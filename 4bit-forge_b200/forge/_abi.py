@@ -63,6 +63,8 @@ _PROTOS = {
     "forge_pack_int4": (_c_int, [_ptr, _ptr, _c_i64, _c_i64, _c_int, _ptr, _ptr]),
     "forge_pack_sparse14": (_c_int, [_ptr, _ptr, _ptr, _c_i64, _c_i64, _ptr, _ptr]),
     "forge_sparse14_gemm": (_c_int, [_ptr, _ptr, _c_i64, _c_i64, _c_i64, _c_i64, _ptr, _ptr]),
+    "forge_sparse14_moe_w13_swiglu": (_c_int, [_ptr, _ptr, _c_i64, _c_i64, _ptr, _ptr, _ptr, _c_int, _c_i64, _c_i64, _c_i64, _ptr, _ptr]),
+    "forge_sparse14_moe_w2": (_c_int, [_ptr, _ptr, _c_i64, _c_i64, _ptr, _ptr, _ptr, _c_int, _c_i64, _c_i64, _c_i64, _ptr, _ptr]),
 }
 
 _lib = None

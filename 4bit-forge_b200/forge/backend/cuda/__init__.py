@@ -87,5 +87,26 @@ class _Kernels:
             w = w.view(torch.int64)
         return ops.sparse14_gemm(w, X)
 
+    @staticmethod
+    def _grouped_args(W, X, offsets, U):
+        if not (W.dim() == 4 and W.size(3) == 2):
+            raise RuntimeError("W must be [E, G2, R, 2]")
+        if X.dim() != 2 or X.dtype != torch.bfloat16:
+            raise RuntimeError("X must be bfloat16 [N, C]")
+        w = W.contiguous()
+        return (w if w.dtype == torch.int64 else w.view(torch.int64)), X, offsets, U
+
+    @staticmethod
+    def sparsegptq14_grouped_gemm_w13(W13, X, offsets, U):
+        """fused_moe_usp14w4a16_gemm.cu:1028-1084 — W13 [E, G2, 2I, 2] uint64, X bf16 [N, H] sorted by expert,
+        offsets int64 [E+1], U int32 active expert ids -> X2 bf16 [N, I] = silu(gate) * up."""
+        return ops.sparse14_moe_w13_swiglu(*_Kernels._grouped_args(W13, X, offsets, U))
+
+    @staticmethod
+    def sparsegptq14_grouped_gemm_w2(W2, X2, offsets, U):
+        """fused_moe_usp14w4a16_gemm.cu:1086-1140 — W2 [E, G2, H, 2] uint64, X2 bf16 [N, I] sorted by expert -> Y bf16
+        [N, H]."""
+        return ops.sparse14_moe_w2(*_Kernels._grouped_args(W2, X2, offsets, U))
+
 
 kernels = _Kernels()

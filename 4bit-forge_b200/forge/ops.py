@@ -299,3 +299,37 @@ def sparse14_gemm(wpair: torch.Tensor, X: torch.Tensor) -> torch.Tensor:
     Y = torch.empty((N, R), dtype=torch.bfloat16, device=_dev(X))
     call("forge_sparse14_gemm", ptr(wpair.contiguous()), ptr(X), X.stride(0), N, R, C, ptr(Y), stream_ptr())
     return Y
+
+
+def _sparse14_moe(entry: str, W: torch.Tensor, X: torch.Tensor, offsets: torch.Tensor, active: torch.Tensor,
+                  token_idx, n_out: int, swiglu: bool) -> torch.Tensor:
+    assert X.dtype == torch.bfloat16 and X.dim() == 2 and W.dim() == 4 and W.shape[3] == 2
+    E, G2, R, _ = W.shape
+    C = X.shape[1]
+    if G2 != (C + 63) // 64:
+        raise RuntimeError(f"Wpair G2 mismatch: got {G2} expected {(C + 63) // 64}")
+    if offsets.numel() != E + 1:
+        raise RuntimeError("offsets must hold E + 1 entries")
+    X = X.contiguous()
+    offsets = offsets.to(torch.int64).contiguous()
+    active = active.to(torch.int32).contiguous()
+    if token_idx is not None:
+        token_idx = token_idx.to(torch.int32).contiguous()
+        assert token_idx.numel() >= n_out
+    out = torch.zeros((n_out, R // 2 if swiglu else R), dtype=torch.bfloat16, device=_dev(X))
+    call(entry, ptr(W.contiguous()), ptr(X), X.stride(0), X.shape[0], ptr(token_idx), ptr(offsets), ptr(active),
+         int(active.numel()), n_out, R, C, ptr(out), stream_ptr())
+    return out
+
+
+def sparse14_moe_w13_swiglu(W13, X, offsets, active, token_idx=None, n_out=None) -> torch.Tensor:
+    """X2[m, :] = silu(gate) * up of the expert that owns permuted position m (forge_sparse14_moe_w13_swiglu).
+    W13 [E, G2, 2I, 2] Wpair words, X bf16 [rows, H]; rows of inactive experts stay zero."""
+    return _sparse14_moe("forge_sparse14_moe_w13_swiglu", W13, X, offsets, active, token_idx,
+                         X.shape[0] if n_out is None else int(n_out), True)
+
+
+def sparse14_moe_w2(W2, X2, offsets, active, token_idx=None, n_out=None) -> torch.Tensor:
+    """Y[m, :] = X2[m, :] @ What_e^T for the expert e that owns permuted position m (forge_sparse14_moe_w2)."""
+    return _sparse14_moe("forge_sparse14_moe_w2", W2, X2, offsets, active, token_idx,
+                         X2.shape[0] if n_out is None else int(n_out), False)

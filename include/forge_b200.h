@@ -297,6 +297,24 @@ int forge_pack_sparse14(const uint8_t *q, const uint32_t *M, const float *scales
 int forge_sparse14_gemm(const uint64_t *wpair, const void *X_bf16, int64_t ldx, int64_t N, int64_t R, int64_t C,
                         void *Y_bf16, void *stream);
 
+/* Grouped forms for a mixture-of-experts layer.  The routed rows are sorted by expert: permuted positions
+ * [offsets[e], offsets[e+1]) (int64, device) belong to expert e; `active` (int32 [n_active], device) lists the experts to
+ * run; w13 / w2 hold all experts' packets, [E, ceil(C/64), R, 2] uint64.  `token_idx` (int32 [N], device) maps a permuted
+ * position to its row of X [x_rows, ldx]; NULL means X is already in permuted order.  Claims beyond N and rows outside X
+ * are clipped / read as zeros.
+ *   forge_sparse14_moe_w13_swiglu: R = 2 I with the gate rows first;  X2[m, i] = bf16( silu(g) * u ), g and u the fp32 sums
+ *     of rows i and I + i, silu(g) = g / (1 + expf(-g)); X2 bf16 [N, I].  Interface and arithmetic of
+ *     kernels.sparsegptq14_grouped_gemm_w13 (usp14w4a16sym_sm80_fused_moe_w13_gemm,
+ *     forge/backend/cuda/fused_moe_usp14w4a16_gemm.cu:398-439, :722-723, :1028-1084).
+ *   forge_sparse14_moe_w2: Y[m, r] = bf16( sum ), bit-identical to forge_sparse14_gemm run per expert; Y bf16 [N, R].
+ *     Replaces kernels.sparsegptq14_grouped_gemm_w2 (:1086-1140). */
+int forge_sparse14_moe_w13_swiglu(const uint64_t *w13, const void *X_bf16, int64_t ldx, int64_t x_rows,
+                                  const int32_t *token_idx, const int64_t *offsets, const int32_t *active, int n_active,
+                                  int64_t N, int64_t R, int64_t C, void *X2_bf16, void *stream);
+int forge_sparse14_moe_w2(const uint64_t *w2, const void *X2_bf16, int64_t ldx, int64_t x_rows, const int32_t *token_idx,
+                          const int64_t *offsets, const int32_t *active, int n_active, int64_t N, int64_t R, int64_t C,
+                          void *Y_bf16, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -386,3 +386,71 @@ def mxfp4_dequant(blocks_u8: torch.Tensor, scales_u8: torch.Tensor):
         sc = np.where(e == 0, np.float32(2.0 ** -23), np.power(np.float32(2.0), (e - 127).astype(np.float32))).astype(np.float32)
     out = (vals * sc[..., None]).astype(np.float32).reshape(*vals.shape[:-2], vals.shape[-2] * 32)
     return torch.from_numpy(np.ascontiguousarray(np.swapaxes(out, -1, -2)))
+
+
+def wpair_to_dense(wpair: torch.Tensor, C: int) -> torch.Tensor:
+    """The weights a Wpair tensor [G2,R,2] encodes, fp32 [R,C] (exact: bf16 scale times an integer in [-8, 7]); word
+    layout of bitpacking_sparsegptq14.cu:58-107 as consumed by sparse14_gemm.cu:96-131."""
+    G2, R, _ = wpair.shape
+    w = wpair.contiguous().view(torch.int64)
+    out = torch.zeros((R, G2 * 64), dtype=torch.float32)
+    rows = torch.arange(R)
+    for g2 in range(G2):
+        for half in range(2):
+            u = w[g2, :, half]
+            qw = u & 0xFFFFFFFF
+            idx = (u >> 32) & 0xFFFF
+            sc_bits = ((u >> 48) & 0xFFFF).to(torch.int32) << 16
+            scale = sc_bits.view(torch.float32)
+            for i in range(8):
+                ch = g2 * 64 + half * 32 + 4 * i + ((idx >> (2 * i)) & 3)
+                val = (((qw >> (4 * i)) & 0xF).to(torch.float32) - 8.0) * scale
+                out[rows, ch] = val
+    return out[:, :C].contiguous()
+
+
+def sparse14_grouped_w13(W13, X, offsets, active):
+    """usp14w4a16sym_sm80_fused_moe_w13_gemm's contract (fused_moe_usp14w4a16_gemm.cu:398-439, :722-723, :1028-1084):
+    X rows sorted by expert, gate rows then up rows, X2 = bf16(silu(g) * u) from unrounded sums.  The sums are taken
+    in fp64 here (the tensor-core summation order of that kernel is unspecified)."""
+    E, G2, R, _ = W13.shape
+    N, C = X.shape
+    I = R // 2
+    X2 = torch.zeros((N, I), dtype=torch.bfloat16)
+    for e in [int(a) for a in active]:
+        s, t = int(offsets[e]), int(offsets[e + 1])
+        if t <= s:
+            continue
+        Wd = wpair_to_dense(W13[e], C).double()
+        y = X[s:t].double() @ Wd.T
+        g, u = y[:, :I], y[:, I:]
+        X2[s:t] = ((g / (1.0 + torch.exp(-g))) * u).to(torch.bfloat16)
+    return X2
+
+
+def sparse14_moe_runtime_forward(w13, w2, hidden_states, topk_ids, topk_weights, chunk_m=256):
+    """Sparse14MoERuntime.forward, sparse14_gemm.py:32-65, with the permutation written out (stable sort of the
+    (token, slot) pairs by expert = moe_permute) and the weighted un-permute as an fp32 sum rounded once."""
+    T, H = hidden_states.shape
+    K = topk_ids.shape[1]
+    E = w13.shape[0]
+    I = w13.shape[2] // 2
+    flat = topk_ids.reshape(-1).to(torch.int64)
+    order = torch.argsort(flat, stable=True)
+    tok = order // K
+    hs_perm = hidden_states[tok]
+    counts = torch.bincount(flat, minlength=E)
+    offs = torch.cat([torch.zeros(1, dtype=torch.int64), counts.cumsum(0)])
+    out_perm = torch.zeros((T * K, H), dtype=hidden_states.dtype)
+    for e in range(E):
+        s0, t0 = int(offs[e]), int(offs[e + 1])
+        for s in range(s0, t0, chunk_m):
+            t = min(s + chunk_m, t0)
+            y13 = sparsegptq14_gemm(w13[e], hs_perm[s:t])
+            gate, up = y13.split(I, dim=1)
+            a2 = torch.nn.functional.silu(gate) * up
+            out_perm[s:t] = sparsegptq14_gemm(w2[e], a2.contiguous())
+    wts = topk_weights.reshape(-1)[order].float()
+    out = torch.zeros((T, H), dtype=torch.float32)
+    out.index_add_(0, tok, out_perm.float() * wts[:, None])
+    return out.to(hidden_states.dtype)

@@ -156,3 +156,94 @@ def test_packed_sparse_layer_is_consumed_end_to_end():
     keep = ((Mi.unsqueeze(-1) >> torch.arange(32, device=DEV)) & 1).permute(1, 0, 2).reshape(What.shape[0], -1).float()
     ref_y = xin.float() @ (What * keep[:, :What.shape[1]]).T
     assert float((Y - ref_y).norm() / ref_y.norm()) < 1e-2
+
+
+def _random_moe_wpair(E, R, C, seed):
+    """Stacked Wpair words [E, G2, R, 2] from the engine's own packer (bit-exact with the reference's, see above)."""
+    from forge.backend.cuda import kernels
+    out = []
+    for e in range(E):
+        g = torch.Generator().manual_seed(seed + e)
+        G32 = (C + 31) // 32
+        q = torch.randint(0, 16, (R, C), generator=g, dtype=torch.uint8)
+        pos = torch.randint(0, 4, (G32, R, 8), generator=g)
+        keep = torch.rand(G32, R, 8, generator=g) > 0.1
+        M = ((keep.long() << (4 * torch.arange(8) + pos)).sum(-1) & 0xFFFFFFFF).to(torch.int32)
+        s32 = (torch.rand(G32, R, generator=g) * 0.01 + 1e-3).float()
+        out.append(kernels.pack_sparsegptq14_to_u64x2(q.to(DEV), M.to(DEV).view(torch.uint32), s32.to(DEV)).view(torch.int64))
+    return torch.stack(out).contiguous()
+
+
+def _bf16_ulps(a, b):
+    """Distance in bf16 steps between two bf16 tensors (sign-magnitude bit patterns mapped to a line)."""
+    def line(t):
+        v = t.contiguous().view(torch.int16).to(torch.int32)
+        return torch.where(v < 0, -(v & 0x7FFF), v)
+    return (line(a) - line(b)).abs()
+
+
+@pytest.mark.parametrize("E,H,I,counts", [(4, 256, 128, [5, 0, 17, 8]), (6, 160, 96, [1, 2, 3, 40, 0, 9]),
+                                          (3, 1536, 256, [300, 7, 64])])
+def test_grouped_moe_gemms_over_wpair(E, H, I, counts):
+    """The grouped W13+SwiGLU and W2 kernels (interfaces of fused_moe_usp14w4a16_gemm.cu:1028-1140) on rows sorted by
+    expert: W2 bit-identical to the per-expert inference GEMM (itself bit-identical to the reference's kernel), W13
+    within one bf16 step of silu(g)*u from fp64 sums of the decoded weights; inactive experts' rows stay zero; the
+    gather by token index gives the same bytes as a permuted copy."""
+    from forge.backend.cuda import kernels
+    from forge import ops
+    import ref_port as O
+    w13 = _random_moe_wpair(E, 2 * I, H, 100 * E + H)
+    w2 = _random_moe_wpair(E, H, I, 200 * E + I)
+    N = sum(counts)
+    offsets = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int64, device=DEV)
+    g = torch.Generator().manual_seed(N)
+    X = (torch.randn(N, H, generator=g) * 0.7).to(torch.bfloat16).to(DEV)
+    active = torch.tensor([e for e in range(E) if e != 1], dtype=torch.int32, device=DEV)
+    X2 = kernels.sparsegptq14_grouped_gemm_w13(w13, X, offsets, active)
+    assert X2.shape == (N, I)
+    X2o = O.sparse14_grouped_w13(w13.cpu(), X.cpu(), offsets.cpu(), active.cpu())
+    d = _bf16_ulps(X2.cpu(), X2o)
+    assert float((d == 0).float().mean()) >= 0.99
+    # the rest: one bf16 step apart, or a near-cancelled sum whose fp32 error is small against the output's scale
+    err = (X2.cpu().float() - X2o.float()).abs()
+    assert bool(((d <= 1) | (err <= 1e-4 * X2o.float().abs().mean())).all())
+    s1, t1 = int(offsets[1]), int(offsets[2])
+    assert not X2[s1:t1].any()
+    Y = kernels.sparsegptq14_grouped_gemm_w2(w2, X2, offsets, active)
+    assert Y.shape == (N, H)
+    for e in range(E):
+        s, t = int(offsets[e]), int(offsets[e + 1])
+        if t == s:
+            continue
+        if e == 1:
+            assert not Y[s:t].any()
+            continue
+        Ye = kernels.sparsegptq14_gemm(w2[e], X2[s:t].contiguous())
+        assert torch.equal(Ye.view(torch.int16), Y[s:t].view(torch.int16))
+    # gather fused into the load: X in token order + a position -> token list
+    perm = torch.randperm(N, generator=g).to(DEV)
+    Xtok = torch.empty_like(X)
+    Xtok[perm] = X
+    X2g = ops.sparse14_moe_w13_swiglu(w13, Xtok, offsets, active, token_idx=perm.to(torch.int32), n_out=N)
+    assert torch.equal(X2g.view(torch.int16), X2.view(torch.int16))
+
+
+def test_sparse14_moe_runtime_matches_reference_runtime():
+    """forge.inference.Sparse14MoERuntime against the restated Sparse14MoERuntime.forward of the reference
+    (sparse14_gemm.py:32-65: per-expert GEMM, bf16 SwiGLU in torch, per-expert GEMM, weighted un-permute).  The grouped
+    W13 kernel rounds once where the reference rounds gate and up first, hence a tolerance."""
+    from forge import inference
+    import ref_port as O
+    E, H, I, T, K = 8, 256, 128, 96, 2
+    w13 = _random_moe_wpair(E, 2 * I, H, 7)
+    w2 = _random_moe_wpair(E, H, I, 9)
+    g = torch.Generator().manual_seed(3)
+    X = (torch.randn(T, H, generator=g) * 0.7).to(torch.bfloat16)
+    logits = torch.randn(T, E, generator=g)
+    wts, ids = torch.topk(torch.softmax(logits, -1), K, dim=-1)
+    rt = inference.Sparse14MoERuntime(w13, w2, I, E)
+    out = rt.forward(X.to(DEV), ids.to(torch.int32).to(DEV), wts.to(DEV))
+    ref_out = O.sparse14_moe_runtime_forward(w13.cpu(), w2.cpu(), X, ids, wts)
+    assert out.shape == (T, H)
+    rel = float((out.cpu().float() - ref_out.float()).norm() / ref_out.float().norm())
+    assert rel < 1e-2, rel

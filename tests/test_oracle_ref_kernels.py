@@ -96,3 +96,43 @@ def test_sparse14_gemm_equals_dense_product_of_the_decoded_weights():
     What = (q.double() - 8.0) * s_bf * keep
     ref = X.double() @ What.T
     assert float((Y - ref).abs().max()) <= 0.01 * float(ref.abs().max()) + 1e-6
+
+
+def test_wpair_decode_and_grouped_restatements_agree_with_the_pinned_gemm():
+    """O.wpair_to_dense, O.sparse14_grouped_w13 and O.sparse14_moe_runtime_forward (the checkers of the grouped MoE
+    kernels) against O.sparsegptq14_gemm, which the reference's own kernel pins above."""
+    g = torch.Generator().manual_seed(11)
+    E, H, I, T, K = 3, 128, 64, 10, 2
+
+    def stack(R, C, seed):
+        out = []
+        for e in range(E):
+            ge = torch.Generator().manual_seed(seed + e)
+            q = torch.randint(0, 16, (R, C), generator=ge, dtype=torch.uint8)
+            pos = torch.randint(0, 4, (C // 32, R, 8), generator=ge)
+            M = ((1 << (4 * torch.arange(8) + pos)).sum(-1)).to(torch.int32)
+            s32 = (torch.rand(C // 32, R, generator=ge) * 0.01 + 1e-3).float()
+            out.append(O.pack_sparsegptq14_to_u64x2(q, M, s32).view(torch.int64))
+        return torch.stack(out)
+
+    w13, w2 = stack(2 * I, H, 1), stack(H, I, 5)
+    X = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    dense = O.wpair_to_dense(w13[1], H)
+    y = O.sparsegptq14_gemm(w13[1], X).double()
+    ref = X.double() @ dense.double().T
+    assert float((y - ref).abs().max()) <= 0.01 * float(ref.abs().max()) + 1e-6
+    # grouped W13: two experts' row ranges, the third inactive
+    offsets = torch.tensor([0, 4, 4, 10])
+    X2 = O.sparse14_grouped_w13(w13, X, offsets, torch.tensor([0, 2]))
+    gu = O.sparsegptq14_gemm(w13[2], X[4:10]).float()
+    want = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+    assert float((X2[4:10].float() - want).norm() / want.norm()) < 2e-2
+    assert not X2[4:4].any()
+    # runtime: top-1 routing with unit weights reduces to one expert's two GEMMs per token
+    ids = torch.randint(0, E, (T, 1), generator=g)
+    out = O.sparse14_moe_runtime_forward(w13, w2, X, ids, torch.ones(T, 1))
+    for t in range(T):
+        e = int(ids[t, 0])
+        y13 = O.sparsegptq14_gemm(w13[e], X[t:t + 1])
+        a2 = torch.nn.functional.silu(y13[:, :I]) * y13[:, I:]
+        assert torch.equal(O.sparsegptq14_gemm(w2[e], a2.contiguous()).view(torch.int16), out[t:t + 1].view(torch.int16))
