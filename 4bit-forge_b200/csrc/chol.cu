@@ -221,14 +221,15 @@ __global__ void __launch_bounds__(64) chol_diag_kernel(float *__restrict__ Aall,
 
 // ---- panel: rows below the diagonal block <- rows * Dinv^T; also stored transposed above ------
 __global__ void __launch_bounds__(256, 3) chol_panel_kernel(float *__restrict__ Aall, int64_t C, int k, int nblk,
-                                                          const float *__restrict__ dinv_all, int vec) {
+                                                          const float *__restrict__ dinv_all, int vec,
+                                                          int64_t row_end) {
     __shared__ __align__(16) float As[TM * AS];
     __shared__ __align__(16) float Bs[KC * 64];
     const int b = blockIdx.y, tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
     float *A = Aall + (int64_t)b * C * C;
     const int64_t cb = (int64_t)k * NB, rb = cb + NB;
     const int64_t i0 = (int64_t)blockIdx.x * TM;
-    const int m_valid = (int)imin64(TM, C - rb - i0);
+    const int m_valid = (int)imin64(TM, row_end - rb - i0);     // rows [rb, row_end) only
     if (m_valid <= 0) return;
     const float *dinvT = dinv_all + ((int64_t)b * nblk + k) * 2 * NB * NB + NB * NB;
     float acc[8][4];
@@ -338,7 +339,7 @@ constexpr size_t kSyrkSmem = (size_t)kSyrkStages * kSyrkStageBytes + 1024 + 256;
 
 __global__ void __launch_bounds__(kSyrkThreads, 3) chol_syrk_tc_kernel(float *__restrict__ Aall, int64_t C, int64_t kb, int K,
                                                                         int64_t r0, int64_t ncols, int nb,
-                                                                        int32_t *status) {
+                                                                        int32_t *status, int64_t row_end) {
     using namespace forge::tc;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -369,7 +370,7 @@ __global__ void __launch_bounds__(kSyrkThreads, 3) chol_syrk_tc_kernel(float *__
     const uint32_t tmem_base = *tmem_holder;
 
     const int64_t cb = kb, rb = r0;
-    const int64_t m = C - rb;                       // rows of the block being updated
+    const int64_t m = row_end - rb;                 // rows of the block being updated: [r0, row_end)
     const int64_t ncol = ncols < m ? ncols : m;     // its columns
     const int nti = (int)((m + 127) / 128), ntj = (int)((ncol + 127) / 128);
     const int ntri = syrk_tiles(nti, ntj);
@@ -492,6 +493,269 @@ __global__ void __launch_bounds__(kSyrkThreads, 3) chol_syrk_tc_kernel(float *__
             if (!ok) break;
             if (lane == 0) umma_commit(bar_acc);
             __syncwarp();
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && tid == 0 && status) atomicExch(status, FORGE_ERR_TIMEOUT);
+    if (warp == 4) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(128u) : "memory");
+    }
+}
+
+// ---- inverse of an outer block's factor -----------------------------------------------------------------------
+// M = L11^-1 for the W x W diagonal block that starts at column ob (W = 64 P), from the 64x64 inverses the diagonal
+// kernel left behind:  M[p][p] = Dinv_p,  M[p][q] = -Dinv_p * sum_{q <= r < p} L[p][r] M[r][q]  (p > q).
+// CTA (q, b) owns block column q of matrix b and walks p = q .. P-1 with the finished blocks in shared memory.
+// Output MT[k][c] = M[c][k] (row-major [W][W]): rows of MT are K rows of the operand the kernel below multiplies by.
+// Only the zero block the multiplication reads is cleared (k-block 2t+1 against c-block 2t: same 128-column tile).
+__global__ void __launch_bounds__(256) chol_block_inv_kernel(const float *__restrict__ Aall, int64_t C, int64_t ob,
+                                                             int P, int nblk, const float *__restrict__ dinv_all,
+                                                             float *__restrict__ minv_all) {
+    extern __shared__ __align__(16) float binv_smem[];
+    float *Xs = binv_smem;                 // [P][64][64]  finished blocks of this block column
+    float *Ls = Xs + (int64_t)P * 4096;    // [64][65]     left operand of the current product
+    float *Ss = Ls + 64 * 65;              // [64][64]     the sum before the multiplication by Dinv_p
+    const int q = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+    const int64_t W = (int64_t)P * 64;
+    const float *A = Aall + (int64_t)b * C * C;
+    float *MT = minv_all + (int64_t)b * W * W;
+    const int kb0 = (int)(ob / 64);
+    if (q & 1) {
+        for (int idx = tid; idx < 1024; idx += 256) {
+            const int j = idx >> 4, i4 = (idx & 15) * 4;
+            *reinterpret_cast<float4 *>(MT + (int64_t)(64 * q + j) * W + 64 * (q - 1) + i4) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    auto load_block = [&](const float *src, int64_t ld) {     // Ls[i][k] = src[i * ld + k]
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = (tid >> 4) + 16 * u, k4 = (tid & 15) * 4;
+            const float4 v = *reinterpret_cast<const float4 *>(src + (int64_t)i * ld + k4);
+            Ls[i * 65 + k4 + 0] = v.x; Ls[i * 65 + k4 + 1] = v.y; Ls[i * 65 + k4 + 2] = v.z; Ls[i * 65 + k4 + 3] = v.w;
+        }
+    };
+    for (int p = q; p < P; ++p) {
+        float acc[4][4];
+#pragma unroll
+        for (int ii = 0; ii < 4; ++ii)
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) acc[ii][jj] = (p == q && ty * 4 + ii == tx * 4 + jj) ? 1.0f : 0.0f;
+        for (int r = q; r < p; ++r) {
+            load_block(A + (ob + 64 * (int64_t)p) * C + ob + 64 * (int64_t)r, C);
+            __syncthreads();
+            const float *Xr = Xs + (int64_t)r * 4096;
+#pragma unroll 8
+            for (int k = 0; k < 64; ++k) {
+                const float4 bv = *reinterpret_cast<const float4 *>(Xr + k * 64 + tx * 4);
+#pragma unroll
+                for (int ii = 0; ii < 4; ++ii) {
+                    const float a = Ls[(ty * 4 + ii) * 65 + k];
+                    acc[ii][0] = fmaf(-a, bv.x, acc[ii][0]);
+                    acc[ii][1] = fmaf(-a, bv.y, acc[ii][1]);
+                    acc[ii][2] = fmaf(-a, bv.z, acc[ii][2]);
+                    acc[ii][3] = fmaf(-a, bv.w, acc[ii][3]);
+                }
+            }
+            __syncthreads();
+        }
+#pragma unroll
+        for (int ii = 0; ii < 4; ++ii)
+            *reinterpret_cast<float4 *>(Ss + (ty * 4 + ii) * 64 + tx * 4) =
+                make_float4(acc[ii][0], acc[ii][1], acc[ii][2], acc[ii][3]);
+        load_block(dinv_all + ((int64_t)b * nblk + kb0 + p) * 2 * NB * NB, NB);      // Dinv_p, row-major
+        __syncthreads();
+#pragma unroll
+        for (int ii = 0; ii < 4; ++ii)
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) acc[ii][jj] = 0.0f;
+#pragma unroll 8
+        for (int k = 0; k < 64; ++k) {
+            const float4 bv = *reinterpret_cast<const float4 *>(Ss + k * 64 + tx * 4);
+#pragma unroll
+            for (int ii = 0; ii < 4; ++ii) {
+                const float a = Ls[(ty * 4 + ii) * 65 + k];
+                acc[ii][0] = fmaf(a, bv.x, acc[ii][0]);
+                acc[ii][1] = fmaf(a, bv.y, acc[ii][1]);
+                acc[ii][2] = fmaf(a, bv.z, acc[ii][2]);
+                acc[ii][3] = fmaf(a, bv.w, acc[ii][3]);
+            }
+        }
+        float *Xp = Xs + (int64_t)p * 4096;
+#pragma unroll
+        for (int ii = 0; ii < 4; ++ii)
+            *reinterpret_cast<float4 *>(Xp + (ty * 4 + ii) * 64 + tx * 4) =
+                make_float4(acc[ii][0], acc[ii][1], acc[ii][2], acc[ii][3]);
+        // MT[64 q + j][64 p + i] = X_p[i][j]: four consecutive i per store
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj)
+            *reinterpret_cast<float4 *>(MT + (int64_t)(64 * q + tx * 4 + jj) * W + 64 * p + ty * 4) =
+                make_float4(acc[0][jj], acc[1][jj], acc[2][jj], acc[3][jj]);
+        __syncthreads();
+    }
+}
+
+// ---- rows below an outer block:  L21 = A21 * M11^T on the tensor cores ---------------------------------------------
+// A21 = rows [ob + W, C) x columns [ob, ob + W) as the earlier outer blocks' updates left it, M11 = the block inverse
+// above.  One pass replaces, for these rows, the eight panel multiplications and the eight K = 64 updates of the
+// right-looking form (each a read-modify-write of the strip in HBM) by one TF32 x3 GEMM that reads A21 once.
+// A CTA owns a strip of 128 rows and walks the W / 128 column tiles from the LAST to the first: tile tj needs
+// columns [0, 128 (tj + 1)) of the strip (M11 is lower triangular) and overwrites columns [128 tj, 128 tj + 128), which
+// no later tile of the strip reads.  The A operand is row-major in memory (k contiguous): a producer thread owns one
+// row, loads 32 k-values at a time and scatters the hi / lo parts into the MN-major piece (a warp's 32 rows are 128
+// contiguous bytes of a K row: no bank conflict).  B pieces come from MT exactly like the update kernel's operands.
+// The result goes to the lower triangle (row-major) and, transposed, to the upper triangle, where the update kernel
+// reads its operands.
+constexpr int kTrsmThreads = 160;
+__global__ void __launch_bounds__(kTrsmThreads, 3) chol_trsm_tc_kernel(float *__restrict__ Aall, int64_t C, int64_t ob, int W,
+                                                                        const float *__restrict__ minv_all, int nb,
+                                                                        int32_t *status) {
+    using namespace forge::tc;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *ring = smem_raw + (smem_base - smem_u32(smem_raw));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(ring + kSyrkStages * kSyrkStageBytes);  // full[4], empty[4], acc
+    uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + 9);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
+    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + kSyrkStages), bar_acc = smem_u32(bars + 8);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (int s = 0; s < kSyrkStages; ++s) {
+            mbar_init(bar_full + 8 * s, 128);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        mbar_init(bar_acc, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 4) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
+                     "r"(128u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    const int64_t oe = ob + W, m = C - oe;
+    const int nstrips = (int)((m + 127) / 128), ntj = W / 128;
+    const int total = nb * nstrips;
+    uint32_t it = 0, acc_it = 0;
+
+    if (warp < 4) {
+        const int jB = tid >> 5, c4 = tid & 31;
+        const uint32_t swB[2] = {piece_offset(jB, c4), piece_offset(jB + 4, c4)};
+        const uint32_t rowA = (uint32_t)((tid & 3) * 4);        // byte offset of this thread's row inside a 16-byte chunk
+        uint32_t swA[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) swA[j] = piece_offset(j, tid >> 2) + rowA;
+        bool ok = true;
+        for (int unit = blockIdx.x; unit < total && ok; unit += gridDim.x) {
+            const int b = unit / nstrips;
+            const int64_t i0 = (int64_t)(unit % nstrips) * 128;
+            float *A = Aall + (int64_t)b * C * C;
+            const float *MT = minv_all + (int64_t)b * W * W;
+            const bool a_ok = (i0 + tid) < m;
+            const float *srcA = A + (oe + i0 + tid) * C + ob;
+            for (int tj = ntj - 1; tj >= 0 && ok; --tj) {
+                const int K = 128 * (tj + 1);
+                const float *srcB = MT + 128 * tj + 4 * c4;
+#pragma unroll 1
+                for (int half = 0; half < K / 32 && ok; ++half) {
+                    float4 ra[8], rbv[4][2];
+#pragma unroll
+                    for (int d = 0; d < 8; ++d)
+                        ra[d] = a_ok ? ldg128_here(srcA + half * 32 + 4 * d) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int d = 0; d < 4; ++d)
+#pragma unroll
+                        for (int h = 0; h < 2; ++h)
+                            rbv[d][h] = ldg128_here(srcB + (int64_t)(half * 32 + d * kKS + jB + 4 * h) * W);
+#pragma unroll
+                    for (int d = 0; d < 4; ++d) {
+                        if (!ok) break;
+                        const uint32_t s = it % kSyrkStages, ph = (it / kSyrkStages) & 1u;
+                        ok = mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag);
+                        if (!ok) break;
+                        uint8_t *stage = ring + s * kSyrkStageBytes;
+                        const float av[8] = {ra[2 * d].x, ra[2 * d].y, ra[2 * d].z, ra[2 * d].w,
+                                             ra[2 * d + 1].x, ra[2 * d + 1].y, ra[2 * d + 1].z, ra[2 * d + 1].w};
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float hi = tf32_round(av[j]);
+                            const float lo = tf32_round(__fsub_rn(av[j], hi));
+                            *reinterpret_cast<float *>(stage + 0 * kPieceBytes + swA[j]) = hi;
+                            *reinterpret_cast<float *>(stage + 1 * kPieceBytes + swA[j]) = lo;
+                        }
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            float4 hi, lo;
+                            split4(rbv[d][h], hi, lo);
+                            *reinterpret_cast<float4 *>(stage + 2 * kPieceBytes + swB[h]) = hi;
+                            *reinterpret_cast<float4 *>(stage + 3 * kPieceBytes + swB[h]) = lo;
+                        }
+                        fence_proxy_async();
+                        mbar_arrive(bar_full + 8 * s);
+                        ++it;
+                    }
+                }
+                // ---- epilogue of (strip, tj): one row per thread, both orientations
+                if (ok) ok = mbar_wait(bar_acc, acc_it & 1u, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                ++acc_it;
+                if (!ok) break;
+                tc_fence_after();
+                const int64_t row = i0 + tid, col0 = ob + 128 * (int64_t)tj;
+#pragma unroll 1
+                for (int qd = 0; qd < 4; ++qd) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(qd * 32), v);
+                    tmem_ld_wait();
+                    if (row < m) {
+                        float *dst = A + (oe + row) * C + col0 + qd * 32;
+#pragma unroll
+                        for (int g4 = 0; g4 < 8; ++g4)
+                            *reinterpret_cast<float4 *>(dst + 4 * g4) =
+                                make_float4(__uint_as_float(v[4 * g4 + 0]), __uint_as_float(v[4 * g4 + 1]),
+                                            __uint_as_float(v[4 * g4 + 2]), __uint_as_float(v[4 * g4 + 3]));
+                        float *dstT = A + (col0 + qd * 32) * C + oe + row;
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) dstT[(int64_t)c * C] = __uint_as_float(v[c]);
+                    }
+                }
+                tc_fence_before();
+            }
+        }
+    } else {
+        bool ok = true;
+        for (int unit = blockIdx.x; unit < total && ok; unit += gridDim.x) {
+            for (int tj = ntj - 1; tj >= 0 && ok; --tj) {
+                const int kSteps = 128 * (tj + 1) / kKS;
+                for (int ks = 0; ks < kSteps && ok; ++ks) {
+                    const uint32_t s = it % kSyrkStages, ph = (it / kSyrkStages) & 1u;
+                    ok = mbar_wait(bar_full + 8 * s, ph, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (lane == 0) {
+                        const uint32_t st = smem_base + s * kSyrkStageBytes;
+                        const uint64_t ahi = make_desc_tf32(st), alo = make_desc_tf32(st + kPieceBytes);
+                        const uint64_t bhi = make_desc_tf32(st + 2 * kPieceBytes), blo = make_desc_tf32(st + 3 * kPieceBytes);
+                        const uint32_t id = idesc_tf32(128);
+                        umma_tf32(tmem_base, ahi, bhi, id, ks > 0 ? 1u : 0u);
+                        umma_tf32(tmem_base, alo, bhi, id, 1u);
+                        umma_tf32(tmem_base, ahi, blo, id, 1u);
+                        umma_commit(bar_empty + 8 * s);
+                    }
+                    __syncwarp();
+                    ++it;
+                }
+                if (!ok) break;
+                if (lane == 0) umma_commit(bar_acc);
+                __syncwarp();
+            }
         }
     }
     tc_fence_before();
@@ -641,9 +905,13 @@ __global__ void status_to_info_kernel(int32_t *info, int nb, const int32_t *stat
 
 }  // namespace
 
+// width of the outer blocks of the two-level factorisation (measured: wider blocks pay from C ~ 4096 on)
+static inline int64_t chol_outer(int64_t C) { return (C >= 4096) ? 2 * kOuter : kOuter; }
+
+// workspace: the (Dinv, Dinv^T) pairs of every 64-column block, one inverted outer block per matrix, the status word
 extern "C" int64_t forge_chol_workspace_bytes(int nb, int64_t C) {
-    const int64_t nblk = cdiv(C, NB);
-    return (int64_t)nb * nblk * 2 * NB * NB * (int64_t)sizeof(float) + 256;
+    const int64_t nblk = cdiv(C, NB), W = chol_outer(C);
+    return ((int64_t)nb * nblk * 2 * NB * NB + (int64_t)nb * W * W) * (int64_t)sizeof(float) + 256;
 }
 
 extern "C" int64_t forge_chol_workspace_bytes(int nb, int64_t C);
@@ -656,7 +924,8 @@ static void launch_factor(float *A, int nb, int64_t C, float *U, float *udiag, i
     cudaFuncSetAttribute(chol_syrk_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSyrkSmem);
     const char *env = getenv("FORGE_SYRK_IMPL");
     const bool syrk_simt = env && strcmp(env, "simt") == 0;   // cross-checks: plain-FMA trailing update
-    const int64_t outer = (C >= 4096) ? 2 * kOuter : kOuter;   // measured: wider outer blocks pay from C ~ 4096 on
+    const int64_t outer = chol_outer(C);
+    float *minv = dinv + (int64_t)nb * nblk * 2 * NB * NB;
     info_clear_kernel<<<(nb + 127) / 128, 128, 0, st>>>(info, nb, status); FORGE_NOTE_LAUNCH();
     if (!vec || syrk_simt) {
         // plain right-looking form: every panel updates the whole matrix behind it
@@ -665,28 +934,44 @@ static void launch_factor(float *A, int nb, int64_t C, float *U, float *udiag, i
             const int64_t m = C - (int64_t)(k + 1) * NB;
             if (m > 0) {
                 const unsigned nt = (unsigned)cdiv(m, TM);
-                chol_panel_kernel<<<dim3(nt, nb), 256, 0, st>>>(A, C, k, nblk, dinv, vec); FORGE_NOTE_LAUNCH();
+                chol_panel_kernel<<<dim3(nt, nb), 256, 0, st>>>(A, C, k, nblk, dinv, vec, C); FORGE_NOTE_LAUNCH();
                 chol_syrk_kernel<<<dim3(nt, nt, nb), 256, 0, st>>>(A, C, k, vec); FORGE_NOTE_LAUNCH();
             }
         }
     } else {
-        auto update = [&](int64_t kb, int K, int64_t r0, int64_t ncols) {
-            const int64_t m = C - r0, nc = ncols < m ? ncols : m;
-            const int total = nb * syrk_tiles((int)cdiv(m, 128), (int)cdiv(nc, 128));
+        // T[rows [r0, row_end), columns [r0, r0 + ncols)] -= P P^T with the K factored columns from kb on
+        auto update = [&](int64_t kb, int K, int64_t r0, int64_t ncols, int64_t row_end) {
+            const int64_t m = row_end - r0, nc = ncols < m ? ncols : m;
+            const int total = nb * syrk_tiles((int)cdiv(m, (int64_t)128), (int)cdiv(nc, (int64_t)128));
             const int grid = total < 148 * 3 ? total : 148 * 3;
-            chol_syrk_tc_kernel<<<grid, kSyrkThreads, kSyrkSmem, st>>>(A, C, kb, K, r0, ncols, nb, status);
+            chol_syrk_tc_kernel<<<grid, kSyrkThreads, kSyrkSmem, st>>>(A, C, kb, K, r0, ncols, nb, status, row_end);
             FORGE_NOTE_LAUNCH();
         };
+        cudaFuncSetAttribute(chol_trsm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSyrkSmem);
+        const int binv_smem = (int)((outer / NB * 4096 + 64 * 65 + 4096) * sizeof(float));
+        cudaFuncSetAttribute(chol_block_inv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, binv_smem);
         for (int64_t ob = 0; ob < C; ob += outer) {
             const int64_t oe = imin64(C, ob + outer);
+            // the outer block's own rows: 64-column panels, right-looking inside the block
             for (int k = (int)(ob / NB); (int64_t)k * NB < oe; ++k) {
                 chol_diag_kernel<<<nb, NB, 0, st>>>(A, C, k, nblk, dinv, U, udiag, info); FORGE_NOTE_LAUNCH();
-                const int64_t rb = (int64_t)(k + 1) * NB, m = C - rb;
-                if (m <= 0) continue;
-                chol_panel_kernel<<<dim3((unsigned)cdiv(m, TM), nb), 256, 0, st>>>(A, C, k, nblk, dinv, vec); FORGE_NOTE_LAUNCH();
-                if (rb < oe) update((int64_t)k * NB, NB, rb, oe - rb);     // the rest of this outer block
+                const int64_t rb = (int64_t)(k + 1) * NB;
+                if (rb >= oe) continue;
+                chol_panel_kernel<<<dim3((unsigned)cdiv(oe - rb, (int64_t)TM), nb), 256, 0, st>>>(A, C, k, nblk, dinv, vec, oe);
+                FORGE_NOTE_LAUNCH();
+                update((int64_t)k * NB, NB, rb, oe - rb, oe);
             }
-            if (oe < C) update(ob, (int)(oe - ob), oe, C - oe);           // everything behind the outer block
+            if (oe < C) {
+                // the rows behind it: block inverse, ONE multiplication for the panel, ONE update of the rest
+                const int P = (int)(outer / NB);
+                chol_block_inv_kernel<<<dim3(P, nb), 256, binv_smem, st>>>(A, C, ob, P, nblk, dinv, minv);
+                FORGE_NOTE_LAUNCH();
+                const int64_t units = (int64_t)nb * cdiv(C - oe, (int64_t)128);
+                chol_trsm_tc_kernel<<<(unsigned)(units < 148 * 3 ? units : 148 * 3), kTrsmThreads, kSyrkSmem, st>>>(
+                    A, C, ob, (int)outer, minv, nb, status);
+                FORGE_NOTE_LAUNCH();
+                update(ob, (int)(oe - ob), oe, C - oe, C);
+            }
         }
     }
     status_to_info_kernel<<<(nb + 127) / 128, 128, 0, st>>>(info, nb, status); FORGE_NOTE_LAUNCH();

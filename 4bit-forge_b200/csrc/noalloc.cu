@@ -10,7 +10,8 @@
 //     from a callback) is not allowed to call cudaMalloc at all, and cudaMalloc would also synchronise
 //     the device under the other streams.
 // For them the workspace lives here, in a file-scope __device__ array that every GPU loading the
-// library holds until the process exits (kMaxC^2/32 floats = 2 MiB for kMaxC = 4096).
+// library holds until the process exits (3 MiB for kMaxC = 4096: kMaxC^2/32 floats of inverted diagonal blocks and
+// one inverted 512-column outer block).
 //
 // Rules of use (also in include/forge_b200.h):
 //   * C <= FORGE_NOALLOC_MAX_C, otherwise FORGE_ERR_UNSUPPORTED;
@@ -28,9 +29,9 @@ using namespace forge;
 namespace {
 
 constexpr int64_t kMaxC = 4096;
-// one (Dinv, Dinv^T) pair per 64-column block, plus the 256-byte tail that forge_chol_workspace_bytes reserves
-// for the status word of the tensor-core kernels
-constexpr int64_t kScratchFloats = (kMaxC / 64) * 2 * 64 * 64 + 64;
+// what forge_chol_workspace_bytes(1, kMaxC) asks for: one (Dinv, Dinv^T) pair per 64-column block, one inverted outer
+// block (512 x 512), and the 256-byte tail for the status word of the tensor-core kernels
+constexpr int64_t kScratchFloats = (kMaxC / 64) * 2 * 64 * 64 + 512 * 512 + 64;
 
 // In host code this name is only a handle for the runtime, not a device address: the address the
 // kernels can use comes from cudaGetSymbolAddress below.
