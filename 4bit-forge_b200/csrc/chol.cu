@@ -504,6 +504,188 @@ __global__ void __launch_bounds__(kSyrkThreads, 3) chol_syrk_tc_kernel(float *__
     }
 }
 
+// ---- the same update on 256 x 256 tiles (the big update behind an outer block) -----------------------------------
+// The 128 x 128 kernel above stages 16 KB of split operands per k-step for three 128 x 128 x 8 MMAs: shared-memory
+// stores and operand loads keep the L1 / shared-memory pipe as busy as the tensor pipe (ncu: 78 % against 44 %).  A
+// 256 x 256 tile stages 32 KB per k-step for SIX 128 x 256 x 8 MMAs: half the staging per multiply-add.  One CTA per SM:
+// eight producer / epilogue warps (thread t owns tile row t), one MMA warp, both 128-row halves' accumulators fill
+// tensor memory (2 x 256 columns).  Stage = [A0hi A1hi A0lo A1lo B0hi B1hi B0lo B1lo] (4 KB pieces): the two pieces of
+// a B part are adjacent and form one N = 256 operand; on diagonal tiles B is A.
+constexpr int kSyrk2Threads = 288;
+constexpr int kSyrk2Stages = 4;
+constexpr int kSyrk2StageBytes = 8 * forge::tc::kPieceBytes;
+constexpr size_t kSyrk2Smem = (size_t)kSyrk2Stages * kSyrk2StageBytes + 1024 + 256;
+
+__global__ void __launch_bounds__(kSyrk2Threads, 1) chol_syrk256_tc_kernel(float *__restrict__ Aall, int64_t C, int64_t kb,
+                                                                            int K, int64_t r0, int nb,
+                                                                            int32_t *status) {
+    using namespace forge::tc;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *ring = smem_raw + (smem_base - smem_u32(smem_raw));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(ring + kSyrk2Stages * kSyrk2StageBytes);  // full[4], empty[4], acc
+    uint32_t *tmem_holder = reinterpret_cast<uint32_t *>(bars + 9);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_holder + 1);
+    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + kSyrk2Stages), bar_acc = smem_u32(bars + 8);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (int s = 0; s < kSyrk2Stages; ++s) {
+            mbar_init(bar_full + 8 * s, 256);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        mbar_init(bar_acc, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 8) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_holder)),
+                     "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_holder;
+
+    const int64_t cb = kb, rb = r0;
+    const int64_t m = C - rb;                       // the square block [r0, C) x [r0, C), lower tiles
+    const int nt = (int)((m + 255) / 256);
+    const int ntri = syrk_tiles(nt, nt);
+    const int total = nb * ntri;
+    uint32_t it = 0, acc_it = 0;
+    const int kSteps = K / kKS;
+
+    if (warp < 8) {
+        const int half = tid >> 7, jA = (tid >> 5) & 3, c4 = tid & 31;
+        const uint32_t sw_off[2] = {piece_offset(jA, c4), piece_offset(jA + 4, c4)};
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+            const int b = tile / ntri;
+            int ti, tj;
+            syrk_tile(tile % ntri, nt, ti, tj);
+            float *A = Aall + (int64_t)b * C * C;
+            const int64_t i0 = (int64_t)ti * 256, j0 = (int64_t)tj * 256;
+            const bool diag = (ti == tj);
+            const int64_t ia = i0 + half * 128 + 4 * c4, jb = j0 + half * 128 + 4 * c4;
+            const bool a_ok = ia < m, b_ok = jb < m;
+            const float *srcA = A + cb * C + rb + ia;
+            const float *srcB = A + cb * C + rb + jb;
+#pragma unroll 1
+            for (int grp = 0; grp < K / 32 && ok; ++grp) {
+                float4 ra[4][2], rbv[4][2];
+#pragma unroll
+                for (int d = 0; d < 4; ++d)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int64_t row = (int64_t)(grp * 4 + d) * kKS + jA + 4 * h;
+                        ra[d][h] = a_ok ? ldg128_here(srcA + row * C) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (!diag) rbv[d][h] = b_ok ? ldg128_here(srcB + row * C) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                for (int d = 0; d < 4; ++d) {
+                    if (!ok) break;
+                    const uint32_t s = it % kSyrk2Stages, ph = (it / kSyrk2Stages) & 1u;
+                    ok = mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag);
+                    if (!ok) break;
+                    uint8_t *stage = ring + s * kSyrk2StageBytes + half * kPieceBytes;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        float4 hi, lo;
+                        split4(ra[d][h], hi, lo);
+                        *reinterpret_cast<float4 *>(stage + 0 * kPieceBytes + sw_off[h]) = hi;
+                        *reinterpret_cast<float4 *>(stage + 2 * kPieceBytes + sw_off[h]) = lo;
+                        if (!diag) {
+                            split4(rbv[d][h], hi, lo);
+                            *reinterpret_cast<float4 *>(stage + 4 * kPieceBytes + sw_off[h]) = hi;
+                            *reinterpret_cast<float4 *>(stage + 6 * kPieceBytes + sw_off[h]) = lo;
+                        }
+                    }
+                    fence_proxy_async();
+                    mbar_arrive(bar_full + 8 * s);
+                    ++it;
+                }
+            }
+            // ---- epilogue: T -= acc, one row per thread (thread t <-> tile row t <-> TMEM lane t % 128 of half t / 128)
+            if (ok) ok = mbar_wait(bar_acc, acc_it & 1u, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            ++acc_it;
+            if (!ok) break;
+            tc_fence_after();
+            const int64_t row = i0 + tid;
+            float *Crow = A + (rb + row) * C + rb + j0;
+            const uint32_t tm = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(half * 256);
+#pragma unroll 1
+            for (int qd = 0; qd < 8; ++qd) {
+                if (j0 + qd * 32 >= m) break;                // columns past the matrix (same for the whole CTA)
+                // on a diagonal tile the columns right of this row's 32-column group boundary are never used
+                uint32_t v[32];
+                tmem_ld32(tm + (uint32_t)(qd * 32), v);
+                tmem_ld_wait();
+                if (row < m && !(diag && qd * 32 > tid)) {
+#pragma unroll
+                    for (int g4 = 0; g4 < 8; ++g4) {
+                        const int64_t col = j0 + qd * 32 + g4 * 4;
+                        if (col + 3 < m) {
+                            float4 *dst = reinterpret_cast<float4 *>(Crow + qd * 32 + g4 * 4);
+                            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst),
+                                         "f"(-__uint_as_float(v[4 * g4 + 0])), "f"(-__uint_as_float(v[4 * g4 + 1])),
+                                         "f"(-__uint_as_float(v[4 * g4 + 2])), "f"(-__uint_as_float(v[4 * g4 + 3]))
+                                         : "memory");
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e)
+                                if (col + e < m) Crow[qd * 32 + g4 * 4 + e] -= __uint_as_float(v[4 * g4 + e]);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+        }
+    } else {
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+            int ti, tj;
+            syrk_tile(tile % ntri, nt, ti, tj);
+            const bool diag = (ti == tj);
+            for (int ks = 0; ks < kSteps && ok; ++ks) {
+                const uint32_t s = it % kSyrk2Stages, ph = (it / kSyrk2Stages) & 1u;
+                ok = mbar_wait(bar_full + 8 * s, ph, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t st = smem_base + s * kSyrk2StageBytes;
+                    const uint64_t bhi = make_desc_tf32(st + (diag ? 0 : 4) * kPieceBytes);
+                    const uint64_t blo = make_desc_tf32(st + (diag ? 2 : 6) * kPieceBytes);
+                    const uint32_t id = idesc_tf32(256);
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const uint64_t ahi = make_desc_tf32(st + h * kPieceBytes);
+                        const uint64_t alo = make_desc_tf32(st + (2 + h) * kPieceBytes);
+                        const uint32_t d = tmem_base + (uint32_t)(h * 256);
+                        umma_tf32(d, ahi, bhi, id, ks > 0 ? 1u : 0u);
+                        umma_tf32(d, alo, bhi, id, 1u);
+                        umma_tf32(d, ahi, blo, id, 1u);
+                    }
+                    umma_commit(bar_empty + 8 * s);
+                }
+                __syncwarp();
+                ++it;
+            }
+            if (!ok) break;
+            if (lane == 0) umma_commit(bar_acc);
+            __syncwarp();
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && tid == 0 && status) atomicExch(status, FORGE_ERR_TIMEOUT);
+    if (warp == 8) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
 // ---- inverse of an outer block's factor -----------------------------------------------------------------------
 // M = L11^-1 for the W x W diagonal block that starts at column ob (W = 64 P), from the 64x64 inverses the diagonal
 // kernel left behind:  M[p][p] = Dinv_p,  M[p][q] = -Dinv_p * sum_{q <= r < p} L[p][r] M[r][q]  (p > q).
@@ -948,6 +1130,10 @@ static void launch_factor(float *A, int nb, int64_t C, float *U, float *udiag, i
             FORGE_NOTE_LAUNCH();
         };
         cudaFuncSetAttribute(chol_trsm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSyrkSmem);
+        cudaFuncSetAttribute(chol_syrk256_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSyrk2Smem);
+        int dev = 0, sms = 148;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         const int binv_smem = (int)((outer / NB * 4096 + 64 * 65 + 4096) * sizeof(float));
         cudaFuncSetAttribute(chol_block_inv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, binv_smem);
         for (int64_t ob = 0; ob < C; ob += outer) {
@@ -970,7 +1156,15 @@ static void launch_factor(float *A, int nb, int64_t C, float *U, float *udiag, i
                 chol_trsm_tc_kernel<<<(unsigned)(units < 148 * 3 ? units : 148 * 3), kTrsmThreads, kSyrkSmem, st>>>(
                     A, C, ob, (int)outer, minv, nb, status);
                 FORGE_NOTE_LAUNCH();
-                update(ob, (int)(oe - ob), oe, C - oe, C);
+                if (C - oe > 256) {
+                    const int nt2 = (int)cdiv(C - oe, (int64_t)256);
+                    const int total2 = nb * syrk_tiles(nt2, nt2);
+                    chol_syrk256_tc_kernel<<<total2 < sms ? total2 : sms, kSyrk2Threads, kSyrk2Smem, st>>>(
+                        A, C, ob, (int)(oe - ob), oe, nb, status);
+                    FORGE_NOTE_LAUNCH();
+                } else {
+                    update(ob, (int)(oe - ob), oe, C - oe, C);
+                }
             }
         }
     }
