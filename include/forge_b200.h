@@ -176,14 +176,14 @@ int forge_chol_inv_upper_batched(float *A, int nb, int64_t C, float *U, float *u
                                  int zero_lower, void *ws, void *stream);
 
 /* Allocation-free variant for ONE matrix; it has no counterpart in the reference.
- * Same result as forge_chol_inv_upper_batched(A, 1, C, ...), but the workspace is a 2 MiB array that
+ * Same result as forge_chol_inv_upper_batched(A, 1, C, ...), but the workspace is a 3 MiB array that
  * lives inside the library on every GPU that loads it, for callers that cannot obtain device memory
  * when they need a factorisation: a layer driver that has already given all of HBM to its Hessian
  * batches and must redo one expert (info > 0) with a larger damping, or a host application whose memory
  * manager forbids cudaMalloc (which would also stall its other streams).
  * C <= forge_noalloc_max_c() (4096), else FORGE_ERR_UNSUPPORTED.  The first call on a device looks up the
  * array's address (cudaGetSymbolAddress): make that call outside of stream capture, and make it early — the CUDA
- * runtime loads the library's code lazily, so the 2 MiB array itself is created on a device by that first call;
+ * runtime loads the library's code lazily, so the 3 MiB array itself is created on a device by that first call;
  * a warm-up call at start-up, while device memory is still free, guarantees it exists when memory has run out.  All calls on a device
  * share the array, so calls that overlap on the GPU (different streams) race; calls on one stream are safe,
  * and nothing in the array needs clearing between calls. */
