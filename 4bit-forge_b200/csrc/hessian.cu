@@ -31,13 +31,20 @@ namespace {
 constexpr int32_t kNoRow = INT32_MIN;         // padding slot of a k-tile (past the end of the token list)
 constexpr int kTile = 256;                    // output tile edge (channels)
 constexpr int kKT = 64;                       // tokens per k-tile
+// The tensor core adds each k-step's products to the fp32 accumulator with truncation, not round-to-nearest: the
+// accumulated bias grows with the number of k-steps (measured against float64 at 7168 channels: 2e-6 relative after
+// 1024 tokens, 3e-5 after 8192, 3e-4 after 65536, all towards zero; a round-to-nearest fp32 sum stays near 2e-6).  A
+// tile's token range is therefore accumulated in pieces of at most kChunkKT k-tiles; each piece is added to H in the
+// epilogue in ordinary fp32 arithmetic.  With 4096 tokens per piece the error stays below 2e-5 for any token count.
+constexpr int kChunkKT = 64;
 constexpr int kSubBytes = kKT * 128;          // one 64-channel x 64-token sub-tile: 8 KB
 constexpr int kOperandBytes = 4 * kSubBytes;  // 256 channels: 32 KB
 constexpr int kStageBytes = 2 * kOperandBytes;
 constexpr int kStages = 3;
 constexpr int kLag = 2;                       // cp.async groups in flight per thread
 constexpr int kProducerThreads = 128;
-constexpr int kThreads = 160;
+constexpr int kEpilogueThreads = 256;           // warps 5..12: two per TMEM lane quarter, one accumulator half each
+constexpr int kThreads = 160 + kEpilogueThreads; // 4 producer warps, the MMA warp, 8 epilogue warps
 constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
 
 struct HessParams {
@@ -107,7 +114,7 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_tc_kernel(const HessParam
             mbar_init(bar_empty + 8 * s, 1);
         }
         mbar_init(bar_acc_full, 1);
-        mbar_init(bar_acc_empty, kProducerThreads);
+        mbar_init(bar_acc_empty, kEpilogueThreads);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -125,7 +132,7 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_tc_kernel(const HessParam
     const int64_t C = P.C;
     const int total_tiles = P.nb * P.ntri;
     uint32_t it = 0;         // k-tile counter of this CTA (ring position), same sequence in both roles
-    uint32_t tile_iter = 0;  // tiles done by this CTA
+    uint32_t tile_iter = 0;  // accumulator hand-overs (pieces of tiles) done by this CTA
 
     if (warp < 4) {
         // ------------------------------ producers + epilogue ------------------------------
@@ -162,10 +169,14 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_tc_kernel(const HessParam
                     dst[i] = t;
                 }
             };
-            load_tokens(0, tok_cur);
+            const int nch = (nkt + kChunkKT - 1) / kChunkKT, kt_per = (nkt + nch - 1) / nch;
             // channel offsets of the (up to) eight 64-channel sub-tiles this thread copies a chunk of
             const int64_t chA = (int64_t)ti * kTile + chunk * 8, chB = (int64_t)tj * kTile + chunk * 8;
-            for (int kt = 0; kt < nkt && ok; ++kt) {
+            for (int piece = 0; piece < nch && ok; ++piece) {
+            const int kt0 = piece * kt_per, kt1 = (kt0 + kt_per < nkt) ? kt0 + kt_per : nkt;
+            const bool first_piece = (piece == 0);
+            load_tokens(kt0, tok_cur);
+            for (int kt = kt0; kt < kt1 && ok; ++kt) {
                 const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
                 ok = mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag);
                 if (!ok) break;
@@ -186,7 +197,7 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_tc_kernel(const HessParam
                         cp_async16_zfill(stage + sub * kSubBytes + drow, v ? (const void *)(xrow + ch) : (const void *)P.X, v);
                     }
                 }
-                if (kt + 1 < nkt) load_tokens(kt + 1, tok_nxt);
+                if (kt + 1 < kt1) load_tokens(kt + 1, tok_nxt);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) tok_cur[i] = tok_nxt[i];
                 cp_async_commit();
@@ -206,9 +217,29 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_tc_kernel(const HessParam
                 mbar_arrive(bar_full + 8 * ((it - pend) % kStages));
                 --pend;
             }
+            if (!ok) break;
+            }   // pieces of the token range
             if (bad_token && P.status) atomicExch(P.status, FORGE_ERR_INVALID);
             if (!ok) break;
-            // ---- epilogue: TMEM -> registers -> global
+        }
+        cp_async_wait<0>();
+    } else if (warp >= 5) {
+        // ------------------------------ epilogue (warps 5..12) ------------------------------
+        // Warp w reads TMEM lanes 32 (w % 4) .. +31 (the hardware's rule) of accumulator half mh = (w - 5) / 4: the
+        // eight warps cover the 256 x 256 tile once.  The producers meanwhile refill the operand ring for the next
+        // piece or tile; the MMA warp resumes when all 256 threads have arrived on acc_empty.
+        const int q = warp & 3, mh = (warp - 5) >> 2;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            const int b = tile / P.ntri;
+            int ti, tj;
+            tile_coords(tile % P.ntri, P.nt, ti, tj);
+            const int64_t n = P.offsets[b + 1] - P.offsets[b];
+            if (n <= 0 || !slot_in_bounds(P, P.offsets[b], n)) continue;
+            const int nkt = (int)((n + kKT - 1) / kKT);
+            const int nch = (nkt + kChunkKT - 1) / kChunkKT;
+            bool ok = true;
+            for (int piece = 0; piece < nch && ok; ++piece) {
+            const bool first_piece = (piece == 0);
             ok = mbar_wait(bar_acc_full, tile_iter & 1u, abort_flag);
             ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld below is warp-aligned: the whole warp goes or none
             if (!ok) break;
@@ -218,17 +249,16 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_tc_kernel(const HessParam
             const float alpha = (float)(2.0 / Ntot);
             const float beta = (float)((double)np / Ntot);
             float *Hb = P.H + (int64_t)b * C * C;
-#pragma unroll 1
-            for (int mh = 0; mh < 2; ++mh) {
-                const int64_t m = (int64_t)ti * kTile + mh * 128 + warp * 32 + lane;
+            {
+                const int64_t m = (int64_t)ti * kTile + mh * 128 + q * 32 + lane;
 #pragma unroll 1
                 for (int cc = 0; cc < 8; ++cc) {
                     const int64_t n0 = (int64_t)tj * kTile + cc * 32;
                     // whole 32x32 sub-block below the diagonal or out of range: nothing to store
-                    const int64_t m_lo = (int64_t)ti * kTile + mh * 128 + warp * 32;
+                    const int64_t m_lo = (int64_t)ti * kTile + mh * 128 + q * 32;
                     if (n0 + 31 < m_lo || n0 >= C || m_lo >= C) continue;  // warp-uniform
                     uint32_t v[32];
-                    tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(mh * 256 + cc * 32), v);
+                    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(mh * 256 + cc * 32), v);
                     tmem_ld_wait();
                     if (m < C) {
                         const bool vec_ok = (C % 4 == 0);
@@ -238,7 +268,30 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_tc_kernel(const HessParam
                             float val[4];
 #pragma unroll
                             for (int e = 0; e < 4; ++e) val[e] = alpha * __uint_as_float(v[4 * g4 + e]);
-                            if (vec_ok && nn0 >= m && nn0 + 3 < C) {
+                            if (!first_piece) {
+                                // later pieces: H += alpha acc as fire-and-forget fp32 additions in L2 (round to
+                                // nearest), on the entry and on its mirror image: both see the same sequence of
+                                // additions, so the matrix stays exactly symmetric, and no load sits in the epilogue
+                                if (vec_ok && nn0 >= m && nn0 + 3 < C) {
+                                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(Hb + m * C + nn0),
+                                                 "f"(val[0]), "f"(val[1]), "f"(val[2]), "f"(val[3])
+                                                 : "memory");
+                                    if (P.mirror) {
+#pragma unroll
+                                        for (int e = 0; e < 4; ++e)
+                                            if (nn0 + e > m) atomicAdd(Hb + (nn0 + e) * C + m, val[e]);
+                                    }
+                                } else {
+#pragma unroll
+                                    for (int e = 0; e < 4; ++e) {
+                                        const int64_t nn = nn0 + e;
+                                        if (nn < C && nn >= m) {
+                                            atomicAdd(Hb + m * C + nn, val[e]);
+                                            if (P.mirror && nn > m) atomicAdd(Hb + nn * C + m, val[e]);
+                                        }
+                                    }
+                                }
+                            } else if (vec_ok && nn0 >= m && nn0 + 3 < C) {
                                 float4 *dst = reinterpret_cast<float4 *>(Hb + m * C + nn0);
                                 if (np > 0) {
                                     const float4 old = *dst;
@@ -270,8 +323,9 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_tc_kernel(const HessParam
             tc_fence_before();
             mbar_arrive(bar_acc_empty);
             ++tile_iter;
+            }   // pieces of the token range
+            if (!ok) break;
         }
-        cp_async_wait<0>();
     } else {
         // ------------------------------ MMA issuer (warp 4) ------------------------------
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
@@ -282,10 +336,14 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_tc_kernel(const HessParam
             if (n <= 0 || !slot_in_bounds(P, P.offsets[b], n)) continue;
             const bool diag = (ti == tj);
             const int nkt = (int)((n + kKT - 1) / kKT);
-            bool ok = mbar_wait(bar_acc_empty, (tile_iter & 1u) ^ 1u, abort_flag);
+            const int nch = (nkt + kChunkKT - 1) / kChunkKT, kt_per = (nkt + nch - 1) / nch;
+            bool ok = true;
+            for (int piece = 0; piece < nch && ok; ++piece) {
+            const int kt0 = piece * kt_per, kt1 = (kt0 + kt_per < nkt) ? kt0 + kt_per : nkt;
+            ok = mbar_wait(bar_acc_empty, (tile_iter & 1u) ^ 1u, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            for (int kt = 0; kt < nkt && ok; ++kt) {
+            for (int kt = kt0; kt < kt1 && ok; ++kt) {
                 const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
                 ok = mbar_wait(bar_full + 8 * s, ph, abort_flag);
                 if (!ok) break;
@@ -299,7 +357,7 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_tc_kernel(const HessParam
 #pragma unroll
                         for (int mh = 0; mh < 2; ++mh) {
                             const uint64_t adesc = make_desc(a_base + mh * 2 * kSubBytes + kk * 2048);
-                            umma_bf16(tmem_base + mh * 256, adesc, bdesc, (kt > 0 || kk > 0) ? 1u : 0u);
+                            umma_bf16(tmem_base + mh * 256, adesc, bdesc, (kt > kt0 || kk > 0) ? 1u : 0u);
                         }
                     }
                     umma_commit(bar_empty + 8 * s);  // frees the stage once these MMAs have read it
@@ -311,6 +369,8 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_tc_kernel(const HessParam
             if (lane == 0) umma_commit(bar_acc_full);
             __syncwarp();
             ++tile_iter;
+            }   // pieces of the token range
+            if (!ok) break;
         }
     }
     // ------------------------------ teardown ------------------------------

@@ -362,3 +362,28 @@ def test_presplit_factor_pieces_give_identical_codes(nb, R, C, sparse):
         assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
     else:
         assert torch.equal(a, b)
+
+
+def test_full_width_expert_matches_the_oracle():
+    """The benchmark recipe (W4 symmetric g128, activation order, inversion-free solve) at the FULL hidden size of the
+    DeepSeek-V3 / Kimi-K2 shapes, 7168, against the oracle: one expert with 8192 tokens, gate / up [512, 7168], down
+    [7168, 512].  At this width the Hessian goes through every level of the blocked factorisation (outer blocks of 512,
+    block inverse, the multiplication for the rows behind a block, 256 x 256 update tiles) and the solver through its
+    wide-matrix build (56 column blocks, errors through tensor memory)."""
+    from forge import synth, moe
+    shape = synth.LayerShape("w", 1, 0, 7168, 512, 8192, 1)
+    X = synth.student_t_activations(shape.tokens, shape.hidden, seed=77)
+    ids = torch.zeros((shape.tokens, 1), dtype=torch.int32)
+    Wg, Wu, Wd = synth.expert_weights(shape, range(1), seed=77)
+    cfg = moe.MoEQuantConfig(bits=4, group_size=128, symmetric=True, quantization_scale="absmax",
+                             quantization_order="activation", rel_damp=0.01, algorithm="gptq")
+    qz = moe.MoELayerQuantizer(cfg)
+    Wdev = [w.to(DEV) for w in (Wg, Wu, Wd)]
+    out = qz.quantize_experts(X.to(DEV), ids.to(DEV), *Wdev)
+    assert qz._form([Wdev[0]]) == 1
+    lists = _token_lists(ids, 1, shape.tokens, 0)
+    acts = _engine_acts(out, lists)
+    kw = dict(bits=4, group_size=128, symmetric=True, quantization_scale="absmax", quantization_order="activation",
+              rel_damp=0.01, algorithm="gptq")
+    worst = _check_layer(out, lists, X, (Wg, Wu, Wd), acts, kw, 128)
+    assert worst >= 0.995
