@@ -130,3 +130,24 @@ def test_solver_is_idempotent_on_quantised_weights():
     q2 = ops.gptq_solve_batched(Wq, U, s, z, gs, 4, status=st)
     assert int(st.item()) == 0
     assert float((q2 == q1).float().mean()) >= 0.9999
+
+
+def test_hessian_error_does_not_grow_with_the_token_count():
+    """The tensor core adds to its fp32 accumulator with truncation, so one long accumulation drifts (3e-4 relative
+    after 65536 tokens).  The kernel accumulates at most 4096 tokens per pass and adds the passes in fp32: the error
+    against float64 stays at the level of an fp32 sum for a shared expert's token count as for a cold expert's, well
+    inside the 1e-4 the Hessian is allowed."""
+    from forge import synth
+    ops = _ops()
+    C = 1024
+    errs = {}
+    for T in (2048, 65536):
+        X = synth.student_t_activations(T, C, seed=5, device=DEV)
+        H = torch.zeros((1, C, C), dtype=torch.float32, device=DEV)
+        offs = torch.tensor([0, T], dtype=torch.int64, device=DEV)
+        ops.hessian_grouped(X, C, None, offs, H)
+        Xd = X.double()
+        H64 = (2.0 / T) * (Xd.T @ Xd)
+        errs[T] = float((H[0].double() - H64).norm() / H64.norm())
+        assert torch.equal(H[0], H[0].T)                       # the mirror image follows the same additions
+    assert errs[2048] <= 2e-5 and errs[65536] <= 3e-5, errs
