@@ -37,6 +37,7 @@ constexpr int kKT = 64;                       // tokens per k-tile
 // tile's token range is therefore accumulated in pieces of at most kChunkKT k-tiles; each piece is added to H in the
 // epilogue in ordinary fp32 arithmetic.  With 4096 tokens per piece the error stays below 2e-5 for any token count.
 constexpr int kChunkKT = 64;
+constexpr int kMaxSortedSlots = 512;           // more slots than this keep their index order
 constexpr int kSubBytes = kKT * 128;          // one 64-channel x 64-token sub-tile: 8 KB
 constexpr int kOperandBytes = 4 * kSubBytes;  // 256 channels: 32 KB
 constexpr int kStageBytes = 2 * kOperandBytes;
@@ -124,9 +125,32 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_tc_kernel(const HessParam
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    // Slots in order of decreasing token count.  Tiles go to the CTAs round-robin along this order, so tiles of similar
+    // cost are neighbours: the CTAs' loads differ by at most one tile of each weight class, and the last, partly filled
+    // round consists of the cheapest tiles.  (In index order every heavy slot leaves some CTAs one heavy tile ahead, and
+    // with a few hot experts among many cold ones those surpluses pile up: 42.9 ms against 30 ms on a rank of four.)
+    // Every CTA computes the same order itself; results do not depend on it (a tile is still one CTA's sum).
+    __shared__ int32_t s_cnt[kMaxSortedSlots];
+    __shared__ int16_t s_order[kMaxSortedSlots];
+    const bool sorted = P.nb <= kMaxSortedSlots;
+    if (sorted) {
+        for (int i = tid; i < P.nb; i += kThreads) {
+            const int64_t n = P.offsets[i + 1] - P.offsets[i];
+            s_cnt[i] = (int32_t)(n < 0 ? 0 : (n > 0x7fffffff ? 0x7fffffff : n));
+        }
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    if (sorted) {
+        for (int i = tid; i < P.nb; i += kThreads) {
+            const int32_t ni = s_cnt[i];
+            int rank = 0;
+            for (int j = 0; j < P.nb; ++j) rank += (s_cnt[j] > ni) || (s_cnt[j] == ni && j < i);
+            s_order[rank] = (int16_t)i;
+        }
+        __syncthreads();
+    }
     const uint32_t tmem_base = *tmem_holder;
 
     const int64_t C = P.C;
@@ -140,7 +164,7 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_tc_kernel(const HessParam
         const int chunk = lane & 7;   // 16-byte chunk within the 128-byte row
         int pend = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-            const int b = tile / P.ntri;
+            const int b = sorted ? (int)s_order[tile / P.ntri] : tile / P.ntri;
             int ti, tj;
             tile_coords(tile % P.ntri, P.nt, ti, tj);
             const int64_t off = P.offsets[b];
@@ -230,7 +254,7 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_tc_kernel(const HessParam
         // piece or tile; the MMA warp resumes when all 256 threads have arrived on acc_empty.
         const int q = warp & 3, mh = (warp - 5) >> 2;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-            const int b = tile / P.ntri;
+            const int b = sorted ? (int)s_order[tile / P.ntri] : tile / P.ntri;
             int ti, tj;
             tile_coords(tile % P.ntri, P.nt, ti, tj);
             const int64_t n = P.offsets[b + 1] - P.offsets[b];
@@ -329,7 +353,7 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_tc_kernel(const HessParam
     } else {
         // ------------------------------ MMA issuer (warp 4) ------------------------------
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-            const int b = tile / P.ntri;
+            const int b = sorted ? (int)s_order[tile / P.ntri] : tile / P.ntri;
             int ti, tj;
             tile_coords(tile % P.ntri, P.nt, ti, tj);
             const int64_t n = P.offsets[b + 1] - P.offsets[b];
