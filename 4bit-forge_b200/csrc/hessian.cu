@@ -128,8 +128,8 @@ __global__ void __launch_bounds__(kThreads, 1) hessian_tc_kernel(const HessParam
     // Slots in order of decreasing token count.  Tiles go to the CTAs round-robin along this order, so tiles of similar
     // cost are neighbours: the CTAs' loads differ by at most one tile of each weight class, and the last, partly filled
     // round consists of the cheapest tiles.  (In index order every heavy slot leaves some CTAs one heavy tile ahead, and
-    // with a few hot experts among many cold ones those surpluses pile up: 42.9 ms against 30 ms on a rank of four.)
-    // Every CTA computes the same order itself; results do not depend on it (a tile is still one CTA's sum).
+    // with a few hot experts among many cold ones those surpluses can pile up on the same CTAs.)  Every CTA computes
+    // the same order itself; results do not depend on it (a tile is still one CTA's sum).
     __shared__ int32_t s_cnt[kMaxSortedSlots];
     __shared__ int16_t s_order[kMaxSortedSlots];
     const bool sorted = P.nb <= kMaxSortedSlots;

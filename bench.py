@@ -594,6 +594,15 @@ def run_ours(args, rank, world, local_rank):
                         "executed_frac_of_tf32_peak": 3.0 * ach / (tf_peak / 2.0),
                         "note": "fp32 algorithm as TF32 x3 on tcgen05; the column loop between the MMAs is a serial "
                                 "dependency chain per weight row"}
+            if top == "forge_gptq_solve_batched":
+                # The solver's MMAs are M128 x N128 x K8 kind::tf32 (a 128-column block per accumulator).  A stand-alone
+                # issue loop of that instruction sustains one per 101 cycles per SM on this part whatever the operand
+                # layout and the number of accumulators (N = 256: 161 cycles), i.e. 2592 flop/cycle/SM: the ceiling of
+                # any kernel built from this instruction shape, at the SM clock seen during the timed region.
+                mhz = (clk or {}).get("sm_mhz") or 1965.0
+                floor = 2.0 * 128 * 128 * 8 / 101.1 * 148 * mhz * 1e6 / 1e12
+                roofline["tf32_m128n128k8_issue_peak_tflops"] = floor
+                roofline["executed_frac_of_issue_peak"] = 3.0 * ach / floor
         else:
             ab = alg_bytes.get(top) or 0.0
             ach = ab / t_s / 1e9
