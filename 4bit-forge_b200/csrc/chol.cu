@@ -690,11 +690,15 @@ __global__ void __launch_bounds__(kSyrk2Threads, 1) chol_syrk256_tc_kernel(float
 // M = L11^-1 for the W x W diagonal block that starts at column ob (W = 64 P), from the 64x64 inverses the diagonal
 // kernel left behind:  M[p][p] = Dinv_p,  M[p][q] = -Dinv_p * sum_{q <= r < p} L[p][r] M[r][q]  (p > q).
 // CTA (q, b) owns block column q of matrix b and walks p = q .. P-1 with the finished blocks in shared memory.
-// Output MT[k][c] = M[c][k] (row-major [W][W]): rows of MT are K rows of the operand the kernel below multiplies by.
-// Only the zero block the multiplication reads is cleared (k-block 2t+1 against c-block 2t: same 128-column tile).
+// Output, row-major [W][W]: transposed != 0: MT[k][c] = M[c][k] (rows of MT are K rows of the operand of L21 = A21 M^T);
+// transposed == 0: M itself (K rows of the operand of T = L21 M, triangular inverse).  Only the zero block the
+// multiplication reads is cleared (the off-diagonal 64 x 64 block of a 128-column tile).  With Uall given, the blocks
+// below the diagonal of  diag(L) M  also go to U[J, J] (the scaled inverse the triangular-inverse pass builds; its
+// 64 x 64 diagonal blocks are the diagonal kernel's).
 __global__ void __launch_bounds__(256) chol_block_inv_kernel(const float *__restrict__ Aall, int64_t C, int64_t ob,
                                                              int P, int nblk, const float *__restrict__ dinv_all,
-                                                             float *__restrict__ minv_all) {
+                                                             float *__restrict__ minv_all, int transposed,
+                                                             float *__restrict__ Uall) {
     extern __shared__ __align__(16) float binv_smem[];
     float *Xs = binv_smem;                 // [P][64][64]  finished blocks of this block column
     float *Ls = Xs + (int64_t)P * 4096;    // [64][65]     left operand of the current product
@@ -704,10 +708,14 @@ __global__ void __launch_bounds__(256) chol_block_inv_kernel(const float *__rest
     const float *A = Aall + (int64_t)b * C * C;
     float *MT = minv_all + (int64_t)b * W * W;
     const int kb0 = (int)(ob / 64);
+    float *U = Uall ? Uall + (int64_t)b * C * C : nullptr;
     if (q & 1) {
         for (int idx = tid; idx < 1024; idx += 256) {
             const int j = idx >> 4, i4 = (idx & 15) * 4;
-            *reinterpret_cast<float4 *>(MT + (int64_t)(64 * q + j) * W + 64 * (q - 1) + i4) = make_float4(0.f, 0.f, 0.f, 0.f);
+            // transposed: rows of k-block q against columns of c-block q - 1; else rows of block q - 1, columns of q
+            float *z = transposed ? MT + (int64_t)(64 * q + j) * W + 64 * (q - 1) + i4
+                                  : MT + (int64_t)(64 * (q - 1) + j) * W + 64 * q + i4;
+            *reinterpret_cast<float4 *>(z) = make_float4(0.f, 0.f, 0.f, 0.f);
         }
     }
     auto load_block = [&](const float *src, int64_t ld) {     // Ls[i][k] = src[i * ld + k]
@@ -769,11 +777,27 @@ __global__ void __launch_bounds__(256) chol_block_inv_kernel(const float *__rest
         for (int ii = 0; ii < 4; ++ii)
             *reinterpret_cast<float4 *>(Xp + (ty * 4 + ii) * 64 + tx * 4) =
                 make_float4(acc[ii][0], acc[ii][1], acc[ii][2], acc[ii][3]);
-        // MT[64 q + j][64 p + i] = X_p[i][j]: four consecutive i per store
+        if (transposed) {
+            // MT[64 q + j][64 p + i] = X_p[i][j]: four consecutive i per store
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj)
-            *reinterpret_cast<float4 *>(MT + (int64_t)(64 * q + tx * 4 + jj) * W + 64 * p + ty * 4) =
-                make_float4(acc[0][jj], acc[1][jj], acc[2][jj], acc[3][jj]);
+            for (int jj = 0; jj < 4; ++jj)
+                *reinterpret_cast<float4 *>(MT + (int64_t)(64 * q + tx * 4 + jj) * W + 64 * p + ty * 4) =
+                    make_float4(acc[0][jj], acc[1][jj], acc[2][jj], acc[3][jj]);
+        } else {
+#pragma unroll
+            for (int ii = 0; ii < 4; ++ii)
+                *reinterpret_cast<float4 *>(MT + (int64_t)(64 * p + ty * 4 + ii) * W + 64 * q + tx * 4) =
+                    make_float4(acc[ii][0], acc[ii][1], acc[ii][2], acc[ii][3]);
+        }
+        if (U && p > q) {
+#pragma unroll
+            for (int ii = 0; ii < 4; ++ii) {
+                const int64_t r = ob + 64 * p + ty * 4 + ii;
+                const float dg = A[r * C + r];            // L[r][r]
+                *reinterpret_cast<float4 *>(U + r * C + ob + 64 * q + tx * 4) =
+                    make_float4(dg * acc[ii][0], dg * acc[ii][1], dg * acc[ii][2], dg * acc[ii][3]);
+            }
+        }
         __syncthreads();
     }
 }
@@ -789,8 +813,17 @@ __global__ void __launch_bounds__(256) chol_block_inv_kernel(const float *__rest
 // contiguous bytes of a K row: no bank conflict).  B pieces come from MT exactly like the update kernel's operands.
 // The result goes to the lower triangle (row-major) and, transposed, to the upper triangle, where the update kernel
 // reads its operands.
+//
+// The same kernel serves the blocked triangular inverse (MODE 1 and 2), which walks the outer blocks from the last to
+// the first:  (D L^-1)[below, J] = -(D L^-1)[below, below] * ( L[below, J] * M_JJ ),  M_JJ the block inverse:
+//   MODE 1: T = L21 * M_JJ in place of L21 (B rows from the row-major block inverse, K range [128 tj, W), column tiles
+//           in ascending order so that no tile overwrites columns a later one reads);
+//   MODE 2: U21 = -U22 * T, U22 = the finished scaled inverse of the rows below (row-major, lower triangular: K ends
+//           at the strip's last row, entries right of the diagonal read as zero), T from A.
 constexpr int kTrsmThreads = 160;
-__global__ void __launch_bounds__(kTrsmThreads, 3) chol_trsm_tc_kernel(float *__restrict__ Aall, int64_t C, int64_t ob, int W,
+template <int MODE>
+__global__ void __launch_bounds__(kTrsmThreads, 3) chol_trsm_tc_kernel(float *__restrict__ Aall, float *__restrict__ Uall,
+                                                                        int64_t C, int64_t ob, int W,
                                                                         const float *__restrict__ minv_all, int nb,
                                                                         int32_t *status) {
     using namespace forge::tc;
@@ -839,12 +872,17 @@ __global__ void __launch_bounds__(kTrsmThreads, 3) chol_trsm_tc_kernel(float *__
             const int b = unit / nstrips;
             const int64_t i0 = (int64_t)(unit % nstrips) * 128;
             float *A = Aall + (int64_t)b * C * C;
+            float *U = (MODE == 2) ? Uall + (int64_t)b * C * C : nullptr;
             const float *MT = minv_all + (int64_t)b * W * W;
             const bool a_ok = (i0 + tid) < m;
-            const float *srcA = A + (oe + i0 + tid) * C + ob;
-            for (int tj = ntj - 1; tj >= 0 && ok; --tj) {
-                const int K = 128 * (tj + 1);
-                const float *srcB = MT + 128 * tj + 4 * c4;
+            for (int tt = 0; tt < ntj && ok; ++tt) {
+                const int tj = (MODE == 0) ? ntj - 1 - tt : tt;
+                // K range of this tile and where its operands start
+                const int k0 = (MODE == 1) ? 128 * tj : 0;
+                const int K = (MODE == 0) ? 128 * (tj + 1) : (MODE == 1) ? W - 128 * tj : (int)(i0 + 128 < m ? i0 + 128 : m);
+                const float *srcA = (MODE == 2) ? U + (oe + i0 + tid) * C + oe : A + (oe + i0 + tid) * C + ob + k0;
+                const float *srcB = (MODE == 2) ? A + oe * C + ob + 128 * tj + 4 * c4 : MT + (int64_t)k0 * W + 128 * tj + 4 * c4;
+                const int64_t ldb = (MODE == 2) ? C : (int64_t)W;
 #pragma unroll 1
                 for (int half = 0; half < K / 32 && ok; ++half) {
                     float4 ra[8], rbv[4][2];
@@ -855,7 +893,7 @@ __global__ void __launch_bounds__(kTrsmThreads, 3) chol_trsm_tc_kernel(float *__
                     for (int d = 0; d < 4; ++d)
 #pragma unroll
                         for (int h = 0; h < 2; ++h)
-                            rbv[d][h] = ldg128_here(srcB + (int64_t)(half * 32 + d * kKS + jB + 4 * h) * W);
+                            rbv[d][h] = ldg128_here(srcB + (int64_t)(half * 32 + d * kKS + jB + 4 * h) * ldb);
 #pragma unroll
                     for (int d = 0; d < 4; ++d) {
                         if (!ok) break;
@@ -863,8 +901,15 @@ __global__ void __launch_bounds__(kTrsmThreads, 3) chol_trsm_tc_kernel(float *__
                         ok = mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag);
                         if (!ok) break;
                         uint8_t *stage = ring + s * kSyrkStageBytes;
-                        const float av[8] = {ra[2 * d].x, ra[2 * d].y, ra[2 * d].z, ra[2 * d].w,
-                                             ra[2 * d + 1].x, ra[2 * d + 1].y, ra[2 * d + 1].z, ra[2 * d + 1].w};
+                        float av[8] = {ra[2 * d].x, ra[2 * d].y, ra[2 * d].z, ra[2 * d].w,
+                                       ra[2 * d + 1].x, ra[2 * d + 1].y, ra[2 * d + 1].z, ra[2 * d + 1].w};
+                        if (MODE == 2) {
+                            // lower triangular operand: column k of row i counts only for k <= i
+                            const int64_t kfirst = (int64_t)half * 32 + d * kKS;
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                if (kfirst + j > i0 + tid) av[j] = 0.0f;
+                        }
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
                             const float hi = tf32_round(av[j]);
@@ -897,15 +942,18 @@ __global__ void __launch_bounds__(kTrsmThreads, 3) chol_trsm_tc_kernel(float *__
                     tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(qd * 32), v);
                     tmem_ld_wait();
                     if (row < m) {
-                        float *dst = A + (oe + row) * C + col0 + qd * 32;
+                        const float sgn = (MODE == 2) ? -1.0f : 1.0f;
+                        float *dst = ((MODE == 2) ? U : A) + (oe + row) * C + col0 + qd * 32;
 #pragma unroll
                         for (int g4 = 0; g4 < 8; ++g4)
                             *reinterpret_cast<float4 *>(dst + 4 * g4) =
-                                make_float4(__uint_as_float(v[4 * g4 + 0]), __uint_as_float(v[4 * g4 + 1]),
-                                            __uint_as_float(v[4 * g4 + 2]), __uint_as_float(v[4 * g4 + 3]));
-                        float *dstT = A + (col0 + qd * 32) * C + oe + row;
+                                make_float4(sgn * __uint_as_float(v[4 * g4 + 0]), sgn * __uint_as_float(v[4 * g4 + 1]),
+                                            sgn * __uint_as_float(v[4 * g4 + 2]), sgn * __uint_as_float(v[4 * g4 + 3]));
+                        if (MODE == 0) {
+                            float *dstT = A + (col0 + qd * 32) * C + oe + row;
 #pragma unroll
-                        for (int c = 0; c < 32; ++c) dstT[(int64_t)c * C] = __uint_as_float(v[c]);
+                            for (int c = 0; c < 32; ++c) dstT[(int64_t)c * C] = __uint_as_float(v[c]);
+                        }
                     }
                 }
                 tc_fence_before();
@@ -914,8 +962,11 @@ __global__ void __launch_bounds__(kTrsmThreads, 3) chol_trsm_tc_kernel(float *__
     } else {
         bool ok = true;
         for (int unit = blockIdx.x; unit < total && ok; unit += gridDim.x) {
-            for (int tj = ntj - 1; tj >= 0 && ok; --tj) {
-                const int kSteps = 128 * (tj + 1) / kKS;
+            const int64_t i0 = (int64_t)(unit % nstrips) * 128;
+            for (int tt = 0; tt < ntj && ok; ++tt) {
+                const int tj = (MODE == 0) ? ntj - 1 - tt : tt;
+                const int K = (MODE == 0) ? 128 * (tj + 1) : (MODE == 1) ? W - 128 * tj : (int)(i0 + 128 < m ? i0 + 128 : m);
+                const int kSteps = K / kKS;
                 for (int ks = 0; ks < kSteps && ok; ++ks) {
                     const uint32_t s = it % kSyrkStages, ph = (it / kSyrkStages) & 1u;
                     ok = mbar_wait(bar_full + 8 * s, ph, abort_flag);
@@ -1129,7 +1180,7 @@ static void launch_factor(float *A, int nb, int64_t C, float *U, float *udiag, i
             chol_syrk_tc_kernel<<<grid, kSyrkThreads, kSyrkSmem, st>>>(A, C, kb, K, r0, ncols, nb, status, row_end);
             FORGE_NOTE_LAUNCH();
         };
-        cudaFuncSetAttribute(chol_trsm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSyrkSmem);
+        cudaFuncSetAttribute(chol_trsm_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSyrkSmem);
         cudaFuncSetAttribute(chol_syrk256_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSyrk2Smem);
         int dev = 0, sms = 148;
         cudaGetDevice(&dev);
@@ -1150,11 +1201,11 @@ static void launch_factor(float *A, int nb, int64_t C, float *U, float *udiag, i
             if (oe < C) {
                 // the rows behind it: block inverse, ONE multiplication for the panel, ONE update of the rest
                 const int P = (int)(outer / NB);
-                chol_block_inv_kernel<<<dim3(P, nb), 256, binv_smem, st>>>(A, C, ob, P, nblk, dinv, minv);
+                chol_block_inv_kernel<<<dim3(P, nb), 256, binv_smem, st>>>(A, C, ob, P, nblk, dinv, minv, 1, nullptr);
                 FORGE_NOTE_LAUNCH();
                 const int64_t units = (int64_t)nb * cdiv(C - oe, (int64_t)128);
-                chol_trsm_tc_kernel<<<(unsigned)(units < 148 * 3 ? units : 148 * 3), kTrsmThreads, kSyrkSmem, st>>>(
-                    A, C, ob, (int)outer, minv, nb, status);
+                chol_trsm_tc_kernel<0><<<(unsigned)(units < 148 * 3 ? units : 148 * 3), kTrsmThreads, kSyrkSmem, st>>>(
+                    A, nullptr, C, ob, (int)outer, minv, nb, status);
                 FORGE_NOTE_LAUNCH();
                 if (C - oe > 256) {
                     const int nt2 = (int)cdiv(C - oe, (int64_t)256);
@@ -1196,10 +1247,39 @@ extern "C" int forge_chol_inv_upper_batched(float *A, int nb, int64_t C, float *
     float *dinv = (float *)ws;
     const int vec = (C % 4 == 0) && ((uintptr_t)A % 16 == 0) && ((uintptr_t)U % 16 == 0);
     launch_factor(A, nb, C, U, udiag, info, dinv, vec, st);
-    for (int j = nblk - 2; j >= 0; --j) {
-        const int64_t m = C - (int64_t)(j + 1) * NB;
-        const unsigned nt = (unsigned)cdiv(m, TM);
-        trtri_step_kernel<<<dim3(nt, nb), 256, 0, st>>>(A, U, C, j, nblk, dinv, vec); FORGE_NOTE_LAUNCH();
+    const char *env = getenv("FORGE_SYRK_IMPL");
+    const bool simt = env && strcmp(env, "simt") == 0;
+    const int64_t outer = chol_outer(C);
+    if (vec && !simt && C % 128 == 0 && C > outer) {
+        // blocked triangular inverse on the tensor cores, outer blocks from the last to the first: block inverse
+        // (also D M_JJ into U[J, J]), T = L21 M_JJ in place, U21 = -U22 T
+        float *minv = dinv + (int64_t)nb * nblk * 2 * NB * NB;
+        int32_t *status = reinterpret_cast<int32_t *>(reinterpret_cast<char *>(dinv) + forge_chol_workspace_bytes(nb, C) - 256);
+        cudaFuncSetAttribute(chol_trsm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSyrkSmem);
+        cudaFuncSetAttribute(chol_trsm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSyrkSmem);
+        const int binv_smem = (int)((outer / NB * 4096 + 64 * 65 + 4096) * sizeof(float));
+        cudaFuncSetAttribute(chol_block_inv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, binv_smem);
+        for (int64_t ob = ((C - 1) / outer) * outer; ob >= 0; ob -= outer) {
+            const int64_t oe = imin64(C, ob + outer);
+            const int P = (int)((oe - ob) / NB);
+            chol_block_inv_kernel<<<dim3(P, nb), 256, binv_smem, st>>>(A, C, ob, P, nblk, dinv, minv, 0, U);
+            FORGE_NOTE_LAUNCH();
+            if (oe < C) {
+                const int64_t units = (int64_t)nb * cdiv(C - oe, (int64_t)128);
+                const unsigned grid = (unsigned)(units < 148 * 3 ? units : 148 * 3);
+                chol_trsm_tc_kernel<1><<<grid, kTrsmThreads, kSyrkSmem, st>>>(A, U, C, ob, (int)outer, minv, nb, status);
+                FORGE_NOTE_LAUNCH();
+                chol_trsm_tc_kernel<2><<<grid, kTrsmThreads, kSyrkSmem, st>>>(A, U, C, ob, (int)outer, minv, nb, status);
+                FORGE_NOTE_LAUNCH();
+            }
+        }
+        status_to_info_kernel<<<(nb + 127) / 128, 128, 0, st>>>(info, nb, status); FORGE_NOTE_LAUNCH();
+    } else {
+        for (int j = nblk - 2; j >= 0; --j) {
+            const int64_t m = C - (int64_t)(j + 1) * NB;
+            const unsigned nt = (unsigned)cdiv(m, TM);
+            trtri_step_kernel<<<dim3(nt, nb), 256, 0, st>>>(A, U, C, j, nblk, dinv, vec); FORGE_NOTE_LAUNCH();
+        }
     }
     dim3 g2((unsigned)cdiv(C, 32), (unsigned)cdiv(C, 8), nb);
     rotate_upper_kernel<<<g2, dim3(32, 8), 0, st>>>(U, C, info, udiag); FORGE_NOTE_LAUNCH();
