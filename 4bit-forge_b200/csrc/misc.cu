@@ -940,6 +940,11 @@ __device__ __forceinline__ uint64_t pack_one_group(const uint32_t words[8], uint
 __global__ void pack_sparse14_kernel(const uint8_t *__restrict__ q, const uint32_t *__restrict__ M,
                                      const float *__restrict__ scales, int64_t R, int64_t C, int64_t G32,
                                      int64_t G2, ulonglong2 *__restrict__ out, int vec_ok) {
+    // blockIdx.y = matrix of the batch
+    q += (int64_t)blockIdx.y * R * C;
+    M += (int64_t)blockIdx.y * G32 * R;
+    scales += (int64_t)blockIdx.y * G32 * R;
+    out += (int64_t)blockIdx.y * G2 * R;
     const int64_t total = G2 * R;
     for (int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; tid < total;
          tid += (int64_t)gridDim.x * blockDim.x) {
@@ -987,4 +992,19 @@ extern "C" int forge_pack_sparse14(const uint8_t *q, const uint32_t *M, const fl
     pack_sparse14_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(q, M, scales32, R, C, G32, G2,
                                                                  (ulonglong2 *)out, vec_ok); FORGE_NOTE_LAUNCH();
     return check_launch("forge_pack_sparse14");
+}
+
+extern "C" int forge_pack_sparse14_batched(const uint8_t *q, const uint32_t *M, const float *scales32, int nb, int64_t R,
+                                           int64_t C, uint64_t *out, void *stream) {
+    FORGE_REQUIRE(q && M && scales32 && out, "null pointer");
+    FORGE_REQUIRE(nb > 0 && nb <= 65535 && R > 0 && C > 0, "bad sizes");
+    FORGE_REQUIRE((uintptr_t)out % 16 == 0, "output must be 16-byte aligned");
+    const int64_t G32 = cdiv(C, 32), G2 = (G32 + 1) >> 1;
+    // every matrix of the batch starts R * C bytes after the previous one: 16-byte accesses need that to be a multiple
+    const int vec_ok = (C % 16 == 0) && ((uintptr_t)q % 16 == 0) && ((R * C) % 16 == 0);
+    const int per = (int)imin64(cdiv(G2 * R, 256), cdiv((int64_t)148 * 32, (int64_t)nb) + 1);
+    pack_sparse14_kernel<<<dim3((unsigned)per, (unsigned)nb), 256, 0, (cudaStream_t)stream>>>(
+        q, M, scales32, R, C, G32, G2, (ulonglong2 *)out, vec_ok);
+    FORGE_NOTE_LAUNCH();
+    return check_launch("forge_pack_sparse14_batched");
 }

@@ -62,6 +62,7 @@ _PROTOS = {
     "forge_dequantize": (_c_int, [_ptr, _ptr, _ptr, _c_i64, _c_i64, _c_int, _ptr, _c_int, _ptr]),
     "forge_pack_int4": (_c_int, [_ptr, _ptr, _c_i64, _c_i64, _c_int, _ptr, _ptr]),
     "forge_pack_sparse14": (_c_int, [_ptr, _ptr, _ptr, _c_i64, _c_i64, _ptr, _ptr]),
+    "forge_pack_sparse14_batched": (_c_int, [_ptr, _ptr, _ptr, _c_int, _c_i64, _c_i64, _ptr, _ptr]),
     "forge_sparse14_gemm": (_c_int, [_ptr, _ptr, _c_i64, _c_i64, _c_i64, _c_i64, _ptr, _ptr]),
     "forge_sparse14_moe_w13_swiglu": (_c_int, [_ptr, _ptr, _c_i64, _c_i64, _ptr, _ptr, _ptr, _c_int, _c_i64, _c_i64, _c_i64, _ptr, _ptr]),
     "forge_sparse14_moe_w2": (_c_int, [_ptr, _ptr, _c_i64, _c_i64, _ptr, _ptr, _ptr, _c_int, _c_i64, _c_i64, _c_i64, _ptr, _ptr]),

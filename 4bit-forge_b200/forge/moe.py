@@ -269,11 +269,8 @@ class MoELayerQuantizer:
             # one scale per 32 columns: a group scale repeated gs/32 times (quant.py:438-440 assumes gs == 32)
             rep = cfg.group_size // 32
             G32 = (C + 31) // 32
-            packed = []
-            for b in range(nb):
-                s32 = scales[b].repeat_interleave(rep, dim=1)[:, :G32].transpose(0, 1).contiguous()
-                packed.append(ops.pack_sparse14(q[b], M[b], s32))
-            return {"wpair": torch.stack(packed)}
+            s32 = scales.reshape(nb, R, -1).repeat_interleave(rep, dim=2)[:, :, :G32].transpose(1, 2).contiguous()
+            return {"wpair": ops.pack_sparse14_batched(q.contiguous(), M.contiguous(), s32)}
         return {"weight_packed": ops.pack_int4(q, qzeros.reshape(-1), cfg.group_size),
                 "weight_scale": scales.to(torch.float16)}
 

@@ -288,6 +288,16 @@ def pack_sparse14(q_rc, M, scales32):
     return out
 
 
+def pack_sparse14_batched(q, M, scales32):
+    """q [nb,R,C] u8, M [nb,G32,R], scales32 [nb,G32,R] fp32 -> Wpair int64 bit patterns [nb,G2,R,2], one launch."""
+    nb, R, C = q.shape
+    G32 = (C + 31) // 32
+    assert M.shape == (nb, G32, R) and scales32.shape == (nb, G32, R)
+    out = torch.empty((nb, (G32 + 1) // 2, R, 2), dtype=torch.int64, device=_dev(q))
+    call("forge_pack_sparse14_batched", ptr(q), ptr(M), ptr(scales32), nb, R, C, ptr(out), stream_ptr())
+    return out
+
+
 def sparse14_gemm(wpair: torch.Tensor, X: torch.Tensor) -> torch.Tensor:
     """Y = X @ What^T with What decoded from the Wpair words [G2, R, 2] (forge_sparse14_gemm).  X bf16 [N, C]."""
     assert X.dtype == torch.bfloat16 and X.dim() == 2 and wpair.dim() == 3 and wpair.shape[2] == 2

@@ -286,6 +286,10 @@ int forge_pack_int4(const uint8_t *q, const float *qzeros, int64_t rows, int64_t
  * Replaces kernels.pack_sparsegptq14_to_u64x2, forge/backend/cuda/bitpacking_sparsegptq14.cu:58-175. */
 int forge_pack_sparse14(const uint8_t *q, const uint32_t *M, const float *scales32, int64_t R, int64_t C,
                         uint64_t *out, void *stream);
+/* The same for nb matrices in one launch: q [nb,R,C], M [nb,ceil(C/32),R], scales32 [nb,ceil(C/32),R] -> out
+ * [nb,G2,R,2] (a layer's experts; the reference calls its packer once per Linear, quant.py:438-447). */
+int forge_pack_sparse14_batched(const uint8_t *q, const uint32_t *M, const float *scales32, int nb, int64_t R, int64_t C,
+                                uint64_t *out, void *stream);
 
 /* ---- inference over the Wpair layout ------------------------------------------
  * Y[n, r] = bf16( sum_c X[n, c] * What[r, c] ), What decoded on the fly from wpair [ceil(C/64), R, 2] uint64
