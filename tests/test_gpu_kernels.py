@@ -203,7 +203,7 @@ def _factor_ref(Hd):
     return T / T.diag()[:, None], T.diag()
 
 
-@pytest.mark.parametrize("C", [32, 64, 96, 99, 130, 200, 512, 1100])
+@pytest.mark.parametrize("C", [32, 64, 96, 99, 130, 200, 384, 512, 640, 1100])
 def test_cholesky_inverse_factor(C):
     ops = _ops()
     nb = 3
