@@ -594,31 +594,44 @@ gather_damp_stream_kernel(const float *__restrict__ H, int64_t C, const int32_t 
             }
             __syncthreads();
         }
-        for (int64_t jo = (int64_t)threadIdx.x * 4; jo < C; jo += (int64_t)blockDim.x * 4) {
-            const int64_t jlo = C - 4 - jo;   // positions jlo+3 .. jlo <-> output columns jo .. jo+3
-            const uint4 cq = *reinterpret_cast<const uint4 *>(code + jlo);
-            const uint32_t cws[4] = {cq.w, cq.z, cq.y, cq.x};
-            for (int rr = 0; rr < R; ++rr) {
-                const int64_t i = g * R + rr;
-                if (i >= C) break;
-                const uint32_t cwi = code[i] | (inv ? 0x40000000u : 0u);
-                const bool row_wz = (cwi & 0x80000000u) != 0u, row_dead = (cwi & 0x40000000u) != 0u;
-                const uint32_t pi = cwi & 0x3FFFFFFFu;
-                const float *row = buf + (int64_t)rr * C;
-                float v[4];
+        // rows outermost: a row's facts (source row, dead / zero flags, output pointer) are set up once; the inner loop
+        // handles four output columns per thread with 32-bit indices, and takes a short cut when none of the four
+        // column codes carries a flag (the usual case): four shared-memory reads, one 16-byte store
+        const int Ci = (int)C;
+        for (int rr = 0; rr < R; ++rr) {
+            const int i = (int)(g * R) + rr;
+            if (i >= Ci) break;
+            const uint32_t cwi = code[i] | (inv ? 0x40000000u : 0u);
+            const bool row_wz = (cwi & 0x80000000u) != 0u, row_dead = (cwi & 0x40000000u) != 0u;
+            const uint32_t pi = cwi & 0x3FFFFFFFu;
+            const float *row = buf + (int64_t)rr * C;
+            float *orow = A + b * C * C + (int64_t)(Ci - 1 - i) * C;
+            const bool row_plain = !row_wz && !row_dead;
+            for (int jo = (int)threadIdx.x * 4; jo < Ci; jo += (int)blockDim.x * 4) {
+                const int jlo = Ci - 4 - jo;   // positions jlo+3 .. jlo <-> output columns jo .. jo+3
+                const uint4 cq = *reinterpret_cast<const uint4 *>(code + jlo);
+                float4 v;
+                if (row_plain && ((cq.x | cq.y | cq.z | cq.w) & 0xC0000000u) == 0u) {
+                    v = make_float4(row[cq.w], row[cq.z], row[cq.y], row[cq.x]);
+                } else {
+                    const uint32_t cws[4] = {cq.w, cq.z, cq.y, cq.x};
+                    float x[4];
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int64_t j = jlo + 3 - e;
-                    const uint32_t cw = cws[e];
-                    const uint32_t pj = cw & 0x3FFFFFFFu;
-                    float x;
-                    if (row_wz || (cw & 0x80000000u)) x = (i == j) ? 1.0f : 0.0f;
-                    else if (row_dead || (cw & 0x40000000u)) x = (pi == pj) ? 1.0f : 0.0f;
-                    else x = row[pj];
-                    if (i == j) x += dmp;
-                    v[e] = x;
+                    for (int e = 0; e < 4; ++e) {
+                        const int j = jlo + 3 - e;
+                        const uint32_t cw = cws[e];
+                        const uint32_t pj = cw & 0x3FFFFFFFu;
+                        if (row_wz || (cw & 0x80000000u)) x[e] = (i == j) ? 1.0f : 0.0f;
+                        else if (row_dead || (cw & 0x40000000u)) x[e] = (pi == pj) ? 1.0f : 0.0f;
+                        else x[e] = row[pj];
+                    }
+                    v = make_float4(x[0], x[1], x[2], x[3]);
                 }
-                *reinterpret_cast<float4 *>(A + b * C * C + (C - 1 - i) * C + jo) = make_float4(v[0], v[1], v[2], v[3]);
+                const int d = i - jlo;         // the diagonal position j == i is element 3 - d of this group
+                if ((unsigned)d < 4u) {
+                    if (d == 3) v.x += dmp; else if (d == 2) v.y += dmp; else if (d == 1) v.z += dmp; else v.w += dmp;
+                }
+                *reinterpret_cast<float4 *>(orow + jo) = v;
             }
         }
         __syncthreads();   // the buffer and (at a change of matrix) the code table are free again
