@@ -151,3 +151,33 @@ def test_hessian_error_does_not_grow_with_the_token_count():
         errs[T] = float((H[0].double() - H64).norm() / H64.norm())
         assert torch.equal(H[0], H[0].T)                       # the mirror image follows the same additions
     assert errs[2048] <= 2e-5 and errs[65536] <= 3e-5, errs
+
+
+def test_running_mean_over_batches_that_need_several_accumulation_passes():
+    """Two updates of 6000 and 9000 tokens (two and three accumulation passes each) in the running-mean form equal the
+    Hessian of the 15000 tokens at once, and both match float64; token lists with a gather, two slots of unequal
+    length."""
+    from forge import synth
+    ops = _ops()
+    C, T = 512, 15000
+    X = synth.student_t_activations(T, C, seed=9, device=DEV)
+    g = torch.Generator(device=DEV).manual_seed(9)
+    perm = torch.randperm(T, generator=g, device=DEV).to(torch.int32)
+    # slot 0 sees tokens perm[:6000] then perm[6000:15000]; slot 1 sees the first 100 tokens once
+    H = torch.zeros((2, C, C), dtype=torch.float32, device=DEV)
+    lists1 = torch.cat([perm[:6000], torch.arange(100, device=DEV, dtype=torch.int32)]).contiguous()
+    offs1 = torch.tensor([0, 6000, 6100], dtype=torch.int64, device=DEV)
+    ops.hessian_grouped(X, C, lists1, offs1, H)
+    n_prev = torch.tensor([6000, 100], dtype=torch.int64, device=DEV)
+    lists2 = perm[6000:].contiguous()
+    offs2 = torch.tensor([0, 9000, 9000], dtype=torch.int64, device=DEV)
+    ops.hessian_grouped(X, C, lists2, offs2, H, n_prev=n_prev)
+    Xd = X.double()
+    H0 = (2.0 / T) * (Xd.T @ Xd)
+    H1 = (2.0 / 100) * (Xd[:100].T @ Xd[:100])
+    assert float((H[0].double() - H0).norm() / H0.norm()) < 3e-5
+    assert float((H[1].double() - H1).norm() / H1.norm()) < 3e-5
+    assert torch.equal(H[0], H[0].T) and torch.equal(H[1], H[1].T)
+    one = torch.zeros((1, C, C), dtype=torch.float32, device=DEV)
+    ops.hessian_grouped(X, C, perm.contiguous(), torch.tensor([0, T], dtype=torch.int64, device=DEV), one)
+    assert float((H[0] - one[0]).norm() / one[0].norm()) < 2e-5
