@@ -36,7 +36,10 @@ __device__ __forceinline__ Best warp_argmax(Best x) {
     return x;
 }
 
-// mode 0: softmax scores, plain top-k; mode 1: sigmoid scores, plain top-k; mode 2: sigmoid, group-limited
+// mode 0: softmax scores, plain top-k; mode 1: sigmoid scores, plain top-k; mode 2: sigmoid, group-limited.
+// kPerLane = experts per lane this instance is compiled for (E <= 32 kPerLane): every scan over a token's scores is
+// unrolled to exactly that length.
+template <int kPerLane>
 __global__ void route_topk_kernel(const float *__restrict__ logits, const float *__restrict__ bias, int64_t T, int E,
                                   int k, int mode, int n_groups, int topk_groups, int32_t *__restrict__ ids,
                                   float *__restrict__ weights) {
@@ -45,11 +48,11 @@ __global__ void route_topk_kernel(const float *__restrict__ logits, const float 
     if (t >= T) return;
     const int npl = (E + 31) / 32;
     const float NEG = -3.0e38f;
-    float sel[kMaxPerLane];   // what the selection compares
-    float raw[kMaxPerLane];   // what is reported as the weight
+    float sel[kPerLane];   // what the selection compares
+    float raw[kPerLane];   // what is reported as the weight
     float mx = NEG;
 #pragma unroll
-    for (int j = 0; j < kMaxPerLane; ++j) {
+    for (int j = 0; j < kPerLane; ++j) {
         sel[j] = NEG;
         raw[j] = 0.0f;
         if (j < npl) {
@@ -74,7 +77,7 @@ __global__ void route_topk_kernel(const float *__restrict__ logits, const float 
         for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
         float sum = 0.0f;
 #pragma unroll
-        for (int j = 0; j < kMaxPerLane; ++j)
+        for (int j = 0; j < kPerLane; ++j)
             if (j < npl && j * 32 + lane < E) sum += expf(raw[j] - mx);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
@@ -90,7 +93,7 @@ __global__ void route_topk_kernel(const float *__restrict__ logits, const float 
             for (int rep = 0; rep < 2; ++rep) {
                 Best b{NEG, 0x7fffffff};
 #pragma unroll
-                for (int j = 0; j < kMaxPerLane; ++j) {
+                for (int j = 0; j < kPerLane; ++j) {
                     if (j < npl) {
                         const int e = j * 32 + lane;
                         if (e < E && e / gsz == g && e != taken) b = better(b, Best{sel[j], e});
@@ -111,7 +114,7 @@ __global__ void route_topk_kernel(const float *__restrict__ logits, const float 
             if (b.idx < n_groups) keep |= 1u << b.idx;
         }
 #pragma unroll
-        for (int j = 0; j < kMaxPerLane; ++j) {
+        for (int j = 0; j < kPerLane; ++j) {
             if (j < npl) {
                 const int e = j * 32 + lane;
                 if (e < E && !((keep >> (e / gsz)) & 1u)) sel[j] = NEG;
@@ -122,7 +125,7 @@ __global__ void route_topk_kernel(const float *__restrict__ logits, const float 
         Best b{NEG, 0x7fffffff};
         float w = 0.0f;
 #pragma unroll
-        for (int j = 0; j < kMaxPerLane; ++j) {
+        for (int j = 0; j < kPerLane; ++j) {
             if (j < npl) {
                 const int e = j * 32 + lane;
                 if (e < E) {
@@ -139,7 +142,7 @@ __global__ void route_topk_kernel(const float *__restrict__ logits, const float 
             if (weights) weights[t * k + r] = (mode == 0) ? expf(w - mx) / denom : w;
         }
 #pragma unroll
-        for (int j = 0; j < kMaxPerLane; ++j)
+        for (int j = 0; j < kPerLane; ++j)
             if (j < npl && j * 32 + lane == win.idx) sel[j] = NEG;
     }
 }
@@ -158,8 +161,18 @@ extern "C" int forge_route_topk(const float *logits, const float *bias, int64_t 
     }
     if (T == 0) return FORGE_OK;
     const int warps = 8;
-    route_topk_kernel<<<(unsigned)cdiv(T, warps), warps * 32, 0, (cudaStream_t)stream>>>(
-        logits, bias, T, E, k, mode, n_groups, topk_groups, topk_ids, topk_weights);
+    const dim3 grid((unsigned)cdiv(T, warps)), block(warps * 32);
+    cudaStream_t st = (cudaStream_t)stream;
+    const int npl = (E + 31) / 32;
+#define FORGE_ROUTE_LAUNCH(N) \
+    route_topk_kernel<N><<<grid, block, 0, st>>>(logits, bias, T, E, k, mode, n_groups, topk_groups, topk_ids, topk_weights)
+    if (npl <= 1) FORGE_ROUTE_LAUNCH(1);
+    else if (npl <= 2) FORGE_ROUTE_LAUNCH(2);
+    else if (npl <= 4) FORGE_ROUTE_LAUNCH(4);
+    else if (npl <= 8) FORGE_ROUTE_LAUNCH(8);
+    else if (npl <= 16) FORGE_ROUTE_LAUNCH(16);
+    else FORGE_ROUTE_LAUNCH(32);
+#undef FORGE_ROUTE_LAUNCH
     FORGE_NOTE_LAUNCH();
     return check_launch("forge_route_topk");
 }
