@@ -197,6 +197,20 @@ def reference_gpu_sample(shape, recipe, n_tokens_list, dev, seed=0):
     return e0.elapsed_time(e1) / 1e3
 
 
+def fixed_cost_in_tokens(Hd, I, recipe):
+    """What an expert costs whatever its traffic (factorisation, scale search, column solve), in units of one routed
+    token's cost (its share of the two Hessians and of the expert forward): the exchange rate of the placement.  From
+    the rates the kernels reach on one GPU: solver and factorisation ~1.1e14 algorithmic flop/s (R C^2 per matrix,
+    C^3/3 per Hessian; the triangular inverse of the SparseGPT path doubles the latter), the MSE search ~5.5e12
+    element-candidates/s, Hessian and expert forward ~1e15 flop/s.  19 600 tokens at hidden 7168 / inter 2048, 12 600
+    at 2048 / 768 with the MSE search."""
+    solve = (2.0 * I * Hd * Hd + Hd * I * I) / 1.1e14
+    factor = (Hd ** 3 + I ** 3) / 3.0 / 1.1e14 * (2.0 if recipe["algorithm"] == "sparsegptq" else 1.0)
+    search = (300.0 * Hd * I / 5.5e12) if recipe["quantization_scale"] == "mse" else 0.0
+    per_token = 2.0 * (Hd * Hd + I * I) / 1.0e15 + 4.0 * Hd * I / 1.0e15
+    return (solve + factor + search) / per_token
+
+
 def run_reference(args, rank, world):
     if rank != 0:
         return
@@ -295,9 +309,8 @@ def run_ours(args, rank, world, local_rank):
     remap = None
     if args.placement == "lpt" and world > 1:
         counts_all = torch.bincount(ids_host.reshape(-1).long(), minlength=E)
-        # an expert's fixed cost (factor, search, solve) in units of routed tokens: measured ~15k at hidden 2048
         owned = fdist.balance_experts(counts_all.tolist(), world, shape.n_shared, T,
-                                      fixed_cost_tokens=15000.0 * Hd / 2048.0)
+                                      fixed_cost_tokens=fixed_cost_in_tokens(Hd, I, recipe))
         table, spans = fdist.placement_tables(owned, E)
         remap = table.to(dev)
         my_ids = owned[rank]
