@@ -10,6 +10,7 @@ Rank 0 prints one JSON line.  `--impl reference` times the CPU restatement of th
 (oracle/) on the host cores over a bounded sample of the same workload.
 """
 import argparse
+import gc
 import json
 import os
 
@@ -427,6 +428,10 @@ def run_ours(args, rank, world, local_rank):
     def timed(fn, steps):
         """Total device time of `steps` calls (barrier + synchronize on both sides, max over ranks) and the per-step
         device times (events between the steps, max over ranks per step)."""
+        # the steps are queued from Python: a collection of the cyclic garbage collector in the middle of a step
+        # (hundreds of ms with this many live tensors) would leave the GPU waiting for the host
+        gc.collect()
+        gc.disable()
         barrier()
         torch.cuda.synchronize()
         evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
@@ -436,6 +441,7 @@ def run_ours(args, rank, world, local_rank):
             evs[i + 1].record()
         torch.cuda.synchronize()
         barrier()
+        gc.enable()
         total = max_over_ranks([evs[0].elapsed_time(evs[-1])])[0]
         per_step = max_over_ranks([evs[i].elapsed_time(evs[i + 1]) for i in range(steps)])
         return total, per_step
@@ -473,6 +479,13 @@ def run_ours(args, rank, world, local_rank):
     pt.enabled = False
     counts = out["counts"].cpu().double()
     del out
+    # every rank's own kernel time in that step (sum over its entry points): how even the placement is
+    phase_sums = [float(sum(phases.values()))]
+    if world > 1:
+        t = torch.zeros(world, dtype=torch.float64, device=dev)
+        t[rank] = phase_sums[0]
+        dist.all_reduce(t)
+        phase_sums = [round(float(v), 3) for v in t.tolist()]
     barrier()
     mem("after the device-resident phases")
 
@@ -680,7 +693,8 @@ def run_ours(args, rank, world, local_rank):
                 "clocks": clk, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline,
                 "cpu_baseline": cpu_base, "reference_same_gpu": ref_gpu,
                 "ms_per_step_median": sorted(per_step)[len(per_step) // 2],
-                "phases_ms_rank0": {k: round(v, 3) for k, v in sorted(phases.items(), key=lambda kv: -kv[1])}}
+                "phases_ms_rank0": {k: round(v, 3) for k, v in sorted(phases.items(), key=lambda kv: -kv[1])},
+                "kernel_ms_by_rank": phase_sums}
         print(json.dumps(line), flush=True)
 
 
