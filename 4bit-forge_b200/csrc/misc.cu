@@ -720,6 +720,55 @@ __global__ void int4_packed_dequant_kernel(const int32_t *__restrict__ packed, c
         }
     }
 }
+// The same for the usual checkpoint layout (bf16 output, every word inside one group).  A CTA walks a run of whole
+// rows with 32-bit indices (the 64-bit division per word of the kernel above costs more issue slots than the memory
+// system leaves); a thread keeps FOUR words in flight, taken 256 words apart, so that a warp's loads are whole 128-byte
+// lines and its stores whole 512-byte runs.
+constexpr int kI4Rows = 16;     // rows per CTA
+__global__ void __launch_bounds__(256) int4_packed_dequant_vec4_kernel(const int32_t *__restrict__ packed,
+                                                                       const float *__restrict__ scales, int64_t O,
+                                                                       int64_t I, int gs, int symmetric,
+                                                                       int scale_is_inv,
+                                                                       __nv_bfloat16 *__restrict__ out) {
+    const uint32_t IP = (uint32_t)(I / 8), G = (uint32_t)(I / gs), gw = (uint32_t)(gs / 8);   // words per row / group
+    const int64_t row0 = (int64_t)blockIdx.x * kI4Rows;
+    const uint32_t nrows = (uint32_t)imin64(kI4Rows, O - row0);
+    const uint32_t total = nrows * IP;
+    const int32_t *src = packed + row0 * IP;
+    const float *srow = scales + row0 * G;
+    __nv_bfloat16 *dst = out + row0 * I;
+    for (uint32_t w0 = threadIdx.x; w0 < total; w0 += 4 * 256) {
+        uint32_t word[4], r[4], c[4];
+        float sf[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const uint32_t w = w0 + q * 256;
+            const bool ok = w < total;
+            r[q] = ok ? w / IP : 0u;
+            c[q] = ok ? w - r[q] * IP : 0u;
+            word[q] = ok ? (uint32_t)__ldg(src + w) : 0u;
+            sf[q] = ok ? __ldg(srow + r[q] * G + c[q] / gw) : 1.0f;
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            if (w0 + q * 256 >= total) break;
+            const float s1 = scale_is_inv ? __fdiv_rn(1.0f, sf[q]) : sf[q];
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                int u = (int)((word[q] >> (4 * e)) & 0xFu);
+                if (symmetric && u >= 8) u -= 16;
+                v[e] = __fmul_rn((float)u, s1);
+            }
+            uint4 pk;
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]), h1 = __floats2bfloat162_rn(v[2], v[3]);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]), h3 = __floats2bfloat162_rn(v[6], v[7]);
+            pk.x = *reinterpret_cast<uint32_t *>(&h0); pk.y = *reinterpret_cast<uint32_t *>(&h1);
+            pk.z = *reinterpret_cast<uint32_t *>(&h2); pk.w = *reinterpret_cast<uint32_t *>(&h3);
+            *reinterpret_cast<uint4 *>(dst + (int64_t)r[q] * I + (int64_t)c[q] * 8) = pk;
+        }
+    }
+}
 extern "C" int forge_int4_packed_dequant(const int32_t *packed, const float *scales, int64_t O, int64_t I, int gs,
                                          int symmetric, int scale_is_inv, void *out, int out_dtype, void *stream) {
     FORGE_REQUIRE(packed && scales && out, "null pointer");
@@ -727,6 +776,13 @@ extern "C" int forge_int4_packed_dequant(const int32_t *packed, const float *sca
     FORGE_REQUIRE(I % 8 == 0 && I % gs == 0, "I must be a multiple of 8 and of the group size");
     FORGE_REQUIRE(out_dtype == FORGE_DTYPE_F32 || out_dtype == FORGE_DTYPE_BF16, "bad dtype");
     FORGE_REQUIRE((uintptr_t)out % 16 == 0, "output must be 16-byte aligned");
+    if (out_dtype == FORGE_DTYPE_BF16 && gs % 8 == 0 && I / 8 * kI4Rows < (1ll << 31) && cdiv(O, (int64_t)kI4Rows) < (1ll << 31)) {
+        const int blocks4 = (int)cdiv(O, (int64_t)kI4Rows);
+        int4_packed_dequant_vec4_kernel<<<blocks4, 256, 0, (cudaStream_t)stream>>>(
+            packed, scales, O, I, gs, symmetric, scale_is_inv, reinterpret_cast<__nv_bfloat16 *>(out));
+        FORGE_NOTE_LAUNCH();
+        return check_launch("forge_int4_packed_dequant");
+    }
     const int blocks = (int)imin64(cdiv(O * (I / 8), 256), 148 * 64);
     int4_packed_dequant_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(packed, scales, O, I, gs, symmetric,
                                                                         scale_is_inv, out, out_dtype); FORGE_NOTE_LAUNCH();

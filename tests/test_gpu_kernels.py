@@ -556,7 +556,10 @@ def test_int4_packed_dequant_against_reference_vectors(sym, inv):
     pk = torch.randint(-2 ** 31, 2 ** 31 - 1, (Ob, Ib // 8), generator=g, dtype=torch.int64).to(torch.int32)
     sc = torch.rand(Ob, Ib // 32, generator=g) * 0.01 + 1e-4
     big = ops.int4_packed_dequant(pk.cuda(), sc.cuda(), (Ob, Ib), sym, inv, dtype=torch.float32)
-    assert torch.equal(big.cpu(), O.int4_packed_dequant(pk, sc, (Ob, Ib), sym, inv))
+    want_big = O.int4_packed_dequant(pk, sc, (Ob, Ib), sym, inv)
+    assert torch.equal(big.cpu(), want_big)
+    big16 = ops.int4_packed_dequant(pk.cuda(), sc.cuda(), (Ob, Ib), sym, inv, dtype=torch.bfloat16)
+    assert torch.equal(big16.cpu(), want_big.to(torch.bfloat16))
 
 
 @pytest.mark.gpu
