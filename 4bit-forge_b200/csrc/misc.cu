@@ -907,30 +907,49 @@ extern "C" int forge_dequantize(const uint8_t *q, const float *scales, const flo
 // 16-byte load, one zero point (the 16 codes share a group), two packed words in one 8-byte store.  General path:
 // one thread per output word (8 codes), every code with its own group index.
 // --------------------------------------------------------------------------------------------
-__global__ void pack_int4_vec16_kernel(const uint8_t *__restrict__ q, const float *__restrict__ qzeros, int64_t rows,
-                                       int C16, int gs16, int G, int32_t *__restrict__ packed) {
-    const int64_t total = rows * C16;      // 16-code chunks
-    for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < total;
-         w += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t r = w / C16;
-        const int j = (int)(w - r * C16);
-        const uint4 raw = reinterpret_cast<const uint4 *>(q)[w];
-        const int z = (int)__ldg(qzeros + r * G + j / gs16);
-        const uint32_t in[4] = {raw.x, raw.y, raw.z, raw.w};
-        uint32_t out[2];
+constexpr int kP4Rows = 16;     // rows per CTA
+__global__ void __launch_bounds__(256) pack_int4_vec16_kernel(const uint8_t *__restrict__ q,
+                                                              const float *__restrict__ qzeros, int64_t rows, int C16,
+                                                              int gs16, int G, int32_t *__restrict__ packed) {
+    // a CTA walks a run of whole rows with 32-bit indices; a thread keeps four 16-code chunks in flight, 256 chunks
+    // apart (a warp's loads are whole 512-byte runs, its stores whole 256-byte runs)
+    const int64_t row0 = (int64_t)blockIdx.x * kP4Rows;
+    const uint32_t nrows = (uint32_t)imin64(kP4Rows, rows - row0);
+    const uint32_t total = nrows * (uint32_t)C16;
+    const uint4 *src = reinterpret_cast<const uint4 *>(q) + row0 * C16;
+    const float *zrow = qzeros + row0 * G;
+    uint2 *dst = reinterpret_cast<uint2 *>(packed) + row0 * C16;
+    for (uint32_t w0 = threadIdx.x; w0 < total; w0 += 4 * 256) {
+        uint4 raw[4];
+        int z[4];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            uint32_t acc = 0;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int b = (int)((in[2 * h + (i >> 2)] >> (8 * (i & 3))) & 0xFFu);
-                // int8(code) - int8(zero) + 8, taken as a byte, shifted in: additions carry like pack_to_int32's sum
-                const uint32_t u = (uint32_t)(uint8_t)(int8_t)((int8_t)(int8_t)b - (int8_t)z + 8);
-                acc += u << (4 * i);
-            }
-            out[h] = acc;
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t w = w0 + k * 256;
+            const bool ok = w < total;
+            const uint32_t r = ok ? w / (uint32_t)C16 : 0u;
+            const uint32_t j = ok ? w - r * (uint32_t)C16 : 0u;
+            raw[k] = ok ? __ldg(src + w) : make_uint4(0u, 0u, 0u, 0u);
+            z[k] = ok ? (int)__ldg(zrow + r * (uint32_t)G + j / (uint32_t)gs16) : 0;
         }
-        reinterpret_cast<uint2 *>(packed)[w] = make_uint2(out[0], out[1]);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (w0 + k * 256 >= total) break;
+            const uint32_t in[4] = {raw[k].x, raw[k].y, raw[k].z, raw[k].w};
+            uint32_t out[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t acc = 0;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int b = (int)((in[2 * h + (i >> 2)] >> (8 * (i & 3))) & 0xFFu);
+                    // int8(code) - int8(zero) + 8, taken as a byte, shifted in: additions carry like pack_to_int32's sum
+                    const uint32_t u = (uint32_t)(uint8_t)(int8_t)((int8_t)(int8_t)b - (int8_t)z[k] + 8);
+                    acc += u << (4 * i);
+                }
+                out[h] = acc;
+            }
+            dst[w0 + k * 256] = make_uint2(out[0], out[1]);
+        }
     }
 }
 
@@ -968,9 +987,9 @@ extern "C" int forge_pack_int4(const uint8_t *q, const float *qzeros, int64_t ro
     FORGE_REQUIRE(q && qzeros && packed, "null pointer");
     FORGE_REQUIRE(rows > 0 && C > 0 && gs > 0, "bad sizes");
     const int64_t G = cdiv(C, gs), CP = cdiv(C, 8);
-    if (C % 16 == 0 && gs % 16 == 0 && (uintptr_t)q % 16 == 0 && (uintptr_t)packed % 8 == 0 && C / 16 < (1 << 30)) {
-        const int64_t chunks = rows * (C / 16);
-        const int blocks = (int)imin64(cdiv(chunks, 256), 148 * 16);
+    if (C % 16 == 0 && gs % 16 == 0 && (uintptr_t)q % 16 == 0 && (uintptr_t)packed % 8 == 0 && C / 16 < (1 << 26) &&
+        cdiv(rows, (int64_t)kP4Rows) < (1ll << 31)) {
+        const int blocks = (int)cdiv(rows, (int64_t)kP4Rows);
         pack_int4_vec16_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(q, qzeros, rows, (int)(C / 16), gs / 16, (int)G,
                                                                          packed);
         FORGE_NOTE_LAUNCH();
