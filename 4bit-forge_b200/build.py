@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libforge_b200.so")
 SOURCES = ["misc.cu", "quant_grid.cu", "solver.cu", "chol.cu", "hessian.cu", "noalloc.cu", "route.cu", "expert_fwd.cu",
-           "recon.cu", "sparse14_gemm.cu"]
+           "recon.cu", "sparse14_gemm.cu", "mma_rate.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]

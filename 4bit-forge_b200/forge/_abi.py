@@ -39,6 +39,7 @@ _PROTOS = {
                                   _ptr, _c_i64, _ptr, _ptr, _ptr, _ptr, _ptr]),
     "forge_hessian_grouped": (_c_int, [_ptr, _c_i64, _c_i64, _c_i64, _ptr, _c_i64, _ptr, _c_int, _ptr, _ptr, _c_int, _ptr, _ptr]),
     "forge_selftest_bounded_wait": (_c_int, [_ptr, _c_i64, _ptr]),
+    "forge_selftest_mma_rate": (_c_int, [_c_int, _c_int, _c_int, _ptr, _ptr, _ptr]),
     "forge_int4_packed_dequant": (_c_int, [_ptr, _ptr, _c_i64, _c_i64, _c_int, _c_int, _c_int, _ptr, _c_int, _ptr]),
     "forge_mxfp4_dequant": (_c_int, [_ptr, _ptr, _c_i64, _c_i64, _ptr, _c_int, _ptr]),
     "forge_counts_add": (_c_int, [_ptr, _ptr, _c_int, _ptr]),

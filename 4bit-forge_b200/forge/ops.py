@@ -343,3 +343,16 @@ def sparse14_moe_w2(W2, X2, offsets, active, token_idx=None, n_out=None) -> torc
     """Y[m, :] = X2[m, :] @ What_e^T for the expert e that owns permuted position m (forge_sparse14_moe_w2)."""
     return _sparse14_moe("forge_sparse14_moe_w2", W2, X2, offsets, active, token_idx,
                          X2.shape[0] if n_out is None else int(n_out), False)
+
+
+def mma_issue_cycles(N: int = 128, iters: int = 2000, pattern: bool = True) -> float:
+    """Cycles per tcgen05.mma kind::tf32 M128 x N x K8 when one thread issues them back to back on every SM
+    (forge_selftest_mma_rate): the issue ceiling of the solver's and the factorisation's MMA shape on this GPU."""
+    dev = torch.device("cuda", torch.cuda.current_device())
+    cyc = torch.zeros(1, dtype=torch.int64, device=dev)
+    st = torch.zeros(1, dtype=torch.int32, device=dev)
+    call("forge_selftest_mma_rate", int(N), int(iters), int(bool(pattern)), ptr(cyc), ptr(st), stream_ptr())
+    vals = torch.cat([cyc, st.to(torch.int64)]).tolist()      # one host read
+    if vals[1] != 0:
+        raise RuntimeError(f"forge_selftest_mma_rate: status {vals[1]}")
+    return vals[0] / float(iters)

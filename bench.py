@@ -621,12 +621,17 @@ def run_ours(args, rank, world, local_rank):
                         "note": "fp32 algorithm as TF32 x3 on tcgen05; the column loop between the MMAs is a serial "
                                 "dependency chain per weight row"}
             if top == "forge_gptq_solve_batched":
-                # The solver's MMAs are M128 x N128 x K8 kind::tf32 (a 128-column block per accumulator).  A stand-alone
-                # issue loop of that instruction sustains one per 101 cycles per SM on this part whatever the operand
-                # layout and the number of accumulators (N = 256: 161 cycles), i.e. 2592 flop/cycle/SM: the ceiling of
-                # any kernel built from this instruction shape, at the SM clock seen during the timed region.
+                # The solver's MMAs are M128 x N128 x K8 kind::tf32 (a 128-column block per accumulator).  The library's
+                # diagnostic measures what one such MMA costs when a thread issues them back to back on every SM (64
+                # cycles on this pool's B200s = 4096 flop/cycle/SM): the ceiling of any kernel built from this
+                # instruction shape, taken at the SM clock seen during the timed region.
                 mhz = (clk or {}).get("sm_mhz") or 1965.0
-                floor = 2.0 * 128 * 128 * 8 / 101.1 * 148 * mhz * 1e6 / 1e12
+                try:
+                    cyc = ops.mma_issue_cycles(128, 2000)      # measured on this GPU, now
+                except RuntimeError:
+                    cyc = 64.0                                 # the figure of this pool's B200s
+                roofline["tf32_m128n128k8_cycles_per_mma"] = cyc
+                floor = 2.0 * 128 * 128 * 8 / cyc * 148 * mhz * 1e6 / 1e12
                 roofline["tf32_m128n128k8_issue_peak_tflops"] = floor
                 roofline["executed_frac_of_issue_peak"] = 3.0 * ach / floor
         else:

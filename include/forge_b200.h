@@ -118,6 +118,13 @@ int forge_hessian_grouped(const void *X_bf16, int64_t n_rows, int64_t ldx, int64
  * and returns normally.  No counterpart in the reference (it has no device-side waits). */
 int forge_selftest_bounded_wait(int32_t *status, int64_t budget_cycles, void *stream);
 
+/* Diagnostic: cycles[0] (device int64) = clock cycles one thread needs to issue and complete `iters` back-to-back
+ * tcgen05.mma kind::tf32 M128 x N x K8 (N = 64, 128 or 256; operands in shared memory — zeros, or pseudo-random values
+ * with pattern != 0 —, accumulator in tensor memory), measured on SM 0 while every SM runs the same loop.  cycles / iters is the issue ceiling of the instruction
+ * the solver and the Cholesky are built from; the benchmark reports its kernels against it.  The only wait in the
+ * kernel is bounded (status = FORGE_ERR_TIMEOUT if it runs out).  No counterpart in the reference. */
+int forge_selftest_mma_rate(int N, int iters, int pattern, int64_t *cycles, int32_t *status, void *stream);
+
 /* n_prev[b] += offsets[b+1]-offsets[b]  (GPTQ.update's num_samples.add_, forge/gptq.py:80) */
 int forge_counts_add(int64_t *n_prev, const int64_t *offsets, int nb, void *stream);
 

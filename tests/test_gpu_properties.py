@@ -181,3 +181,13 @@ def test_running_mean_over_batches_that_need_several_accumulation_passes():
     one = torch.zeros((1, C, C), dtype=torch.float32, device=DEV)
     ops.hessian_grouped(X, C, perm.contiguous(), torch.tensor([0, T], dtype=torch.int64, device=DEV), one)
     assert float((H[0] - one[0]).norm() / one[0].norm()) < 2e-5
+
+
+
+def test_mma_issue_rate_diagnostic():
+    """forge_selftest_mma_rate: the back-to-back cost of the solver's MMA shape, a plausible number of cycles, and the
+    wider shape costs more."""
+    ops = _ops()
+    c128 = ops.mma_issue_cycles(128, 1000)
+    c256 = ops.mma_issue_cycles(256, 1000)
+    assert 40.0 < c128 < 400.0 and c128 < c256 < 2.5 * c128, (c128, c256)
